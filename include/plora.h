@@ -1,0 +1,219 @@
+/* plora — B200 (sm_100a) implementation of pocket-engine's batched multi-adapter
+ * LoRA path behind a C ABI.
+ *
+ * Every entry point names the pocket-engine interface it replaces (file:line in
+ * the pocket-engine source tree). The binding a pocket-engine maintainer would
+ * add on the Rust side is a plain `extern "C"` block over these signatures; all
+ * device addresses are uint64_t like the engine's own `u64` pointers, streams are
+ * the CUstream / cudaStream_t handle passed as void*.
+ *
+ * Threading: a handle is driven from the one thread that created it (as
+ * src/gpu.rs:1-3 requires of the engine); plora_adapter_prepare may run on any
+ * thread (src/lora.rs:283-305).
+ *
+ * Stream semantics: plora_shrink / plora_expand / plora_step_begin /
+ * plora_meta_build issue no host synchronisation and no allocation
+ * (src/linear.rs:425-426), so a step can be captured into a CUDA graph.
+ *
+ * There is no CPU fallback: every compute entry point fails with
+ * PLORA_ERR_CUDA when no sm_100 device is usable.
+ */
+#ifndef PLORA_H
+#define PLORA_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PLORA_MAX_PARTS 4  /* src/lora.rs:14 */
+#define PLORA_RANK_STEP 16 /* src/lora.rs:16 */
+#define PLORA_TILE 16      /* src/lora.rs:18 */
+
+/* Error::Cuda / Error::Config of the engine (src/gpu.rs:19-35) as integer codes. */
+enum {
+    PLORA_OK = 0,
+    PLORA_ERR_CUDA = 1,       /* a CUDA call failed; text in plora_last_error */
+    PLORA_ERR_CONFIG = 2,     /* malformed adapter or site description */
+    PLORA_ERR_RANK = 3,       /* rank over max_rank (src/lora.rs:332-337) */
+    PLORA_ERR_UNKNOWN_ID = 4, /* adapter id is not loaded (src/lora.rs:590-593) */
+    PLORA_ERR_DUPLICATE = 5,  /* name already loaded (src/lora.rs:563-568) */
+    PLORA_ERR_NO_SLOT = 6,    /* no GPU slot can take the adapter now */
+    PLORA_ERR_TIMEOUT = 7,    /* a bounded device-side wait ran out */
+    PLORA_ERR_ARG = 8,        /* bad argument (null, misaligned, out of range) */
+    PLORA_ERR_CAPACITY = 9    /* more tokens / tiles / sequences than the handle was made for */
+};
+
+typedef struct plora plora_t;                 /* src/lora.rs:416-442  Loras */
+typedef struct plora_adapter plora_adapter_t; /* src/lora.rs:82-88    Adapter */
+typedef struct plora_slots plora_slots_t;     /* src/sched.rs:410-420 LoraSlots */
+
+/* src/lora.rs:33-41 SitePart. heads_start < 0 is Heads::None (src/lora.rs:23-31). */
+typedef struct {
+    const char* module;
+    int32_t rows;
+    int32_t off;
+    int32_t heads_start;
+    int32_t heads_block;
+} plora_site_part;
+
+/* src/lora.rs:43-50 Site */
+typedef struct {
+    int32_t layer;
+    int32_t cols;
+    int32_t n_parts;
+    int32_t col_heads_start;
+    int32_t col_heads_block;
+    plora_site_part parts[PLORA_MAX_PARTS];
+} plora_site;
+
+/* src/lora.rs:91-95 Factors, keyed as in Modules (src/lora.rs:139): f32, scale already folded into b
+ * (src/lora.rs:225-228). a_len / b_len carry the element counts so shape mismatches are caught
+ * (src/lora.rs:325-330). */
+typedef struct {
+    int32_t layer;
+    int32_t r;
+    const char* module;
+    const float* a;
+    const float* b;
+    uint64_t a_len;
+    uint64_t b_len;
+} plora_module;
+
+/* src/lora.rs:59-70 Desc == src/kernels/lora.cuh:7-16 LoraDesc; 112 bytes. */
+typedef struct {
+    uint64_t a;
+    uint64_t b[PLORA_MAX_PARTS];
+    int32_t rank;
+    int32_t r[PLORA_MAX_PARTS];
+    int32_t r_off[PLORA_MAX_PARTS];
+    int32_t off[PLORA_MAX_PARTS];
+    int32_t rows[PLORA_MAX_PARTS];
+    int32_t pad_;
+} plora_desc;
+
+/* src/lora.rs:445-452 Hook (+ the layer's input width, which Linear keeps itself: src/linear.rs:44-45) */
+typedef struct {
+    uint64_t table;
+    int32_t parts;
+    int32_t max_rows;
+    int32_t parity;
+    int32_t cols;
+    int32_t site;
+    int32_t pad_;
+} plora_hook;
+
+/* src/lora.rs:455-467 StepLora. `segs` is new: the step's tokens regrouped by slot on the device. */
+typedef struct {
+    uint64_t tiles;
+    uint64_t s;
+    uint64_t s_stride;
+    uint64_t segs;
+    int32_t max_tiles;
+    int32_t lds;
+} plora_step;
+
+/* ---- registry: src/lora.rs ---- */
+
+/* Loras::new (src/lora.rs:470-523). max_seqs sizes the tile region as Meta::max_lora_tiles does
+ * (src/model.rs:1346-1348). Unlike the engine, an odd number of sites is accepted. */
+int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_heads, int value_heads,
+                 int max_slots, int max_rank, int max_tokens, int max_seqs, int device, plora_t** out);
+void plora_destroy(plora_t* h);
+/* text of the last failure on this handle (h may be NULL for plora_create failures) */
+const char* plora_last_error(const plora_t* h);
+/* Loras::bytes (src/lora.rs:526-528) */
+uint64_t plora_bytes(const plora_t* h);
+uint64_t plora_slot_bytes(const plora_t* h);
+/* device addresses the tests and multi-GPU callers need: pool, tables, S */
+uint64_t plora_pool_ptr(const plora_t* h);
+uint64_t plora_tables_ptr(const plora_t* h);
+uint64_t plora_s_ptr(const plora_t* h);
+int plora_max_lora_tiles(const plora_t* h);
+/* how many K-splits the shrink of `site` writes (each [max_tokens, lds] f32, s_stride bytes apart) */
+int plora_site_splits(const plora_t* h, int site);
+
+/* Prep::prepare (src/lora.rs:307-411); tiled_file is read_gguf's flag (src/lora.rs:280). Thread-safe. */
+int plora_adapter_prepare(const plora_t* h, const char* name, const plora_module* modules, int n_modules,
+                          int tiled_file, plora_adapter_t** out);
+void plora_adapter_drop(plora_adapter_t* a);
+/* Adapter.rank / len / the host image of the slot, for inspection */
+int plora_adapter_rank(const plora_adapter_t* a);
+uint64_t plora_adapter_len(const plora_adapter_t* a);
+const uint8_t* plora_adapter_data(const plora_adapter_t* a);
+const char* plora_adapter_error(void); /* thread-local text of the last failed prepare */
+/* the Desc that Loras::upload would write for `site` with the slab at `base` (src/lora.rs:597-615) */
+int plora_adapter_desc(const plora_t* h, const plora_adapter_t* a, int site, uint64_t base, plora_desc* out);
+
+/* Loras::insert / retire / free / id / names (src/lora.rs:540-585). insert takes ownership. */
+int plora_insert(plora_t* h, plora_adapter_t* a, uint32_t* id);
+int plora_retire(plora_t* h, const char* name, uint32_t* id);
+int plora_free(plora_t* h, uint32_t id);
+int plora_id(const plora_t* h, const char* name, uint32_t* id);
+/* names, sorted, '\n'-separated into buf; returns the count */
+int plora_names(const plora_t* h, char* buf, size_t cap);
+/* Loras::upload (src/lora.rs:589-623): slab and descriptors, stream-ordered */
+int plora_upload(plora_t* h, int slot, uint32_t id, void* stream);
+/* Loras::hook (src/lora.rs:530-538) */
+int plora_hook_of(const plora_t* h, int site, plora_hook* out);
+/* the pinned mirror of one descriptor (src/lora.rs:596-615), for inspection */
+int plora_desc_of(const plora_t* h, int site, int slot, plora_desc* out);
+
+/* ---- scheduler side: src/sched.rs ---- */
+
+/* Scheduler::with_lora_slots (src/sched.rs:550-558) */
+plora_slots_t* plora_slots_new(int slots);
+void plora_slots_free(plora_slots_t* s);
+int plora_slots_holding(const plora_slots_t* s, uint32_t adapter);   /* src/sched.rs:422-424; 0 = none */
+int plora_slots_can_place(const plora_slots_t* s, uint32_t adapter); /* src/sched.rs:425-427 */
+int plora_slots_place(plora_slots_t* s, uint32_t adapter);           /* src/sched.rs:430-448; -1 = cannot */
+void plora_slots_release(plora_slots_t* s, int slot);                /* src/sched.rs:846-849 */
+void plora_slots_forget(plora_slots_t* s, uint32_t adapter);         /* src/sched.rs:569-572 */
+/* step.lora_loads = take(loads) (src/sched.rs:1018) */
+int plora_slots_take_loads(plora_slots_t* s, int32_t* slot_out, uint32_t* id_out, int cap);
+
+/* Scheduler::plan's tile count (src/sched.rs:1019-1025) */
+int plora_plan_tiles(const int32_t* row_n, const int32_t* row_slot, int n_rows);
+/* Scheduler::fill's tile words (src/sched.rs:1096-1104,1189): [count,(start,len,slot) x count];
+ * returns the count or -1 when it would pass cap_tiles */
+int plora_fill_tiles(const int32_t* row_n, const int32_t* row_slot, int n_rows, int32_t* words, int cap_tiles);
+
+/* ---- the step: src/model.rs:1603-1618 Act::lora_step and the metadata it points into ---- */
+
+/* Device-side replacement of the tile part of Scheduler::fill + Act::upload_meta: from the step's
+ * cumulative token offsets cu[n_seqs+1] and each sequence's slot (both i32, on the device) write the
+ * tile words into the handle's metadata, bit-exact with plora_fill_tiles. No host round trip. */
+int plora_meta_build(plora_t* h, uint64_t cu_dev, uint64_t seq_slot_dev, int n_seqs, void* stream);
+/* The engine's own route: tile words written on the host (pinned or pageable), copied stream-ordered. */
+int plora_meta_upload(plora_t* h, const int32_t* words, void* stream);
+/* Act::lora_step: regroups the handle's tile words by slot on the device (once per step, before the
+ * first layer) and returns the per-step handle. max_tiles bounds the launch grids (src/engine.rs:448-451). */
+int plora_step_begin(plora_t* h, int max_tiles, void* stream, plora_step* out);
+uint64_t plora_tiles_ptr(const plora_t* h);
+
+/* ---- Linear::forward's bracket: src/linear.rs:428-443,844-921 ---- */
+
+/* Linear::lora_shrink (src/linear.rs:853-885): S = x A^T for every slot present, all parts at once.
+ * x: [rows, cols] bf16 row-major, 16-byte aligned. Launches on `stream` (the engine's side stream). */
+int plora_shrink(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, int rows, void* stream);
+/* Linear::lora_expand (src/linear.rs:889-921): y[:, off_p ..] += S_p B_p^T per part, bf16 (one rounding
+ * of f32(y)+acc) or f32 in place. */
+int plora_expand(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
+                 int f32_out, void* stream);
+/* Gpu::fork / Gpu::join (src/gpu.rs:849-901): order `side` after `main`, and `main` after `side`. */
+int plora_fork(plora_t* h, void* main_stream, void* side_stream);
+int plora_join(plora_t* h, void* main_stream, void* side_stream);
+
+/* Runs of contiguous tokens of one slot at least this long leave the gather kernels for the
+ * tensor-core tile kernels (no counterpart in the engine, whose tiles are always 16 tokens). */
+int plora_set_run_min(plora_t* h, int tokens);
+
+/* Device status word: 0, or the PLORA_ERR_* a kernel recorded (bounded wait ran out, capacity).
+ * Synchronises the device. */
+int plora_device_status(plora_t* h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

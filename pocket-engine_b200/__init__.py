@@ -1,0 +1,509 @@
+"""Host-side mirror of pocket-engine's adapter interface over the plora C ABI.
+
+The names follow the engine (src/lora.rs, src/sched.rs, src/linear.rs): ``Site``/``SitePart``,
+``Loras`` (the registry), ``Prep`` (off-thread preparation), ``Hook``, ``StepLora``, ``LoraSlots``
+(the scheduler's slot policy), ``fill_tiles`` (the tile rule of ``Scheduler::fill``) and ``Linear``
+(the bracket ``Linear::forward`` puts around a layer's own matrix multiply).
+
+Everything that computes goes through ``libplora.so``; importing this package without the built
+library raises, and there is no CPU fallback.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libplora.so")
+
+MAX_PARTS = 4   # src/lora.rs:14
+RANK_STEP = 16  # src/lora.rs:16
+TILE = 16       # src/lora.rs:18
+
+OK, ERR_CUDA, ERR_CONFIG, ERR_RANK, ERR_UNKNOWN_ID, ERR_DUPLICATE, ERR_NO_SLOT, ERR_TIMEOUT, ERR_ARG, \
+    ERR_CAPACITY = range(10)
+_CODE_NAMES = ["ok", "cuda", "config", "rank", "unknown id", "duplicate", "no slot", "timeout", "argument",
+               "capacity"]
+
+
+class PloraError(RuntimeError):
+    """Error::Cuda / Error::Config of the engine (src/gpu.rs:19-35)."""
+
+    def __init__(self, code, text):
+        super().__init__(f"plora [{_CODE_NAMES[code] if 0 <= code < len(_CODE_NAMES) else code}]: {text}")
+        self.code = code
+        self.text = text
+
+
+class CSitePart(C.Structure):
+    _fields_ = [("module", C.c_char_p), ("rows", C.c_int32), ("off", C.c_int32), ("heads_start", C.c_int32),
+                ("heads_block", C.c_int32)]
+
+
+class CSite(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("cols", C.c_int32), ("n_parts", C.c_int32), ("col_heads_start", C.c_int32),
+                ("col_heads_block", C.c_int32), ("parts", CSitePart * MAX_PARTS)]
+
+
+class CModule(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("r", C.c_int32), ("module", C.c_char_p), ("a", C.POINTER(C.c_float)),
+                ("b", C.POINTER(C.c_float)), ("a_len", C.c_uint64), ("b_len", C.c_uint64)]
+
+
+class Desc(C.Structure):
+    """src/lora.rs:59-70"""
+    _fields_ = [("a", C.c_uint64), ("b", C.c_uint64 * MAX_PARTS), ("rank", C.c_int32), ("r", C.c_int32 * MAX_PARTS),
+                ("r_off", C.c_int32 * MAX_PARTS), ("off", C.c_int32 * MAX_PARTS), ("rows", C.c_int32 * MAX_PARTS),
+                ("pad_", C.c_int32)]
+
+
+class Hook(C.Structure):
+    """src/lora.rs:445-452"""
+    _fields_ = [("table", C.c_uint64), ("parts", C.c_int32), ("max_rows", C.c_int32), ("parity", C.c_int32),
+                ("cols", C.c_int32), ("site", C.c_int32), ("pad_", C.c_int32)]
+
+
+class StepLora(C.Structure):
+    """src/lora.rs:455-467"""
+    _fields_ = [("tiles", C.c_uint64), ("s", C.c_uint64), ("s_stride", C.c_uint64), ("segs", C.c_uint64),
+                ("max_tiles", C.c_int32), ("lds", C.c_int32)]
+
+
+assert C.sizeof(Desc) == 112
+
+# name -> (restype, argtypes); also the list of every symbol include/plora.h declares
+_P = C.c_void_p
+_I = C.c_int
+_U64 = C.c_uint64
+_I32P = C.POINTER(C.c_int32)
+_U32P = C.POINTER(C.c_uint32)
+SYMBOLS = {
+    "plora_create": (_I, [C.POINTER(CSite), _I, _I, _I, _I, _I, _I, _I, _I, _I, C.POINTER(_P)]),
+    "plora_destroy": (None, [_P]),
+    "plora_last_error": (C.c_char_p, [_P]),
+    "plora_bytes": (_U64, [_P]),
+    "plora_slot_bytes": (_U64, [_P]),
+    "plora_pool_ptr": (_U64, [_P]),
+    "plora_tables_ptr": (_U64, [_P]),
+    "plora_s_ptr": (_U64, [_P]),
+    "plora_max_lora_tiles": (_I, [_P]),
+    "plora_site_splits": (_I, [_P, _I]),
+    "plora_adapter_prepare": (_I, [_P, C.c_char_p, C.POINTER(CModule), _I, _I, C.POINTER(_P)]),
+    "plora_adapter_drop": (None, [_P]),
+    "plora_adapter_rank": (_I, [_P]),
+    "plora_adapter_len": (_U64, [_P]),
+    "plora_adapter_data": (C.POINTER(C.c_uint8), [_P]),
+    "plora_adapter_error": (C.c_char_p, []),
+    "plora_adapter_desc": (_I, [_P, _P, _I, _U64, C.POINTER(Desc)]),
+    "plora_insert": (_I, [_P, _P, _U32P]),
+    "plora_retire": (_I, [_P, C.c_char_p, _U32P]),
+    "plora_free": (_I, [_P, C.c_uint32]),
+    "plora_id": (_I, [_P, C.c_char_p, _U32P]),
+    "plora_names": (_I, [_P, C.c_char_p, C.c_size_t]),
+    "plora_upload": (_I, [_P, _I, C.c_uint32, _P]),
+    "plora_hook_of": (_I, [_P, _I, C.POINTER(Hook)]),
+    "plora_desc_of": (_I, [_P, _I, _I, C.POINTER(Desc)]),
+    "plora_slots_new": (_P, [_I]),
+    "plora_slots_free": (None, [_P]),
+    "plora_slots_holding": (_I, [_P, C.c_uint32]),
+    "plora_slots_can_place": (_I, [_P, C.c_uint32]),
+    "plora_slots_place": (_I, [_P, C.c_uint32]),
+    "plora_slots_release": (None, [_P, _I]),
+    "plora_slots_forget": (None, [_P, C.c_uint32]),
+    "plora_slots_take_loads": (_I, [_P, _I32P, _U32P, _I]),
+    "plora_plan_tiles": (_I, [_I32P, _I32P, _I]),
+    "plora_fill_tiles": (_I, [_I32P, _I32P, _I, _I32P, _I]),
+    "plora_meta_build": (_I, [_P, _U64, _U64, _I, _P]),
+    "plora_meta_upload": (_I, [_P, _I32P, _P]),
+    "plora_step_begin": (_I, [_P, _I, _P, C.POINTER(StepLora)]),
+    "plora_tiles_ptr": (_U64, [_P]),
+    "plora_shrink": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _U64, _I, _P]),
+    "plora_expand": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _U64, _I, _I, _P]),
+    "plora_fork": (_I, [_P, _P, _P]),
+    "plora_join": (_I, [_P, _P, _P]),
+    "plora_set_run_min": (_I, [_P, _I]),
+    "plora_device_status": (_I, [_P]),
+}
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python pocket-engine_b200/build.py` "
+                          "(there is no fallback path)")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SYMBOLS.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+# ------------------------------------------------------------------------------------------ bf16
+
+def bf16_bits(x):
+    """f32 array -> bf16 bit patterns (uint16), round to nearest even."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = ((u >> 16) & 1) + np.uint32(0x7FFF)
+    return ((u + r) >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(bits):
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+# ------------------------------------------------------------------------------------- sites
+
+class Heads:
+    """src/lora.rs:23-31; ``None`` in a field stands for Heads::None."""
+
+    def __init__(self, start, block):
+        self.start, self.block = start, block
+
+
+class SitePart:
+    """src/lora.rs:33-41"""
+
+    def __init__(self, module, rows, off, heads=None):
+        self.module, self.rows, self.off, self.heads = module, rows, off, heads
+
+
+class Site:
+    """src/lora.rs:43-50"""
+
+    def __init__(self, layer, cols, parts, col_heads=None):
+        self.layer, self.cols, self.parts, self.col_heads = layer, cols, list(parts), col_heads
+
+    @staticmethod
+    def fused(layer, cols, modules):
+        """A site whose parts are laid out back to back: ``modules`` is [(module path, rows), ...]."""
+        parts, off = [], 0
+        for m, rows in modules:
+            parts.append(SitePart(m, rows, off))
+            off += rows
+        return Site(layer, cols, parts)
+
+    def max_rows(self):  # src/lora.rs:52-56
+        return max((p.rows for p in self.parts), default=0)
+
+    def width(self):
+        return max(p.off + p.rows for p in self.parts)
+
+    def _c(self):
+        c = CSite()
+        c.layer, c.cols, c.n_parts = self.layer, self.cols, len(self.parts)
+        c.col_heads_start = self.col_heads.start if self.col_heads else -1
+        c.col_heads_block = self.col_heads.block if self.col_heads else 0
+        for i, p in enumerate(self.parts):
+            c.parts[i].module = p.module.encode()
+            c.parts[i].rows, c.parts[i].off = p.rows, p.off
+            c.parts[i].heads_start = p.heads.start if p.heads else -1
+            c.parts[i].heads_block = p.heads.block if p.heads else 0
+        return c
+
+
+class Factors:
+    """src/lora.rs:91-95: one module's A [r, cols] and B [rows, r] in f32, scale folded into B."""
+
+    def __init__(self, layer, module, a, b):
+        self.layer, self.module = layer, module
+        self.a = np.ascontiguousarray(a, dtype=np.float32)
+        self.b = np.ascontiguousarray(b, dtype=np.float32)
+        self.r = self.a.shape[0]
+
+    @staticmethod
+    def scaled(layer, module, a, b, scale):
+        """Folds ``scale`` into B in f32 as read_peft does (src/lora.rs:225-228)."""
+        b = np.asarray(b, dtype=np.float32) * np.float32(scale)
+        return Factors(layer, module, a, b)
+
+
+class Adapter:
+    """src/lora.rs:82-88. Owns the prepared host image until it is inserted into a registry."""
+
+    def __init__(self, ptr, name):
+        self._ptr, self.name = ptr, name
+
+    @property
+    def rank(self):
+        return lib.plora_adapter_rank(self._ptr)
+
+    @property
+    def len(self):
+        return lib.plora_adapter_len(self._ptr)
+
+    def bytes(self):
+        n = self.len
+        if n == 0:
+            return np.zeros(0, np.uint8)
+        return np.ctypeslib.as_array(lib.plora_adapter_data(self._ptr), shape=(n,)).copy()
+
+    def drop(self):
+        if self._ptr:
+            lib.plora_adapter_drop(self._ptr)
+            self._ptr = None
+
+
+class Prep:
+    """src/lora.rs:286-293: what preparing an adapter needs; usable from a worker thread."""
+
+    def __init__(self, loras):
+        self._loras = loras
+
+    def prepare(self, name, modules, tiled_file=False):
+        """Prep::prepare (src/lora.rs:307-411) over in-memory factors."""
+        arr = (CModule * max(1, len(modules)))()
+        keep = []
+        for i, f in enumerate(modules):
+            arr[i].layer, arr[i].r = f.layer, f.r
+            arr[i].module = f.module.encode()
+            arr[i].a = f.a.ctypes.data_as(C.POINTER(C.c_float))
+            arr[i].b = f.b.ctypes.data_as(C.POINTER(C.c_float))
+            arr[i].a_len, arr[i].b_len = f.a.size, f.b.size
+            keep.append(f)
+        out = _P()
+        rc = lib.plora_adapter_prepare(self._loras._h, name.encode(), arr, len(modules), int(tiled_file),
+                                       C.byref(out))
+        if rc != OK:
+            raise PloraError(rc, lib.plora_adapter_error().decode())
+        return Adapter(out.value, name)
+
+
+class Loras:
+    """src/lora.rs:416-442: adapters by id, the GPU slots and their per-layer descriptor tables."""
+
+    def __init__(self, sites, max_slots, max_rank, max_tokens, max_seqs=None, base_gguf=False, heads=(0, 0),
+                 device=0):
+        self.sites = list(sites)
+        self.max_slots = max_slots
+        self.max_tokens = max_tokens
+        self.max_seqs = max_seqs if max_seqs is not None else max_tokens
+        self.device = device
+        csites = (CSite * len(self.sites))(*[s._c() for s in self.sites])
+        h = _P()
+        rc = lib.plora_create(csites, len(self.sites), int(base_gguf), heads[0], heads[1], max_slots, max_rank,
+                              max_tokens, self.max_seqs, device, C.byref(h))
+        if rc != OK:
+            raise PloraError(rc, lib.plora_last_error(None).decode())
+        self._h = h.value
+        self.max_rank = (max_rank + RANK_STEP - 1) // RANK_STEP * RANK_STEP
+        self.lds = MAX_PARTS * self.max_rank
+
+    def _check(self, rc):
+        if rc != OK:
+            raise PloraError(rc, lib.plora_last_error(self._h).decode())
+
+    def close(self):
+        if self._h:
+            lib.plora_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def bytes(self):  # src/lora.rs:526-528
+        return lib.plora_bytes(self._h)
+
+    @property
+    def slot_bytes(self):
+        return lib.plora_slot_bytes(self._h)
+
+    @property
+    def pool(self):
+        return lib.plora_pool_ptr(self._h)
+
+    @property
+    def s(self):
+        return lib.plora_s_ptr(self._h)
+
+    @property
+    def tiles(self):
+        return lib.plora_tiles_ptr(self._h)
+
+    def max_lora_tiles(self):  # src/model.rs:1346-1348
+        return lib.plora_max_lora_tiles(self._h)
+
+    def site_splits(self, site):
+        return lib.plora_site_splits(self._h, site)
+
+    def prep(self):  # src/lora.rs:551-559
+        return Prep(self)
+
+    def hook(self, site):  # src/lora.rs:530-538
+        hk = Hook()
+        self._check(lib.plora_hook_of(self._h, site, C.byref(hk)))
+        return hk
+
+    def id(self, name):  # src/lora.rs:540-542
+        v = C.c_uint32()
+        rc = lib.plora_id(self._h, name.encode(), C.byref(v))
+        return v.value if rc == OK else None
+
+    def names(self):  # src/lora.rs:544-548
+        buf = C.create_string_buffer(1 << 16)
+        n = lib.plora_names(self._h, buf, len(buf))
+        return buf.value.decode().split("\n") if n else []
+
+    def insert(self, adapter):  # src/lora.rs:562-574
+        v = C.c_uint32()
+        self._check(lib.plora_insert(self._h, adapter._ptr, C.byref(v)))
+        adapter._ptr = None  # the registry owns it now
+        return v.value
+
+    def retire(self, name):  # src/lora.rs:578-580
+        v = C.c_uint32()
+        rc = lib.plora_retire(self._h, name.encode(), C.byref(v))
+        return v.value if rc == OK else None
+
+    def free(self, id):  # src/lora.rs:583-585
+        self._check(lib.plora_free(self._h, id))
+
+    def upload(self, slot, id, stream=0):  # src/lora.rs:589-623
+        self._check(lib.plora_upload(self._h, slot, id, _P(stream)))
+
+    def desc(self, site, slot):
+        d = Desc()
+        self._check(lib.plora_desc_of(self._h, site, slot, C.byref(d)))
+        return d
+
+    def adapter_desc(self, adapter, site, base):
+        d = Desc()
+        self._check(lib.plora_adapter_desc(self._h, adapter._ptr, site, base, C.byref(d)))
+        return d
+
+    # ---- the step (src/model.rs:1603-1618, src/sched.rs:1096-1104) ----
+
+    def meta_build(self, cu_dev, seq_slot_dev, n_seqs, stream=0):
+        """Tile words from cu[n_seqs+1] / seq_slot[n_seqs] already on the device; no host round trip."""
+        self._check(lib.plora_meta_build(self._h, cu_dev, seq_slot_dev, n_seqs, _P(stream)))
+
+    def meta_upload(self, words, stream=0):
+        """The engine's own route: tile words written by the scheduler on the host."""
+        w = np.ascontiguousarray(words, dtype=np.int32)
+        self._check(lib.plora_meta_upload(self._h, w.ctypes.data_as(_I32P), _P(stream)))
+        return w
+
+    def lora_step(self, max_tiles, stream=0):
+        """Act::lora_step: groups the step's tiles by slot on the device and returns the StepLora."""
+        st = StepLora()
+        self._check(lib.plora_step_begin(self._h, max_tiles, _P(stream), C.byref(st)))
+        return st
+
+    def set_run_min(self, tokens):
+        self._check(lib.plora_set_run_min(self._h, tokens))
+
+    def device_status(self):
+        self._check(lib.plora_device_status(self._h))
+
+    # ---- Linear::forward's bracket ----
+
+    def shrink(self, hook, step, x, rows, stream=0):  # src/linear.rs:853-885
+        self._check(lib.plora_shrink(self._h, C.byref(hook), C.byref(step), x, rows, _P(stream)))
+
+    def expand(self, hook, step, rows, y, ldy, f32_out=False, stream=0):  # src/linear.rs:889-921
+        self._check(lib.plora_expand(self._h, C.byref(hook), C.byref(step), rows, y, ldy, int(f32_out), _P(stream)))
+
+    def fork(self, main=0, side=0):  # src/gpu.rs:849-858
+        self._check(lib.plora_fork(self._h, _P(main), _P(side)))
+
+    def join(self, main=0, side=0):  # src/gpu.rs:861-870
+        self._check(lib.plora_join(self._h, _P(main), _P(side)))
+
+
+class Linear:
+    """The adapter bracket of Linear::forward (src/linear.rs:428-443,844-849): shrink forked to the side
+    stream before the layer's own matrix multiply, expand after the join. ``base`` is whatever computes
+    y = x W^T on the main stream (it is an input to this path, not part of it)."""
+
+    def __init__(self, loras, site, base=None):
+        self.loras, self.site, self.base = loras, site, base
+        self.lora = loras.hook(site)  # Linear.lora, src/linear.rs:48-49
+        self.cols = loras.sites[site].cols
+
+    def forward(self, x, rows, y, ldy, f32_out=False, lora=None, main=0, side=None):
+        L = self.loras
+        if lora is not None:
+            if side is not None and side != main:
+                L.fork(main, side)
+                L.shrink(self.lora, lora, x, rows, side)
+            else:
+                L.shrink(self.lora, lora, x, rows, main)
+        if self.base is not None:
+            self.base(x, rows, y, ldy, f32_out)
+        if lora is not None:
+            if side is not None and side != main:
+                L.join(main, side)
+            L.expand(self.lora, lora, rows, y, ldy, f32_out, main)
+
+
+# ----------------------------------------------------------------------------- scheduler side
+
+class LoraSlots:
+    """src/sched.rs:410-449"""
+
+    def __init__(self, slots):
+        self._s = lib.plora_slots_new(slots)
+        self.slots = slots
+
+    def __del__(self):
+        try:
+            if self._s:
+                lib.plora_slots_free(self._s)
+                self._s = None
+        except Exception:
+            pass
+
+    def holding(self, a):
+        v = lib.plora_slots_holding(self._s, a)
+        return v if v else None
+
+    def can_place(self, a):
+        return bool(lib.plora_slots_can_place(self._s, a))
+
+    def place(self, a):
+        v = lib.plora_slots_place(self._s, a)
+        if v < 0:
+            raise PloraError(ERR_NO_SLOT, f"no slot for adapter {a}")
+        return v
+
+    def release(self, slot):
+        lib.plora_slots_release(self._s, slot)
+
+    def forget(self, a):
+        lib.plora_slots_forget(self._s, a)
+
+    def take_loads(self):
+        cap = self.slots + 1
+        sl = (C.c_int32 * cap)()
+        ids = (C.c_uint32 * cap)()
+        out = []
+        while True:
+            n = lib.plora_slots_take_loads(self._s, sl, ids, cap)
+            out += [(sl[i], ids[i]) for i in range(n)]
+            if n < cap:
+                break
+        return out
+
+
+def plan_tiles(row_n, row_slot):
+    """src/sched.rs:1019-1025"""
+    n = np.ascontiguousarray(row_n, dtype=np.int32)
+    s = np.ascontiguousarray(row_slot, dtype=np.int32)
+    return lib.plora_plan_tiles(n.ctypes.data_as(_I32P), s.ctypes.data_as(_I32P), len(n))
+
+
+def fill_tiles(row_n, row_slot, cap_tiles):
+    """src/sched.rs:1096-1104,1189: the step's tile words [count, (start, len, slot) x count]."""
+    n = np.ascontiguousarray(row_n, dtype=np.int32)
+    s = np.ascontiguousarray(row_slot, dtype=np.int32)
+    words = np.zeros(1 + 3 * cap_tiles, np.int32)
+    c = lib.plora_fill_tiles(n.ctypes.data_as(_I32P), s.ctypes.data_as(_I32P), len(n), words.ctypes.data_as(_I32P),
+                             cap_tiles)
+    if c < 0:
+        raise PloraError(ERR_CAPACITY, "more tiles than the metadata holds")
+    return words[:1 + 3 * c]

@@ -1,0 +1,113 @@
+// Internal declarations shared by the host registry (plora_host.cpp) and the
+// kernel launchers (plora_kernels.cu). Not part of the public C ABI.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/plora.h"
+
+// ---- device metadata produced once per step by the grouping kernel ("segs") ----
+// All int32 words. Gather path: tokens of short runs regrouped by slot and cut into work items of at
+// most PLORA_WORK_TOKENS tokens of one slot. Tile path: runs of contiguous tokens of one slot that are
+// at least PLORA_RUN_MIN long, cut into tensor-core tiles of PLORA_MMA_TOKENS tokens.
+#define PLORA_WORK_TOKENS 16
+#define PLORA_MMA_TOKENS 128
+#define PLORA_RUN_MIN_DEFAULT 64
+
+#define SEG_N_ACT 0    // slots that have gather tokens
+#define SEG_N_WORK 1   // gather work items
+#define SEG_N_MMA 2    // tensor-core tiles
+#define SEG_N_GATHER 3 // tokens on the gather path
+#define SEG_N_TILES 4  // tile count the grouping consumed
+#define SEG_STATUS 5   // 0, or PLORA_ERR_* found while grouping
+#define SEG_HDR 8
+
+struct SegLayout {
+    int max_slots, max_tokens, cap_tiles;
+    int run_min;  // runs at least this long take the tensor-core tile path
+    // word offsets
+    __host__ __device__ int act() const { return SEG_HDR; }                            // [max_slots] slot ids, ascending
+    __host__ __device__ int seg_off() const { return act() + max_slots; }              // [max_slots + 1] by active index
+    __host__ __device__ int perm() const { return seg_off() + max_slots + 1; }         // [max_tokens] token rows by slot
+    __host__ __device__ int work() const { return perm() + max_tokens; }               // [cap_tiles][3] slot, perm start, count
+    __host__ __device__ int mma() const { return work() + 3 * cap_tiles; }             // [cap_tiles][3] start, len, slot
+    __host__ __device__ int words() const { return mma() + 3 * cap_tiles; }
+};
+
+struct SiteInfo {
+    int layer = 0, cols = 0;
+    int col_heads_start = -1, col_heads_block = 0;
+    struct Part {
+        std::string module;
+        int rows = 0, off = 0, heads_start = -1, heads_block = 0;
+    };
+    std::vector<Part> parts;
+    int max_rows() const {
+        int m = 0;
+        for (auto& p : parts) m = p.rows > m ? p.rows : m;
+        return m;
+    }
+    // K-split of the shrink: fixed per site so results do not depend on the batch
+    int kchunk = 0, nsplit = 1;
+};
+
+struct SiteData {  // src/lora.rs:74-79
+    size_t a = 0;
+    int rank = 0;
+    size_t b_off[PLORA_MAX_PARTS] = {0, 0, 0, 0};
+    int r_off[PLORA_MAX_PARTS] = {0, 0, 0, 0};
+    int r[PLORA_MAX_PARTS] = {0, 0, 0, 0};
+};
+
+struct plora_adapter {  // src/lora.rs:82-88
+    std::string name;
+    int rank = 0;
+    uint8_t* data = nullptr;  // pinned when a device is present, else plain host memory
+    bool pinned = false;
+    size_t len = 0;
+    std::vector<SiteData> sites;
+};
+
+struct plora {
+    std::vector<SiteInfo> sites;
+    bool base_gguf = false;
+    int hk = 0, hv = 0;
+    int max_slots = 0, max_rank = 0, max_tokens = 0, max_seqs = 0, device = 0;
+    size_t slot_bytes = 0;
+    uint8_t* pool = nullptr;
+    plora_desc* tables = nullptr;       // device
+    plora_desc* host_tables = nullptr;  // pinned mirror
+    size_t table_bytes = 0;
+    std::unordered_map<uint32_t, plora_adapter*> adapters;
+    std::map<std::string, uint32_t> names;
+    uint32_t next_id = 1;
+    float* s = nullptr;
+    size_t s_bytes = 0, s_stride = 0;
+    int lds = 0, nsplit_max = 1;
+    int32_t* meta = nullptr;  // device: tile words, then segs
+    int32_t* host_meta = nullptr;  // pinned staging for plora_meta_upload
+    int cap_tiles = 0;
+    SegLayout seg;
+    int* status = nullptr;  // device status word
+    cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
+    mutable std::string err;
+    int sm_count = 148;
+};
+
+size_t plora_meta_group_smem(const SegLayout& lay);
+
+// ---- kernel launchers (plora_kernels.cu); each returns a cudaError_t from the launch ----
+cudaError_t plora_launch_meta_tiles(const int32_t* cu, const int32_t* seq_slot, int n_seqs, int32_t* tiles,
+                                    int cap_tiles, int* status, cudaStream_t st);
+cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status,
+                                    cudaStream_t st);
+cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay,
+                                const plora_desc* table, float* S, size_t s_stride_elems, int lds, int kchunk,
+                                int nsplit, int work_cap, int max_rank_total, int* status, cudaStream_t st);
+cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, int nsplit, const int32_t* segs,
+                                SegLayout lay, const plora_desc* table, void* y, int ldy, int f32_out, int parts,
+                                int max_rows, int work_cap, int* status, cudaStream_t st);

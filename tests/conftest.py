@@ -1,0 +1,26 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import __graft_entry__ as entry  # noqa: E402
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu)")
+
+
+@pytest.fixture(scope="session")
+def pe():
+    entry.build()
+    return entry.load_package()
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    entry.build()
+    return entry.load_oracle()

@@ -1,0 +1,222 @@
+"""Shared test helpers: build the same registry in the product library and in the CPU oracle from one
+synthetic workload, run the adapter path through the C ABI on the GPU, and compare.
+
+Tolerances (stated by the benchmark definition): against the fp64 oracle, max |d| <= 1e-2 * RMS(y) and
+mean |d| <= 1e-3 * RMS(y), measured in f32-out mode. In bf16-out mode the output is compared with the
+oracle rounded to bf16 at the same point: at most one bf16 ulp apart, and all but a small fraction equal.
+"""
+import numpy as np
+
+import __graft_entry__ as entry
+
+MAX_TOL = 1e-2
+MEAN_TOL = 1e-3
+
+
+def oracle_registry(wl, max_slots=None):
+    orc = entry.load_oracle()
+    max_slots = max_slots or wl.n_adapters
+    table = orc.OracleTable(wl.sites, max_slots)
+    adapters = []
+    for i in range(wl.n_adapters):
+        a = orc.OracleAdapter(wl.sites, wl.factors(i), wl.max_rank)
+        table.upload(i + 1, a)
+        adapters.append(a)
+    return table, adapters
+
+
+def product_registry(pe, wl, device=0, max_slots=None, max_tokens=None, max_seqs=None):
+    max_slots = max_slots or wl.n_adapters
+    loras = pe.Loras(wl.sites, max_slots, wl.max_rank, max_tokens or wl.tokens, max_seqs or wl.n_seqs, device=device)
+    prep = loras.prep()
+    for i in range(wl.n_adapters):
+        ad = prep.prepare(f"adapter-{i}", wl.factors(i))
+        aid = loras.insert(ad)
+        assert aid == i + 1
+        if device >= 0:
+            loras.upload(i + 1, aid)
+    return loras
+
+
+def tiles_of(pe, wl, cap=None):
+    cap = cap or (wl.tokens // 16 + wl.n_seqs)
+    return pe.fill_tiles(wl.row_n, wl.row_slot, cap)
+
+
+def to_dev_bf16(bits, device):
+    import torch
+    return torch.from_numpy(bits.view(np.int16).copy()).to(f"cuda:{device}").view(torch.bfloat16)
+
+
+def run_gpu(pe, loras, wl, f32_out, meta="host", device=0, y_base=None, xs=None):
+    """All sites of the workload once; returns [y numpy per site] (f32 values; bf16 outputs widened)."""
+    import torch
+    torch.cuda.set_device(device)
+    dev = f"cuda:{device}"
+    stream = torch.cuda.current_stream().cuda_stream
+    if meta == "host":
+        loras.meta_upload(tiles_of(pe, wl, loras.max_lora_tiles()), stream)
+    else:
+        cu = torch.from_numpy(wl.cu()).to(dev)
+        ss = torch.from_numpy(wl.row_slot.copy()).to(dev)
+        loras.meta_build(cu.data_ptr(), ss.data_ptr(), wl.n_seqs, stream)
+    step = loras.lora_step(loras.max_lora_tiles(), stream)
+    outs = []
+    for si in range(len(wl.sites)):
+        xb = xs[si] if xs is not None else wl.x_bits(si)
+        x = to_dev_bf16(xb, device)
+        yb = y_base[si] if y_base is not None else wl.y_base(si)
+        if f32_out:
+            y = torch.from_numpy(yb.copy()).to(dev)
+        else:
+            y = to_dev_bf16(pe.bf16_bits(yb), device)
+        lin = pe.Linear(loras, si)
+        lin.forward(x.data_ptr(), wl.tokens, y.data_ptr(), y.shape[1], f32_out, lora=step, main=stream)
+        outs.append(y.float().cpu().numpy())
+    torch.cuda.synchronize()
+    loras.device_status()
+    return outs
+
+
+def oracle_f64(wl, table, tiles, y_base=None, xs=None, f32_out=True, pe=None):
+    orc = entry.load_oracle()
+    outs = []
+    for si, site in enumerate(wl.sites):
+        xb = xs[si] if xs is not None else wl.x_bits(si)
+        yb = y_base[si] if y_base is not None else wl.y_base(si)
+        if not f32_out:
+            yb = pe.bf16_to_f32(pe.bf16_bits(yb)).reshape(yb.shape)
+        y64 = yb.astype(np.float64)
+        orc.site_f64(xb, site.cols, tiles, table.tables[si], y64)
+        outs.append(y64)
+    return outs
+
+
+def oracle_rounded(wl, table, tiles, f32_out, pe, mode="f32s", y_base=None, xs=None):
+    """The oracle with the kernels' rounding points (mode f32s) or the reference kernels' (mode emul)."""
+    orc = entry.load_oracle()
+    fn = orc.site_f32s if mode == "f32s" else orc.site_emul
+    outs = []
+    for si, site in enumerate(wl.sites):
+        xb = xs[si] if xs is not None else wl.x_bits(si)
+        yb = y_base[si] if y_base is not None else wl.y_base(si)
+        if f32_out:
+            y = yb.astype(np.float32).copy()
+            fn(xb, site.cols, tiles, table.tables[si], y, True)
+            outs.append(y)
+        else:
+            y = pe.bf16_bits(yb).reshape(yb.shape).copy()
+            fn(xb, site.cols, tiles, table.tables[si], y, False)
+            outs.append(pe.bf16_to_f32(y).reshape(yb.shape))
+    return outs
+
+
+def tolerance(y, y64):
+    """(max |d| / RMS, mean |d| / RMS) over the whole output."""
+    d = np.abs(y.astype(np.float64) - y64)
+    rms = float(np.sqrt(np.mean(y64 ** 2)))
+    return float(d.max()) / rms, float(d.mean()) / rms
+
+
+def bf16_ulp_diff(a, b, pe):
+    """Distance in bf16 steps between two arrays of bf16-representable f32 values."""
+    def key(v):
+        u = pe.bf16_bits(v).astype(np.int32)
+        return np.where(u & 0x8000, -(u & 0x7FFF), u & 0x7FFF)
+    return np.abs(key(a) - key(b))
+
+
+def run_and_check(pe, wl, device=0, f32_out=True, meta="host"):
+    table, _ = oracle_registry(wl)
+    loras = product_registry(pe, wl, device)
+    tiles = tiles_of(pe, wl)
+    ys = run_gpu(pe, loras, wl, f32_out, meta=meta, device=device)
+    res = {}
+    if f32_out:
+        y64 = oracle_f64(wl, table, tiles)
+        for si, (y, r) in enumerate(zip(ys, y64)):
+            mx, mn = tolerance(y, r)
+            assert mx <= MAX_TOL and mn <= MEAN_TOL, (wl.name, si, mx, mn)
+            res[si] = (mx, mn)
+    else:
+        yr = oracle_rounded(wl, table, tiles, False, pe)
+        for si, (y, r) in enumerate(zip(ys, yr)):
+            ulp = bf16_ulp_diff(y, r, pe)
+            frac = float((ulp > 0).mean())
+            assert ulp.max() <= 1 and frac < 2e-3, (wl.name, si, int(ulp.max()), frac)
+            res[si] = (int(ulp.max()), frac)
+    loras.close()
+    return res
+
+
+# ---------------------------------------------------------------- device inspection
+
+def dev_read(ptr, nbytes):
+    """Copies nbytes from a raw device address to a numpy uint8 array (synchronous)."""
+    import torch
+    from cuda.bindings import runtime as rt
+    torch.cuda.synchronize()
+    out = np.zeros(nbytes, np.uint8)
+    err, = rt.cudaMemcpy(out.ctypes.data, ptr, nbytes, rt.cudaMemcpyKind.cudaMemcpyDeviceToHost)
+    assert int(err) == 0, err
+    return out
+
+
+class SegView:
+    """The grouping kernel's output, decoded (word offsets as in csrc/plora_internal.h SegLayout)."""
+
+    def __init__(self, loras, step):
+        ms, mt, cap = loras.max_slots, loras.max_tokens, loras.max_lora_tiles()
+        act, seg_off = 8, 8 + ms
+        perm = seg_off + ms + 1
+        work = perm + mt
+        mma = work + 3 * cap
+        words = dev_read(step.segs, (mma + 3 * cap) * 4).view(np.int32)
+        self.n_act, self.n_work, self.n_mma, self.n_gather, self.n_tiles, self.status = words[:6]
+        self.act = words[act:act + self.n_act]
+        self.seg_off = words[seg_off:seg_off + self.n_act + 1]
+        self.perm = words[perm:perm + self.n_gather]
+        self.work = words[work:work + 3 * self.n_work].reshape(-1, 3)
+        self.mma = words[mma:mma + 3 * self.n_mma].reshape(-1, 3)
+
+
+def read_tiles(loras):
+    cap = loras.max_lora_tiles()
+    w = dev_read(loras.tiles, (1 + 3 * cap) * 4).view(np.int32)
+    return w[:1 + 3 * int(w[0])]
+
+
+def run_reference_kernels(pe, loras, wl, f32_out, device=0, y_base=None, xs=None):
+    """pocket-engine's own lora_shrink / lora_expand (oracle/_ref) over the product's descriptor tables and
+    tile words, with the engine's grids and its two-buffer S choreography (src/kernels/lora.cuh:69-73)."""
+    import importlib.util
+    import os
+    import torch
+    spec = importlib.util.spec_from_file_location("plora_ref_kernels", os.path.join(entry.ROOT, "oracle", "ref_kernels.py"))
+    rk = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rk)
+    if not rk.available():
+        return None
+    torch.cuda.set_device(device)
+    dev = f"cuda:{device}"
+    ref = rk.RefKernels()
+    stream = torch.cuda.current_stream().cuda_stream
+    loras.meta_upload(tiles_of(pe, wl, loras.max_lora_tiles()), stream)
+    lds = loras.lds
+    s = torch.zeros(2, wl.tokens, lds, dtype=torch.float32, device=dev)
+    max_tiles = loras.max_lora_tiles()
+    outs = []
+    for si, site in enumerate(wl.sites):
+        xb = xs[si] if xs is not None else wl.x_bits(si)
+        x = to_dev_bf16(xb, device)
+        yb = y_base[si] if y_base is not None else wl.y_base(si)
+        y = torch.from_numpy(yb.copy()).to(dev) if f32_out else to_dev_bf16(pe.bf16_bits(yb), device)
+        hook = loras.hook(si)
+        cur, nxt = s[si % 2], s[1 - si % 2]
+        ref.launch_shrink(x.data_ptr(), site.cols, site.cols, loras.tiles, hook.table, cur.data_ptr(), lds, max_tiles,
+                          wl.tokens, hook.parts, stream)
+        ref.launch_expand(cur.data_ptr(), lds, nxt.data_ptr(), loras.tiles, hook.table, y.data_ptr(), y.shape[1],
+                          f32_out, max_tiles, wl.tokens, hook.max_rows, hook.parts, stream)
+        outs.append(y.float().cpu().numpy())
+    torch.cuda.synchronize()
+    return outs

@@ -1,0 +1,237 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle, the reference's own
+kernels, and the properties the reference tests through whole-model logits (tests/gpu.rs:1055-1132)."""
+import numpy as np
+import pytest
+
+import harness
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def wls():
+    from pocket_engine_b200 import workloads
+    return workloads
+
+
+@pytest.mark.parametrize("meta", ["host", "device"])
+@pytest.mark.parametrize("f32_out", [True, False])
+def test_plumbing_config_matches_the_oracle(pe, wls, meta, f32_out):
+    harness.run_and_check(pe, wls.config1(), f32_out=f32_out, meta=meta)
+
+
+@pytest.mark.parametrize("f32_out", [True, False])
+def test_decode_block_matches_the_oracle(pe, wls, f32_out):
+    res = harness.run_and_check(pe, wls.config2(), f32_out=f32_out, meta="device")
+    assert len(res) == 4
+
+
+def test_device_tiles_are_bit_exact_with_the_host_rule(pe, oracle):
+    import torch
+    rng = np.random.default_rng(21)
+    sites = [pe.Site.fused(0, 64, [("q", 32)])]
+    loras = pe.Loras(sites, 7, 16, 4096, 2100, device=0)
+    cases = [([], []), ([1], [0]), ([1], [3]), ([15, 16, 17, 33], [1, 2, 0, 3]), ([2048] * 2, [5, 6])]
+    for trial in range(30):
+        n = int(rng.integers(1, 2100 if trial % 10 == 0 else 80))
+        rows = rng.choice([1, 1, 1, 2, 15, 16, 17, 33], n).astype(np.int32)
+        if rows.sum() > 4096:
+            rows = np.ones(n, np.int32)
+        cases.append((rows, rng.choice([0, 0, 1, 2, 3, 7], n).astype(np.int32)))
+    for rows, slots in cases:
+        rows, slots = np.asarray(rows, np.int32), np.asarray(slots, np.int32)
+        cu = torch.from_numpy(np.concatenate([[0], np.cumsum(rows)]).astype(np.int32)).cuda()
+        ss = torch.from_numpy(np.concatenate([slots, [0]]).astype(np.int32)).cuda()
+        loras.meta_build(cu.data_ptr(), ss.data_ptr(), len(rows))
+        got = harness.read_tiles(loras)
+        want = oracle.fill_tiles(rows, slots, loras.max_lora_tiles())
+        assert np.array_equal(got, want), (rows[:10], slots[:10])
+        assert np.array_equal(got, pe.fill_tiles(rows, slots, loras.max_lora_tiles()))
+    loras.device_status()
+    loras.close()
+
+
+def test_grouping_is_a_stable_sort_by_slot(pe):
+    rng = np.random.default_rng(22)
+    sites = [pe.Site.fused(0, 64, [("q", 32)])]
+    loras = pe.Loras(sites, 9, 16, 4096, 1500, device=0)
+    for trial in range(25):
+        n = int(rng.integers(1, 1400 if trial % 8 == 0 else 70))
+        rows = rng.choice([1, 1, 1, 3, 16, 17, 40], n).astype(np.int32)
+        if rows.sum() > 4096:
+            rows = np.ones(n, np.int32)
+        slots = rng.choice([0, 1, 2, 5, 9], n).astype(np.int32)
+        loras.meta_upload(pe.fill_tiles(rows, slots, loras.max_lora_tiles()))
+        step = loras.lora_step(loras.max_lora_tiles())
+        seg = harness.SegView(loras, step)
+        tslot = np.repeat(slots, rows)
+        tok = np.nonzero(tslot)[0]
+        order = tok[np.argsort(tslot[tok], kind="stable")]
+        assert seg.status == 0 and seg.n_mma == 0
+        assert np.array_equal(seg.perm, order)
+        present = np.unique(tslot[tok])
+        assert np.array_equal(seg.act, present)
+        counts = np.array([(tslot == s).sum() for s in present])
+        assert np.array_equal(seg.seg_off, np.concatenate([[0], np.cumsum(counts)]))
+        # work items: each slot's segment cut into pieces of at most 16 tokens, in order
+        want = [(s, o + k, min(16, c - k)) for s, o, c in zip(present, seg.seg_off, counts) for k in range(0, c, 16)]
+        assert [tuple(w) for w in seg.work] == want
+    loras.device_status()
+    loras.close()
+
+
+def test_long_runs_become_tensor_core_tiles(pe):
+    sites = [pe.Site.fused(0, 64, [("q", 32)])]
+    loras = pe.Loras(sites, 4, 16, 1024, 16, device=0)
+    loras.set_run_min(64)
+    rows, slots = [1, 200, 3, 64, 130, 63], [1, 2, 2, 0, 3, 3]
+    # tokens: [0] s1, [1..201) s2, [201..204) s2 (contiguous with the previous: one run of 203), 64 base,
+    # [268..398) s3 then [398..461) s3: one run of 193
+    loras.meta_upload(pe.fill_tiles(rows, slots, loras.max_lora_tiles()))
+    seg = harness.SegView(loras, loras.lora_step(loras.max_lora_tiles()))
+    assert [tuple(m) for m in seg.mma] == [(1, 128, 2), (129, 75, 2), (268, 128, 3), (396, 65, 3)]
+    assert list(seg.perm) == [0] and list(seg.act) == [1]
+    loras.close()
+
+
+def test_zero_b_adapter_leaves_the_base_bit_identical(pe, wls):
+    # tests/gpu.rs:1055-1078, at the layer boundary
+    wl = wls.config1()
+    wl.scale = 0.0
+    loras = harness.product_registry(pe, wl)
+    for f32_out in (True, False):
+        y = harness.run_gpu(pe, loras, wl, f32_out)[0]
+        base = wl.y_base(0)
+        if not f32_out:
+            base = pe.bf16_to_f32(pe.bf16_bits(base)).reshape(base.shape)
+        assert np.array_equal(y, base)
+    loras.close()
+
+
+def test_mixed_batch_equals_each_adapter_alone_bitwise(pe, wls):
+    # tests/gpu.rs:1083-1132, at the layer boundary and exact: the kernels are deterministic and a token's
+    # arithmetic does not depend on what else is in the batch
+    wl = wls.config2(tokens=48, adapters=6)
+    loras = harness.product_registry(pe, wl, max_tokens=64, max_seqs=64)
+    xs = [wl.x_bits(si) for si in range(4)]
+    yb = [wl.y_base(si) for si in range(4)]
+    mixed = harness.run_gpu(pe, loras, wl, False, xs=xs, y_base=yb)
+    tslot = wl.token_slot()
+    for s in range(1, 7):
+        idx = np.nonzero(tslot == s)[0]
+        if len(idx) == 0:
+            continue
+        alone = wls.Workload("alone", wl.sites, wl.ranks, wl.scale, [1] * len(idx), [s] * len(idx), wl.seed)
+        ya = harness.run_gpu(pe, loras, alone, False, xs=[x[idx] for x in xs], y_base=[y[idx] for y in yb])
+        for si in range(4):
+            assert np.array_equal(ya[si], mixed[si][idx]), (s, si)
+    # base-only tokens are untouched
+    idx = np.nonzero(tslot == 0)[0]
+    for si in range(4):
+        want = pe.bf16_to_f32(pe.bf16_bits(yb[si][idx])).reshape(len(idx), -1)
+        assert np.array_equal(mixed[si][idx], want)
+    loras.close()
+
+
+RAGGED = [
+    ("ragged-rows", [1, 15, 16, 17, 33, 2], [1, 2, 0, 3, 1, 2], [16, 16, 16], 256, [("a", 64), ("b", 32)]),
+    ("all-base", [3, 4], [0, 0], [16], 128, [("a", 64)]),
+    ("one-slot", [40], [1], [24], 512, [("a", 96), ("b", 32), ("c", 32), ("d", 64)]),
+    ("odd-k", [5, 1, 1], [2, 1, 2], [8, 40], 1096, [("a", 130)]),
+    ("one-token", [1], [1], [1], 64, [("a", 2)]),
+]
+
+
+@pytest.mark.parametrize("case", RAGGED, ids=[c[0] for c in RAGGED])
+def test_ragged_and_edge_shapes(pe, wls, case):
+    name, rows, slots, ranks, K, mods = case
+    sites = [pe.Site.fused(0, K, mods), pe.Site.fused(0, K, [("z", 48)])]
+    wl = wls.Workload(name, sites, ranks, 1.5, rows, slots, 3)
+    for f32_out in (True, False):
+        for meta in ("host", "device"):
+            harness.run_and_check(pe, wl, f32_out=f32_out, meta=meta)
+
+
+def test_untargeted_parts_and_sites_are_skipped(pe, wls, oracle):
+    sites = [pe.Site.fused(0, 256, [("q", 64), ("k", 32), ("v", 32)]), pe.Site.fused(0, 256, [("o", 64)])]
+    wl = wls.Workload("partial", sites, [16, 8], 1.0, [3, 2, 4], [1, 2, 1], 5)
+    full = wl.factors
+    wl.factors = lambda i: [f for f in full(i) if (f.module in ("q", "v") if i == 0 else f.module == "o")]
+    res = harness.run_and_check(pe, wl, f32_out=True)
+    assert set(res) == {0, 1}
+    res = harness.run_and_check(pe, wl, f32_out=False)
+
+
+def test_reference_kernels_agree(pe, wls, oracle):
+    """pocket-engine's own lora_shrink / lora_expand on the same descriptor tables and tile words: they
+    must sit within the stated tolerance of the fp64 oracle, within rounding of the oracle's emulation
+    of their rounding points, and within tolerance of the new kernels."""
+    for wl in (wls.config1(), wls.config2()):
+        loras = harness.product_registry(pe, wl)
+        table, _ = harness.oracle_registry(wl)
+        tiles = harness.tiles_of(pe, wl)
+        ref = harness.run_reference_kernels(pe, loras, wl, True)
+        if ref is None:
+            pytest.skip("oracle/_ref fatbin is not built")
+        ours = harness.run_gpu(pe, loras, wl, True)
+        y64 = harness.oracle_f64(wl, table, tiles)
+        emul = harness.oracle_rounded(wl, table, tiles, True, pe, mode="emul")
+        for si in range(len(wl.sites)):
+            mx, mn = harness.tolerance(ref[si], y64[si])
+            assert mx <= harness.MAX_TOL and mn <= harness.MEAN_TOL, ("ref vs f64", wl.name, si, mx, mn)
+            mx, mn = harness.tolerance(ref[si], emul[si].astype(np.float64))
+            assert mx <= 1e-3 and mn <= 5e-5, ("ref vs emul", wl.name, si, mx, mn)
+            mx, mn = harness.tolerance(ours[si], ref[si].astype(np.float64))
+            assert mx <= harness.MAX_TOL and mn <= harness.MEAN_TOL, ("ours vs ref", wl.name, si, mx, mn)
+        # bf16 output: the reference against its emulation, at most one bf16 step apart
+        refb = harness.run_reference_kernels(pe, loras, wl, False)
+        emb = harness.oracle_rounded(wl, table, tiles, False, pe, mode="emul")
+        for si in range(len(wl.sites)):
+            ulp = harness.bf16_ulp_diff(refb[si], emb[si], pe)
+            assert ulp.max() <= 1 and (ulp > 0).mean() < 5e-3, (wl.name, si, int(ulp.max()), float((ulp > 0).mean()))
+        loras.close()
+
+
+def test_prefill_segments_reduced(pe, wls):
+    wl = wls.config3(seqs=3, seq_len=160, rank=64)
+    harness.run_and_check(pe, wl, f32_out=True, meta="device")
+    harness.run_and_check(pe, wl, f32_out=False, meta="device")
+
+
+def test_heterogeneous_ranks_reduced(pe, wls):
+    wl = wls.config4(tokens=96, adapters=20)
+    harness.run_and_check(pe, wl, f32_out=True, meta="device")
+    harness.run_and_check(pe, wl, f32_out=False, meta="host")
+
+
+def test_capacity_errors_are_reported_not_faulted(pe):
+    import torch
+    sites = [pe.Site.fused(0, 64, [("q", 32)])]
+    loras = pe.Loras(sites, 2, 16, 64, 4, device=0)
+    with pytest.raises(pe.PloraError) as e:  # more sequences than max_seqs
+        loras.meta_build(1 << 20, 1 << 20, 5)
+    assert e.value.code == pe.ERR_CAPACITY
+    x = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    step = loras.lora_step(8)
+    with pytest.raises(pe.PloraError) as e:  # more rows than max_tokens
+        loras.shrink(loras.hook(0), step, x.data_ptr(), 100)
+    assert e.value.code == pe.ERR_CAPACITY
+    with pytest.raises(pe.PloraError) as e:  # misaligned x
+        loras.shrink(loras.hook(0), step, x.data_ptr() + 2, 4)
+    assert e.value.code == pe.ERR_ARG
+    with pytest.raises(pe.PloraError) as e:  # upload of an unknown id (src/lora.rs:590-593)
+        loras.upload(1, 42)
+    assert e.value.code == pe.ERR_UNKNOWN_ID
+    # device side: more tiles than the region holds -> status word, count clamped to zero
+    cu = torch.tensor([0, 16, 32, 48, 64], dtype=torch.int32, device="cuda")
+    # cap = 64/16 + 4 = 8 tiles; 4 sequences of 16 -> 4 tiles: fits
+    ss = torch.tensor([1, 1, 2, 2, 0], dtype=torch.int32, device="cuda")
+    loras.meta_build(cu.data_ptr(), ss.data_ptr(), 4)
+    loras.device_status()
+    # a tile word list that names a slot out of range is flagged by the grouping kernel
+    loras.meta_upload(np.array([1, 0, 1, 9], np.int32))
+    loras.lora_step(8)
+    with pytest.raises(pe.PloraError) as e:
+        loras.device_status()
+    assert e.value.code == pe.ERR_ARG
+    loras.close()
