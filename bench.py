@@ -1,0 +1,484 @@
+"""Benchmark of the batched multi-adapter LoRA path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode|prefill] [--impl ours|reference]
+
+A step is one pass of the adapter path (shrink + expand at each of the block's four sites) over one
+batch of synthetic input. The default workload is the decode mixed batch: hidden 4096 / intermediate
+12288 block, 64 one-token sequences, 16 rank-16 adapters on all seven projections, 25% base-only tokens.
+Under torchrun (N > 1) every rank runs that batch on its own GPU over its own disjoint adapter set
+(adapter-affine partitioning, no collective on the data path): weak scaling.
+
+L2: the step rotates over enough copies of the slot pool, inputs and outputs (>= 512 MB in total) that
+every step reads its slabs from HBM, not from the 126 MB L2.
+
+Prints ONE JSON line (rank 0).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+METRIC = "mixed-adapter LoRA tokens/s (one transformer block's adapter path)"
+UNIT = "tokens/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], "measured", d
+    return 6650.0, "fallback", {}
+
+
+def make_workload(name, seed):
+    from pocket_engine_b200 import workloads
+    if name == "decode":
+        return workloads.config2(seed=seed)
+    if name == "prefill":
+        return workloads.config3(seed=seed)
+    if name == "plumbing":
+        return workloads.config1(seed=seed)
+    raise SystemExit(f"unknown workload {name}")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
+                                       "100", "-i", str(index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.f.read().splitlines():
+            c = [v.strip() for v in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1]))
+                mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, c[5:9]):
+                if v == "Active":
+                    reasons.add(n)
+        os.unlink(self.f.name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------- ours
+
+def kernel_bytes(wl, si, which, f32_out=False):
+    """Algorithmic bytes of one launch of the shrink or the expand of site si (true ranks)."""
+    site = wl.sites[si]
+    tslot = wl.token_slot()
+    present = np.unique(tslot[tslot > 0])
+    n_tot = sum(p.rows for p in site.parts)
+    np_ = len(site.parts)
+    ye = 8 if f32_out else 4
+    b = 0
+    for s in present:
+        ta = int((tslot == s).sum())
+        r = wl.ranks[s - 1]
+        if which == "shrink":
+            b += 2 * np_ * r * site.cols + ta * np_ * r * 4
+        else:
+            b += 2 * n_tot * r + ta * np_ * r * 4 + ta * n_tot * ye
+    if which == "shrink":
+        b += 2 * int((tslot > 0).sum()) * site.cols
+    return b
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    pe = entry.load_package()
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    wl = make_workload(args.workload, seed=1000 * rank)
+    work = wl.work()
+    ns = len(wl.sites)
+    # enough rotating copies that the slabs of consecutive steps never sit in L2
+    probe = pe.Loras(wl.sites, wl.n_adapters, wl.max_rank, wl.tokens, wl.n_seqs, device=-1)
+    pool_bytes = probe.slot_bytes * wl.n_adapters
+    probe.close()
+    copies = int(min(32, max(2, -(-512 * 2 ** 20 // pool_bytes))))
+    if args.copies:
+        copies = args.copies
+    main = torch.cuda.Stream(device=dev)
+    side = torch.cuda.Stream(device=dev)
+    facs = [wl.factors(i) for i in range(wl.n_adapters)]
+    sets = []
+    xs_host = [torch.from_numpy(wl.x_bits(si).view(np.int16)).pin_memory() for si in range(ns)]
+    yb_host = [torch.from_numpy(pe.bf16_bits(wl.y_base(si)).reshape(wl.tokens, -1).view(np.int16)).pin_memory()
+               for si in range(ns)]
+    cu_host = torch.from_numpy(wl.cu()).pin_memory()
+    ss_host = torch.from_numpy(wl.row_slot.copy()).pin_memory()
+    for c in range(copies):
+        L = pe.Loras(wl.sites, wl.n_adapters, wl.max_rank, wl.tokens, wl.n_seqs, device=local_rank)
+        prep = L.prep()
+        for i in range(wl.n_adapters):
+            L.upload(i + 1, L.insert(prep.prepare(f"a{i}", facs[i])), main.cuda_stream)
+        x = [h.to(dev, non_blocking=True).view(torch.bfloat16) for h in xs_host]
+        y = [h.to(dev, non_blocking=True).view(torch.bfloat16) for h in yb_host]
+        cu = cu_host.to(dev)
+        ss = ss_host.to(dev)
+        L.meta_build(cu.data_ptr(), ss.data_ptr(), wl.n_seqs, main.cuda_stream)
+        step = L.lora_step(L.max_lora_tiles(), main.cuda_stream)
+        lins = [pe.Linear(L, si) for si in range(ns)]
+        sets.append({"L": L, "x": x, "y": y, "cu": cu, "ss": ss, "step": step, "lins": lins})
+    torch.cuda.synchronize()
+
+    def block(S, m, s):
+        for si in range(ns):
+            S["lins"][si].forward(S["x"][si].data_ptr(), wl.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1], False,
+                                  lora=S["step"], main=m, side=s)
+
+    # one CUDA graph per copy: the block's 8 launches with the engine's fork/join choreography
+    graphs = []
+    with torch.cuda.stream(main):
+        for S in sets:
+            block(S, main.cuda_stream, side.cuda_stream)  # warm every kernel before capture
+        torch.cuda.synchronize()
+        for S in sets:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=main):
+                block(S, main.cuda_stream, side.cuda_stream)
+            graphs.append(g)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: K graph replays
+    with torch.cuda.stream(main):
+        for i in range(args.warmup):
+            graphs[i % copies].replay()
+        barrier()
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(main)
+        for i in range(args.steps):
+            graphs[(args.warmup + i) % copies].replay()
+        e1.record(main)
+        barrier()
+        ms = e0.elapsed_time(e1)
+    # keep the sampler alive a little longer for short runs so it sees load
+    if sampler is not None and ms < 400:
+        with torch.cuda.stream(main):
+            t_end = time.time() + 0.5
+            while time.time() < t_end:
+                for i in range(copies):
+                    graphs[i].replay()
+                torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler is not None else None
+
+    # ---- end to end through the C ABI with host buffers: H2D of x, y_base and the step's sequence table,
+    # device metadata build + grouping, the block, D2H of y
+    y_out = [torch.empty_like(h) for h in yb_host]
+    y_out = [t.pin_memory() for t in y_out]
+    h2d = sum(h.numel() * 2 for h in xs_host) + sum(h.numel() * 2 for h in yb_host) + cu_host.numel() * 4 + \
+        ss_host.numel() * 4
+    d2h = sum(h.numel() * 2 for h in y_out)
+
+    def e2e_step(S):
+        m = main.cuda_stream
+        with torch.cuda.stream(main):
+            for si in range(ns):
+                S["x"][si].view(torch.int16).copy_(xs_host[si], non_blocking=True)
+                S["y"][si].view(torch.int16).copy_(yb_host[si], non_blocking=True)
+            S["cu"].copy_(cu_host, non_blocking=True)
+            S["ss"].copy_(ss_host, non_blocking=True)
+            S["L"].meta_build(S["cu"].data_ptr(), S["ss"].data_ptr(), wl.n_seqs, m)
+            st = S["L"].lora_step(S["L"].max_lora_tiles(), m)
+            for si in range(ns):
+                S["lins"][si].forward(S["x"][si].data_ptr(), wl.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1],
+                                      False, lora=st, main=m, side=side.cuda_stream)
+            for si in range(ns):
+                y_out[si].copy_(S["y"][si].view(torch.int16), non_blocking=True)
+        main.synchronize()
+
+    for i in range(args.warmup):
+        e2e_step(sets[i % copies])
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(sets[(args.warmup + i) % copies])
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    # ---- per-kernel durations (CUDA events on the launching stream, rotating copies)
+    kern = {}
+    reps = max(copies, min(args.steps, 4 * copies))
+    with torch.cuda.stream(main):
+        m = main.cuda_stream
+        for si in range(ns):
+            for which in ("shrink", "expand"):
+                evs = []
+                for i in range(reps + 3):
+                    S = sets[i % copies]
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    hook = S["lins"][si].lora
+                    a.record(main)
+                    if which == "shrink":
+                        S["L"].shrink(hook, S["step"], S["x"][si].data_ptr(), wl.tokens, m)
+                    else:
+                        S["L"].expand(hook, S["step"], wl.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1], False, m)
+                    b.record(main)
+                    evs.append((a, b))
+                torch.cuda.synchronize()
+                ts = [a.elapsed_time(b) for a, b in evs[3:]]
+                kern[f"{which}[{si}]"] = {"us": 1e3 * float(np.mean(ts)), "bytes": kernel_bytes(wl, si, which)}
+        # the step's metadata kernels, for the record
+        evs = []
+        for i in range(reps):
+            S = sets[i % copies]
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(main)
+            S["L"].meta_build(S["cu"].data_ptr(), S["ss"].data_ptr(), wl.n_seqs, m)
+            S["L"].lora_step(S["L"].max_lora_tiles(), m)
+            b.record(main)
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        meta_us = 1e3 * float(np.mean([a.elapsed_time(b) for a, b in evs]))
+    for S in sets:
+        S["L"].device_status()
+
+    # max over ranks
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    if rank != 0:
+        return None
+    peak, peak_kind, _ = peaks()
+    dom = max(kern, key=lambda k: kern[k]["us"])
+    ach = kern[dom]["bytes"] / (kern[dom]["us"] * 1e-6) / 1e9
+    step_us = 1e3 * ms / args.steps
+    out = {
+        "metric": METRIC, "value": world * wl.tokens * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wl.name, "tokens_per_step": wl.tokens, "lora_tokens": work["lora_tokens"],
+                   "adapters": wl.n_adapters, "slots_present": work["slots_present"], "sites": ns,
+                   "l2": f"inputs larger than L2: {copies} rotating copies of pool+x+y = "
+                         f"{copies * (pool_bytes + d2h + h2d // 2) / 2 ** 20:.0f} MiB",
+                   "partitioning": "adapter-affine, one batch per GPU, no collective", "graph": "one CUDA graph per copy"},
+        "e2e": {"value": world * wl.tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": 8 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                     "peak_kind": peak_kind, "traffic": None, "us_per_launch": kern[dom]["us"],
+                     "algorithmic_bytes_per_launch": kern[dom]["bytes"]},
+        "step_roofline": {"algorithmic_bytes_per_step": work["bytes"], "achieved_gbs": work["bytes"] / (step_us * 1e-6) / 1e9,
+                          "frac": work["bytes"] / (step_us * 1e-6) / 1e9 / peak, "us_per_step": step_us},
+        "kernels": {k: {"us": round(v["us"], 3), "gbs": round(v["bytes"] / (v["us"] * 1e-6) / 1e9, 1)} for k, v in kern.items()},
+        "meta_us": meta_us,
+        "clocks": clocks,
+    }
+    return out
+
+
+# -------------------------------------------------------------------------------- CPU port
+
+def cpu_port(wl_name, seconds, seed=0, threads=0, steps=None, warmup=0):
+    """The oracle's multithreaded C restatement of the path, timed on the host cores. Returns
+    (tokens/s, cores, sample description, ms per step)."""
+    orc = entry.load_oracle()
+    pe = entry.load_package()  # only the synthetic inputs and the tile rule (host arithmetic)
+    wl = make_workload(wl_name, seed)
+    table = orc.OracleTable(wl.sites, wl.n_adapters)
+    for i in range(wl.n_adapters):
+        table.upload(i + 1, orc.OracleAdapter(wl.sites, wl.factors(i), wl.max_rank))
+    tiles = orc.fill_tiles(wl.row_n, wl.row_slot, wl.tokens // 16 + wl.n_seqs)
+    xs = [wl.x_bits(si) for si in range(len(wl.sites))]
+    ys = [pe.bf16_bits(wl.y_base(si)).reshape(wl.tokens, -1) for si in range(len(wl.sites))]
+    s = np.zeros((wl.tokens, 4 * ((wl.max_rank + 15) // 16 * 16)), np.float32)
+    threads = threads or orc.hw_threads()
+
+    def one():
+        for si, site in enumerate(wl.sites):
+            orc.site_mt(xs[si], site.cols, tiles, table.tables[si], s, ys[si], False, threads)
+
+    for _ in range(max(1, warmup)):
+        one()
+    n, t0 = 0, time.perf_counter()
+    while True:
+        one()
+        n += 1
+        el = time.perf_counter() - t0
+        if (steps is not None and n >= steps) or (steps is None and el >= seconds):
+            break
+    return wl.tokens * n / el, threads, f"{n} full steps of {wl.name} in {el:.1f} s", 1e3 * el / n, wl
+
+
+def run_reference(args, rank, world):
+    """The reference has no CPU implementation of this path (it is GPU-only), so the timed CPU arm is the
+    oracle's multithreaded port. When the reference's own kernels were compiled (oracle/_ref) and a GPU is
+    visible, they are also timed on the same workload and reported beside it."""
+    if rank != 0:
+        return None
+    v, cores, sample, ms, wl = cpu_port(args.workload, 0, steps=args.steps, warmup=args.warmup)
+    out = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "f32", "data": "synthetic", "config": {"workload": wl.name, "tokens_per_step": wl.tokens},
+           "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+           "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "note": "pocket-engine has no CPU path; this arm times the C port of its algorithm on the host cores"}
+    try:
+        out["reference_gpu_kernels"] = reference_gpu(args)
+    except Exception as e:  # no GPU, no fatbin, or a driver error: report, do not fail the arm
+        out["reference_gpu_kernels"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    return out
+
+
+def reference_gpu(args):
+    """pocket-engine's own lora_shrink / lora_expand (oracle/_ref fatbin) on the same workload and the same
+    rotation over pool copies, with the engine's grids and stream order; none of the product library runs."""
+    import importlib.util
+    import torch
+    spec = importlib.util.spec_from_file_location("plora_ref_kernels", os.path.join(ROOT, "oracle", "ref_kernels.py"))
+    rk = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rk)
+    if not rk.available():
+        return {"unavailable": "oracle/_ref fatbin not built"}
+    if not torch.cuda.is_available():
+        return {"unavailable": "no GPU"}
+    orc = entry.load_oracle()
+    pe = entry.load_package()  # synthetic inputs and bf16 helpers only
+    wl = make_workload(args.workload, 0)
+    torch.cuda.set_device(0)
+    ref = rk.RefKernels()
+    max_rank = (wl.max_rank + 15) // 16 * 16
+    lds = 4 * max_rank
+    adapters = [orc.OracleAdapter(wl.sites, wl.factors(i), wl.max_rank) for i in range(wl.n_adapters)]
+    slot_bytes = orc.lib().po_slot_bytes(orc.c_sites(wl.sites), len(wl.sites), max_rank)
+    copies = int(min(32, max(2, -(-512 * 2 ** 20 // (slot_bytes * wl.n_adapters)))))
+    tiles_h = orc.fill_tiles(wl.row_n, wl.row_slot, wl.tokens // 16 + wl.n_seqs)
+    max_tiles = wl.tokens // 16 + wl.n_seqs
+    sets = []
+    for c in range(copies):
+        pool = torch.empty(slot_bytes * wl.n_adapters, dtype=torch.uint8, device="cuda")
+        tabs = []
+        for si in range(len(wl.sites)):
+            t = (orc.PoDesc * (wl.n_adapters + 1))()
+            for i, a in enumerate(adapters):
+                t[i + 1] = a.desc(si, pool.data_ptr() + i * slot_bytes)
+            tabs.append(torch.frombuffer(bytearray(bytes(t)), dtype=torch.uint8).cuda())
+        for i, a in enumerate(adapters):
+            pool[i * slot_bytes:i * slot_bytes + a.len].copy_(torch.from_numpy(a.data[:a.len]))
+        x = [torch.from_numpy(wl.x_bits(si).view(np.int16)).cuda() for si in range(len(wl.sites))]
+        y = [torch.from_numpy(pe.bf16_bits(wl.y_base(si)).reshape(wl.tokens, -1).view(np.int16)).cuda()
+             for si in range(len(wl.sites))]
+        sets.append({"pool": pool, "tabs": tabs, "x": x, "y": y, "tiles": torch.from_numpy(tiles_h.copy()).cuda(),
+                     "s": torch.zeros(2, wl.tokens, lds, dtype=torch.float32, device="cuda")})
+    main, side = torch.cuda.Stream(), torch.cuda.Stream()
+    fork, join = torch.cuda.Event(), torch.cuda.Event()
+
+    def block(S):
+        for si, site in enumerate(wl.sites):
+            cur, nxt = S["s"][si % 2], S["s"][1 - si % 2]
+            parts, max_rows = len(site.parts), site.max_rows()
+            fork.record(main)
+            side.wait_event(fork)
+            ref.launch_shrink(S["x"][si].data_ptr(), site.cols, site.cols, S["tiles"].data_ptr(), S["tabs"][si].data_ptr(),
+                              cur.data_ptr(), lds, max_tiles, wl.tokens, parts, side.cuda_stream)
+            join.record(side)
+            main.wait_event(join)
+            ref.launch_expand(cur.data_ptr(), lds, nxt.data_ptr(), S["tiles"].data_ptr(), S["tabs"][si].data_ptr(),
+                              S["y"][si].data_ptr(), S["y"][si].shape[1], False, max_tiles, wl.tokens, max_rows, parts,
+                              main.cuda_stream)
+
+    graphs = []
+    with torch.cuda.stream(main):
+        for S in sets:
+            block(S)
+        torch.cuda.synchronize()
+        for S in sets:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=main):
+                block(S)
+            graphs.append(g)
+        torch.cuda.synchronize()
+        for i in range(max(3, args.warmup)):
+            graphs[i % copies].replay()
+        torch.cuda.synchronize()
+        steps = max(args.steps, 50)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(main)
+        for i in range(steps):
+            graphs[i % copies].replay()
+        e1.record(main)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+    work = wl.work()
+    peak, kind, _ = peaks()
+    return {"value": wl.tokens * steps / (ms * 1e-3), "unit": UNIT, "us_per_step": 1e3 * ms / steps, "steps": steps,
+            "achieved_gbs": work["bytes"] / (ms / steps * 1e-3) / 1e9, "frac_of_peak": work["bytes"] / (ms / steps * 1e-3) / 1e9 / peak,
+            "what": "pocket-engine's lora_shrink/lora_expand compiled for sm_100a, CUDA-graph replay, same rotation"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "plumbing"])
+    ap.add_argument("--copies", type=int, default=0, help="override the number of rotating pool copies")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        out = run_reference(args, rank, world)
+        if out is not None:
+            print(json.dumps(out))
+        return
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU fallback")
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    out = run_ours(args, rank, world, local_rank)
+    if rank == 0:
+        v, cores, sample, _, _ = cpu_port(args.workload, args.cpu_seconds)
+        out["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(out))
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -118,12 +118,16 @@ def tolerance(y, y64):
     return float(d.max()) / rms, float(d.mean()) / rms
 
 
-def bf16_ulp_diff(a, b, pe):
-    """Distance in bf16 steps between two arrays of bf16-representable f32 values."""
+def bf16_ulp_diff(a, b, pe, floor=2.0 ** -20):
+    """Distance in bf16 steps between two arrays of bf16-representable f32 values. Values whose absolute
+    difference is under `floor` count as equal: next to zero a bf16 step is far smaller than the f32
+    rounding of the sums that feed it."""
     def key(v):
         u = pe.bf16_bits(v).astype(np.int32)
         return np.where(u & 0x8000, -(u & 0x7FFF), u & 0x7FFF)
-    return np.abs(key(a) - key(b))
+    d = np.abs(key(a) - key(b))
+    d[np.abs(a.astype(np.float64) - b.astype(np.float64)) <= floor] = 0
+    return d
 
 
 def run_and_check(pe, wl, device=0, f32_out=True, meta="host"):
