@@ -209,6 +209,21 @@ int plora_join(plora_t* h, void* main_stream, void* side_stream);
  * tensor-core tile kernels (no counterpart in the engine, whose tiles are always 16 tokens). */
 int plora_set_run_min(plora_t* h, int tokens);
 
+/* No counterpart in pocket-engine. One layer's adapter application (shrink, then expand, straight from the
+ * engine's tile words and descriptor table) for callers that cannot allocate device memory: an engine whose
+ * memory is fully claimed at start-up, code already inside a stream capture, a plugin host that forbids
+ * allocation after initialisation. The f32 intermediate lives in a fixed 8 MiB device array inside the
+ * library (held by every GPU that loads it, until exit), so this call allocates nothing. Calls with
+ * nsplit * rows * lds * 4 bytes over plora_static_scratch_bytes() are rejected with PLORA_ERR_CAPACITY.
+ * All calls on a device share that array: order them on the GPU, overlapping calls race. The first call on
+ * a device resolves the array's address; make it outside any stream capture.
+ * x [rows, cols] bf16; tiles = [count,(start,len,slot) x count] i32; table = the layer's Desc table;
+ * y [rows, ldy] bf16 or f32, updated in place. Error text: plora_static_error(). */
+int plora_site_apply_static(uint64_t x, int rows, int cols, uint64_t tiles, int max_tiles, uint64_t table, int parts,
+                            int max_rows, int lds, uint64_t y, int ldy, int f32_out, void* stream);
+uint64_t plora_static_scratch_bytes(void);
+const char* plora_static_error(void);
+
 /* Device status word: 0, or the PLORA_ERR_* a kernel recorded (bounded wait ran out, capacity).
  * Synchronises the device. */
 int plora_device_status(plora_t* h);

@@ -123,6 +123,9 @@ SYMBOLS = {
     "plora_join": (_I, [_P, _P, _P]),
     "plora_set_run_min": (_I, [_P, _I]),
     "plora_device_status": (_I, [_P]),
+    "plora_site_apply_static": (_I, [_U64, _I, _I, _U64, _I, _U64, _I, _I, _I, _U64, _I, _I, _P]),
+    "plora_static_scratch_bytes": (_U64, []),
+    "plora_static_error": (C.c_char_p, []),
 }
 
 
@@ -439,6 +442,17 @@ class Linear:
             if side is not None and side != main:
                 L.join(main, side)
             L.expand(self.lora, lora, rows, y, ldy, f32_out, main)
+
+
+def site_apply_static(x, rows, cols, tiles, max_tiles, hook, lds, y, ldy, f32_out=False, stream=0):
+    """One layer's shrink + expand for callers that cannot allocate device memory (an engine whose memory is
+    fully claimed at start-up, code inside a stream capture): the f32 intermediate sits in a fixed 8 MiB
+    array inside the library. Calls on one device must not overlap on the GPU; sizes over the array raise
+    a capacity error. ``hook`` supplies the layer's descriptor table, part count and widest part."""
+    rc = lib.plora_site_apply_static(x, rows, cols, tiles, max_tiles, hook.table, hook.parts, hook.max_rows, lds, y,
+                                     ldy, int(f32_out), _P(stream))
+    if rc != OK:
+        raise PloraError(rc, lib.plora_static_error().decode())
 
 
 # ----------------------------------------------------------------------------- scheduler side
