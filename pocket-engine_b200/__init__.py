@@ -14,7 +14,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libplora.so")
+# PLORA_LIB points at another build of the same library (a debug or instrumented one)
+LIB_PATH = os.environ.get("PLORA_LIB") or os.path.join(_HERE, "libplora.so")
 
 MAX_PARTS = 4   # src/lora.rs:14
 RANK_STEP = 16  # src/lora.rs:16

@@ -135,8 +135,9 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
             }
             si.parts.push_back(part);
         }
-        // K-split of the shrink, a function of the site alone: chunks of at least 512 inputs, at most 16.
-        int want = std::min(16, std::max(1, (si.cols + 511) / 512));
+        // K-split of the shrink, a function of the site alone: chunks of at least 512 inputs, at most 16
+        // of them, but never wider than 2048 (what one block stages in shared memory).
+        int want = std::max((si.cols + 2047) / 2048, std::min(16, std::max(1, (si.cols + 511) / 512)));
         si.kchunk = next_mult((si.cols + want - 1) / want, 256);
         si.nsplit = (si.cols + si.kchunk - 1) / si.kchunk;
         h->nsplit_max = std::max(h->nsplit_max, si.nsplit);
@@ -190,6 +191,8 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
             check("alloc meta", cudaMalloc((void**)&h->meta, meta_words * 4));
             check("pinned meta", cudaMallocHost((void**)&h->host_meta, (size_t)(1 + 3 * h->cap_tiles) * 4));
             check("alloc status", cudaMalloc((void**)&h->status, 64));
+            check("kernel attributes", plora_kernels_init(h->seg));
+            if (const char* e = getenv("PLORA_PDL")) h->pdl = e[0] != '0';
             if (rc == PLORA_OK) {
                 memset(h->host_tables, 0, h->table_bytes);
                 check("zero tables", cudaMemset(h->tables, 0, h->table_bytes));  // src/lora.rs:494
@@ -614,6 +617,7 @@ int plora_step_begin(plora_t* h, int max_tiles, void* stream, plora_step* out) {
     if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
     if (max_tiles < 0) return fail(h, PLORA_ERR_ARG, "max_tiles is negative");
     int32_t* segs = h->meta + (1 + 3 * h->cap_tiles);
+    h->pdl_armed = false;
     CU(h, "meta_group", plora_launch_meta_group(h->meta, segs, h->seg, h->status, as_stream(stream)));
     out->tiles = (uint64_t)(uintptr_t)h->meta;
     out->s = (uint64_t)(uintptr_t)h->s;
@@ -633,13 +637,17 @@ int plora_shrink(plora_t* h, const plora_hook* hook, const plora_step* step, uin
     if (rows < 0 || rows > h->max_tokens) return fail(h, PLORA_ERR_CAPACITY, "more rows than max_tokens");
     if (!x || (x & 15)) return fail(h, PLORA_ERR_ARG, "x must be a 16-byte aligned device address");
     const SiteInfo& site = h->sites[(size_t)hook->site];
-    int work_cap = std::min(step->max_tiles, rows);  // src/linear.rs:862
+    // src/linear.rs:862 bounds the grid by min(max_tiles, rows); grouped by slot, the work items are also
+    // at most one per slot plus one per 16 tokens
+    int work_cap = std::min(std::min(step->max_tiles, rows), h->max_slots + rows / PLORA_WORK_TOKENS);
     if (work_cap == 0) return PLORA_OK;
+    const bool pdl = h->pdl && h->pdl_armed;
+    h->pdl_armed = true;
     CU(h, "shrink",
        plora_launch_shrink((const void*)(uintptr_t)x, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
                            h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s,
                            (size_t)(step->s_stride / 4), step->lds, site.kchunk, site.nsplit, work_cap,
-                           hook->parts * h->max_rank, h->status, as_stream(stream)));
+                           hook->parts * h->max_rank, h->status, pdl, as_stream(stream)));
     return PLORA_OK;
 }
 
@@ -652,12 +660,14 @@ int plora_expand(plora_t* h, const plora_hook* hook, const plora_step* step, int
     if (!y || (y & (f32_out ? 7 : 3)) || (ldy & 1))
         return fail(h, PLORA_ERR_ARG, "y must be aligned to two elements and ldy even");
     const SiteInfo& site = h->sites[(size_t)hook->site];
-    int work_cap = std::min(step->max_tiles, rows);  // src/linear.rs:900
+    int work_cap = std::min(std::min(step->max_tiles, rows), h->max_slots + rows / PLORA_WORK_TOKENS);  // src/linear.rs:900
     if (work_cap == 0) return PLORA_OK;
+    const bool pdl = h->pdl && h->pdl_armed;
+    h->pdl_armed = true;
     CU(h, "expand",
        plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
                            (const int32_t*)(uintptr_t)step->segs, h->seg, (const plora_desc*)(uintptr_t)hook->table,
-                           (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap, h->status,
+                           (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap, h->status, pdl,
                            as_stream(stream)));
     return PLORA_OK;
 }

@@ -15,6 +15,7 @@
 // most PLORA_WORK_TOKENS tokens of one slot. Tile path: runs of contiguous tokens of one slot that are
 // at least PLORA_RUN_MIN long, cut into tensor-core tiles of PLORA_MMA_TOKENS tokens.
 #define PLORA_WORK_TOKENS 16
+#define PLORA_WORK_WORDS 32
 #define PLORA_MMA_TOKENS 128
 #define PLORA_RUN_MIN_DEFAULT 64
 
@@ -33,8 +34,10 @@ struct SegLayout {
     __host__ __device__ int act() const { return SEG_HDR; }                            // [max_slots] slot ids, ascending
     __host__ __device__ int seg_off() const { return act() + max_slots; }              // [max_slots + 1] by active index
     __host__ __device__ int perm() const { return seg_off() + max_slots + 1; }         // [max_tokens] token rows by slot
-    __host__ __device__ int work() const { return perm() + max_tokens; }               // [cap_tiles][3] slot, perm start, count
-    __host__ __device__ int mma() const { return work() + 3 * cap_tiles; }             // [cap_tiles][3] start, len, slot
+    // [cap_tiles][PLORA_WORK_WORDS]: slot, perm start, count, 0, then the count token rows themselves, so
+    // one 128-byte line tells a block everything about its work item
+    __host__ __device__ int work() const { return (perm() + max_tokens + 31) / 32 * 32; }
+    __host__ __device__ int mma() const { return work() + PLORA_WORK_WORDS * cap_tiles; }  // [cap_tiles][3] start, len, slot
     __host__ __device__ int words() const { return mma() + 3 * cap_tiles; }
 };
 
@@ -96,6 +99,8 @@ struct plora {
     cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
     mutable std::string err;
     int sm_count = 148;
+    bool pdl = true;        // launch with programmatic stream serialization
+    bool pdl_armed = false;  // false right after the step's grouping kernel: the next launch is a plain one
 };
 
 size_t plora_meta_group_smem(const SegLayout& lay);
@@ -105,9 +110,10 @@ cudaError_t plora_launch_meta_tiles(const int32_t* cu, const int32_t* seq_slot, 
                                     int cap_tiles, int* status, cudaStream_t st);
 cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status,
                                     cudaStream_t st);
+cudaError_t plora_kernels_init(const SegLayout& lay);
 cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay,
                                 const plora_desc* table, float* S, size_t s_stride_elems, int lds, int kchunk,
-                                int nsplit, int work_cap, int max_rank_total, int* status, cudaStream_t st);
+                                int nsplit, int work_cap, int max_rank_total, int* status, bool pdl, cudaStream_t st);
 cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, int nsplit, const int32_t* segs,
                                 SegLayout lay, const plora_desc* table, void* y, int ldy, int f32_out, int parts,
-                                int max_rows, int work_cap, int* status, cudaStream_t st);
+                                int max_rows, int work_cap, int* status, bool pdl, cudaStream_t st);

@@ -14,9 +14,26 @@
 
 typedef __nv_bfloat16 bf16;
 
-namespace {
+#ifdef PLORA_TRACE
+// Debug build only: per-block time stamps (SM cycle counter and the global nanosecond timer).
+__device__ unsigned long long* g_plora_trace = nullptr;
+extern "C" int plora_trace_set(unsigned long long* buf) {
+    return (int)cudaMemcpyToSymbol(g_plora_trace, &buf, sizeof(buf));
+}
+#define TRACE(i)                                                                                         \
+    do {                                                                                                 \
+        if (threadIdx.x == 0 && g_plora_trace) {                                                         \
+            unsigned long long gt_;                                                                      \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                                      \
+            const size_t b_ = ((size_t)blockIdx.z * gridDim.y * gridDim.x + blockIdx.y * gridDim.x + blockIdx.x) * 16; \
+            g_plora_trace[b_ + (i)] = gt_;                                                               \
+        }                                                                                                \
+    } while (0)
+#else
+#define TRACE(i)
+#endif
 
-__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+namespace {
 
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
     // a bf16 is the upper half of an f32
@@ -230,10 +247,13 @@ __global__ void __launch_bounds__(1024) plora_meta_group_kernel(const int* __res
             seg_base[s] = off;
             int* work = segs + lay.work();
             for (int q = 0; q < nw; q++) {
-                work[3 * (woff + q)] = s;
-                work[3 * (woff + q) + 1] = off + q * PLORA_WORK_TOKENS;
-                work[3 * (woff + q) + 2] = min(PLORA_WORK_TOKENS, c - q * PLORA_WORK_TOKENS);
+                int* wi = work + PLORA_WORK_WORDS * (woff + q);
+                wi[0] = s;
+                wi[1] = off + q * PLORA_WORK_TOKENS;
+                wi[2] = min(PLORA_WORK_TOKENS, c - q * PLORA_WORK_TOKENS);
+                wi[3] = 0;
             }
+            cnt[s] = woff;  // from here on: the slot's first work item
         }
         if (tid == 0) segs[lay.seg_off() + n_act] = n_gather;
     }
@@ -276,13 +296,19 @@ __global__ void __launch_bounds__(1024) plora_meta_group_kernel(const int* __res
         __syncthreads();
     }
 
-    // perm
+    // perm, and the same token rows inside the work items
     int* perm = segs + lay.perm();
+    int* work = segs + lay.work();
     for (int r = tid; r < n_runs; r += 1024) {
         const int pos = run_pos[r];
         if (pos < 0) continue;
-        const int start = run_start[r], len = run_len[r];
-        for (int k = 0; k < len; k++) perm[pos + k] = start + k;
+        const int start = run_start[r], len = run_len[r], slot = run_slot[r];
+        const int rel0 = pos - seg_base[slot], w0 = cnt[slot];
+        for (int k = 0; k < len; k++) {
+            perm[pos + k] = start + k;
+            const int rel = rel0 + k;
+            work[PLORA_WORK_WORDS * (w0 + rel / PLORA_WORK_TOKENS) + 4 + rel % PLORA_WORK_TOKENS] = start + k;
+        }
     }
     const int any_bad = __syncthreads_or(bad);
     if (any_bad && tid == 0) atomicMax(status, PLORA_ERR_ARG);
@@ -325,49 +351,135 @@ __device__ __forceinline__ float reduce16(float (&v)[16], int lane) {
     return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
 }
 
-// Shrink over gather work items. Grid (work items, K-splits); 128 threads. A work item is up to 16 tokens
-// of one slot; each warp takes 4 of every 16 rows of the slot's stacked A and 4 tokens at a time, its
-// lanes 8 inputs each per 256-wide step; sums cross the warp by shuffles. Every (token, row, split) is
-// written exactly once.
+// ---- bulk async copies into shared memory, mbarriers, programmatic dependent launch ----
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Waits for a phase of the barrier with an iteration limit; on running out it records PLORA_ERR_TIMEOUT in
+// the status word and returns false, so the kernel can leave instead of hanging.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
+    for (int i = 0; i < (1 << 22); i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicMax(status, PLORA_ERR_TIMEOUT);
+    return false;
+}
+
+// global -> shared bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned), completion
+// counted on `bar`
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Programmatic dependent launch. Every kernel of the path waits for the kernels before it and only then
+// lets the next one start its prologue, so a prologue may read anything written two or more kernels back
+// (slabs, descriptors, the step's grouping) but nothing the kernel right before it writes.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ uint4 lds16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+
+// Shrink over gather work items. Grid (K-splits x row tiles, 1, work items); 128 threads. A work item is up
+// to 16 tokens of one slot, described by one 128-byte record. The block's rows of the slot's stacked A (one
+// K-chunk wide) arrive in shared memory by bulk async copies issued before the dependency wait; the tokens'
+// x chunks follow right after it. Each warp takes 4 of every 16 rows and 4 tokens at a time, its lanes 8
+// inputs each per 256-wide step; sums cross the warp by shuffles. Every (token, row, split) is written
+// exactly once.
 __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __restrict__ X, int ldx, int K,
                                                                    const int* __restrict__ segs, SegLayout lay,
                                                                    const plora_desc* __restrict__ table,
                                                                    float* __restrict__ S, size_t s_stride, int lds,
-                                                                   int kchunk) {
-    const int w = blockIdx.x;
-    if (w >= segs[SEG_N_WORK]) return;
-    const int* work = segs + lay.work() + 3 * w;
-    const int slot = work[0], p0 = work[1], cnt = work[2];
+                                                                   int kchunk, int rps, int rt_max,
+                                                                   int* __restrict__ status) {
+    extern __shared__ __align__(128) unsigned char dsm[];
+    __shared__ __align__(8) uint64_t bars[2];
+    __shared__ int stok[PLORA_WORK_TOKENS];
+    const int w = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* work = segs + lay.work() + PLORA_WORK_WORDS * w;
+    // independent loads first: the header, the record's head, this lane's token
+    const int n_work = segs[SEG_N_WORK];
+    const int slot = work[0], cnt = work[2];
+    const int mytok = work[4 + (lane & 15)];
+    TRACE(0);
+    if (threadIdx.x == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        mbar_fence_init();
+    }
+    if (w >= n_work) return;
+    TRACE(1);
     const plora_desc& d = table[slot];
     const int rank = d.rank;
-    if (rank == 0) return;
-    const bf16* A = reinterpret_cast<const bf16*>(d.a);
-    const int k0 = blockIdx.y * kchunk, k1 = min(K, k0 + kchunk);
-    const int* perm = segs + lay.perm() + p0;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* Sout = S + (size_t)blockIdx.y * s_stride;
+    const int split = blockIdx.x / rt_max, rt = blockIdx.x - split * rt_max;
+    const int row0 = rt * rps;
+    if (row0 >= rank) return;
+    TRACE(2);
+    const int rows = min(rps, rank - row0);
+    const int k0 = split * kchunk, klen = min(kchunk, K - k0);
+    const uint32_t kbytes = (uint32_t)klen * 2u;
+    unsigned char* As = dsm;
+    unsigned char* Xs = dsm + (size_t)rps * kchunk * 2;
+    if (threadIdx.x < PLORA_WORK_TOKENS) stok[threadIdx.x] = mytok;
+    __syncthreads();
+    if (warp == 0) {
+        const bf16* A = reinterpret_cast<const bf16*>(d.a) + (size_t)row0 * K + k0;
+        if (lane == 0) mbar_expect_tx(&bars[0], (uint32_t)rows * kbytes);
+        __syncwarp();
+        for (int r = lane; r < rows; r += 32) bulk_g2s(As + (size_t)r * kbytes, A + (size_t)r * K, kbytes, &bars[0]);
+    }
+    TRACE(3);
+    pdl_wait();
+    TRACE(4);
+    pdl_trigger();
+    if (warp == 0) {
+        if (lane == 0) mbar_expect_tx(&bars[1], (uint32_t)cnt * kbytes);
+        __syncwarp();
+        if (lane < cnt) bulk_g2s(Xs + (size_t)lane * kbytes, X + (size_t)mytok * ldx + k0, kbytes, &bars[1]);
+    }
+    if (!mbar_wait(&bars[0], 0, status)) return;
+    TRACE(5);
+    if (!mbar_wait(&bars[1], 0, status)) return;
+    TRACE(6);
+    float* Sout = S + (size_t)split * s_stride;
     for (int tp = 0; tp < cnt; tp += 4) {
         const int nt = min(4, cnt - tp);
-        int tok[4];
-#pragma unroll
-        for (int t = 0; t < 4; t++) tok[t] = perm[tp + min(t, nt - 1)];
-        for (int n0 = warp * 4; n0 < rank; n0 += 16) {
+        for (int n0 = warp * 4; n0 < rows; n0 += 16) {
             float acc[16];
 #pragma unroll
             for (int i = 0; i < 16; i++) acc[i] = 0.f;
-            for (int k = k0 + lane * 8; k < k1; k += 256) {
-                uint4 av[4], xv[4];
-#pragma unroll
-                for (int r = 0; r < 4; r++) av[r] = ldg16(A + (size_t)(n0 + r) * K + k);
-#pragma unroll
-                for (int t = 0; t < 4; t++) xv[t] = ldg16(X + (size_t)tok[t] * ldx + k);
+            for (int k = lane * 8; k < klen; k += 256) {
                 float xf[4][8];
 #pragma unroll
-                for (int t = 0; t < 4; t++) unpack8(xv[t], xf[t]);
+                for (int t = 0; t < 4; t++) unpack8(lds16(Xs + (size_t)(tp + min(t, nt - 1)) * kbytes + k * 2), xf[t]);
 #pragma unroll
                 for (int r = 0; r < 4; r++) {
                     float af[8];
-                    unpack8(av[r], af);
+                    unpack8(lds16(As + (size_t)(n0 + r) * kbytes + k * 2), af);
 #pragma unroll
                     for (int t = 0; t < 4; t++)
 #pragma unroll
@@ -377,91 +489,148 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
             const float v = reduce16(acc, lane);
             if ((lane & 1) == 0) {
                 const int i = lane >> 1, r = i >> 2, t = i & 3;
-                if (t < nt) Sout[(size_t)tok[t] * lds + n0 + r] = v;
+                if (t < nt) Sout[(size_t)stok[tp + t] * lds + row0 + n0 + r] = v;
             }
         }
     }
+    TRACE(7);
 }
 
-// Expand over gather work items. Grid (work items, ceil(max part rows / 256), parts); 128 threads, two
-// adjacent output columns each. The work item's S rows (partials added in split order) sit in shared
-// memory; every thread streams its two rows of B once and updates y for each token.
-template <int TOKS>
-__device__ __forceinline__ void expand_body(const float* ss, const int* stok, int cnt, int r, const bf16* b, void* Y,
-                                            int ldy, int col, int f32_out) {
-    float acc[TOKS][2];
+// Expand over gather work items. Grid (column blocks, parts, work items); 128 threads, two adjacent output
+// columns each. The block's rows of B arrive in shared memory by one bulk async copy issued before the
+// dependency wait. After it, the work item's S rows (K-split partials, all in flight together, added in
+// split order) go to shared memory while the y values are already on their way; every thread then walks
+// its two rows of B once per group of 4 tokens and writes y back.
+#define EXP_SPAD 12  // floats per 8-wide piece of an S row in shared memory (conflict-free for rotated reads)
+
+__global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float* __restrict__ S, size_t s_stride,
+                                                                      int lds, int nsplit,
+                                                                      const int* __restrict__ segs, SegLayout lay,
+                                                                      const plora_desc* __restrict__ table, void* Y,
+                                                                      int ldy, int f32_out, int nc, int bs_bytes,
+                                                                      int* __restrict__ status) {
+    extern __shared__ __align__(128) unsigned char dsm[];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int stok[PLORA_WORK_TOKENS];
+    const int w = blockIdx.z;
+    const int* work = segs + lay.work() + PLORA_WORK_WORDS * w;
+    const int n_work = segs[SEG_N_WORK];
+    const int slot = work[0], cnt = work[2];
+    const int mytok = work[4 + (threadIdx.x & 15)];
+    TRACE(0);
+    if (w >= n_work) return;
+    TRACE(1);
+    const plora_desc& d = table[slot];
+    const int p = blockIdx.y, r = d.r[p];
+    if (r == 0) return;
+    TRACE(2);
+    const int rows = d.rows[p], c0 = blockIdx.x * nc;
+    if (c0 >= rows) return;
+    const int ncols = min(nc, rows - c0);
+    unsigned char* Bs = dsm;
+    float* ss = reinterpret_cast<float*>(dsm + bs_bytes);
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+        const uint32_t bytes = (uint32_t)ncols * (uint32_t)r * 2u;
+        mbar_expect_tx(&bar, bytes);
+        bulk_g2s(Bs, reinterpret_cast<const bf16*>(d.b[p]) + (size_t)c0 * r, bytes, &bar);
+    }
+    if (threadIdx.x < PLORA_WORK_TOKENS) stok[threadIdx.x] = mytok;
+    const int r_off = d.r_off[p];
+    const int c = 2 * threadIdx.x;
+    const bool mine = c < ncols;
+    const size_t ycol = (size_t)d.off[p] + c0 + c;
+    TRACE(3);
+    pdl_wait();
+    TRACE(4);
+    pdl_trigger();
+    __syncthreads();
+    // y of the first token group: on its way before anything else is waited for
+    float2 yv[4];
+    if (mine) {
 #pragma unroll
-    for (int t = 0; t < TOKS; t++) acc[t][0] = acc[t][1] = 0.f;
-    for (int j = 0; j < r; j += 8) {
-        float f0[8], f1[8];
-        unpack8(ldg16(b + j), f0);
-        unpack8(ldg16(b + r + j), f1);
-#pragma unroll
-        for (int t = 0; t < TOKS; t++) {
+        for (int t = 0; t < 4; t++) {
             if (t < cnt) {
-                const float4 s0 = *reinterpret_cast<const float4*>(ss + t * r + j);
-                const float4 s1 = *reinterpret_cast<const float4*>(ss + t * r + j + 4);
-                const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                const size_t at = (size_t)stok[t] * ldy + ycol;
+                if (f32_out) yv[t] = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(Y) + at);
+                else yv[t] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(Y) + at));
+            }
+        }
+    }
+    const int P = r >> 3;  // 16-byte pieces per row of B
+    for (int i = threadIdx.x; i < cnt * r; i += blockDim.x) {
+        const int t = i / r, j = i - t * r;
+        const float* sp = S + (size_t)stok[t] * lds + r_off + j;
+        float acc = 0.f;
+        for (int s0 = 0; s0 < nsplit; s0 += 8) {
+            float v[8];
 #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    acc[t][0] = fmaf(sv[e], f0[e], acc[t][0]);
-                    acc[t][1] = fmaf(sv[e], f1[e], acc[t][1]);
+            for (int s = 0; s < 8; s++) v[s] = s0 + s < nsplit ? __ldcg(sp + (size_t)(s0 + s) * s_stride) : 0.f;
+#pragma unroll
+            for (int s = 0; s < 8; s++)
+                if (s0 + s < nsplit) acc = s0 + s == 0 ? v[s] : acc + v[s];
+        }
+        ss[t * P * EXP_SPAD + (j >> 3) * EXP_SPAD + (j & 7)] = acc;
+    }
+    __syncthreads();
+    TRACE(5);
+    if (!mbar_wait(&bar, 0, status)) return;
+    TRACE(6);
+    if (!mine) return;
+    const int rot = (P >= 8 ? threadIdx.x : threadIdx.x >> 1) % P;
+    const unsigned char* b0 = Bs + (size_t)c * r * 2;
+    const unsigned char* b1 = b0 + (size_t)r * 2;
+    const int sstride = P * EXP_SPAD;
+    for (int tg = 0; tg < cnt; tg += 4) {
+        if (tg > 0) {
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                if (tg + t < cnt) {
+                    const size_t at = (size_t)stok[tg + t] * ldy + ycol;
+                    if (f32_out) yv[t] = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(Y) + at);
+                    else yv[t] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(Y) + at));
                 }
             }
         }
-    }
+        float acc[4][2];
 #pragma unroll
-    for (int t = 0; t < TOKS; t++) {
-        if (t < cnt) {
-            const size_t at = (size_t)stok[t] * ldy + col;
-            if (f32_out) {
-                float2* p = reinterpret_cast<float2*>(reinterpret_cast<float*>(Y) + at);
-                float2 v = *p;
-                v.x += acc[t][0];
-                v.y += acc[t][1];
-                *p = v;
-            } else {
-                __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<bf16*>(Y) + at);
-                const float2 v = __bfloat1622float2(*p);
-                *p = __floats2bfloat162_rn(v.x + acc[t][0], v.y + acc[t][1]);
+        for (int t = 0; t < 4; t++) acc[t][0] = acc[t][1] = 0.f;
+        int jp = rot;
+        for (int q = 0; q < P; q++) {
+            float f0[8], f1[8];
+            unpack8(lds16(b0 + jp * 16), f0);
+            unpack8(lds16(b1 + jp * 16), f1);
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                if (tg + t < cnt) {
+                    const float* sp = ss + (tg + t) * sstride + jp * EXP_SPAD;
+                    const float4 s0 = *reinterpret_cast<const float4*>(sp);
+                    const float4 s1 = *reinterpret_cast<const float4*>(sp + 4);
+                    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        acc[t][0] = fmaf(sv[e], f0[e], acc[t][0]);
+                        acc[t][1] = fmaf(sv[e], f1[e], acc[t][1]);
+                    }
+                }
+            }
+            jp = jp + 1 == P ? 0 : jp + 1;
+        }
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            if (tg + t < cnt) {
+                const size_t at = (size_t)stok[tg + t] * ldy + ycol;
+                if (f32_out)
+                    *reinterpret_cast<float2*>(reinterpret_cast<float*>(Y) + at) =
+                        make_float2(yv[t].x + acc[t][0], yv[t].y + acc[t][1]);
+                else
+                    *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<bf16*>(Y) + at) =
+                        __floats2bfloat162_rn(yv[t].x + acc[t][0], yv[t].y + acc[t][1]);
             }
         }
     }
-}
-
-__global__ void __launch_bounds__(128) plora_expand_gather_kernel(const float* __restrict__ S, size_t s_stride,
-                                                                   int lds, int nsplit, const int* __restrict__ segs,
-                                                                   SegLayout lay,
-                                                                   const plora_desc* __restrict__ table, void* Y,
-                                                                   int ldy, int f32_out) {
-    extern __shared__ float ss[];  // [16][r]
-    __shared__ int stok[PLORA_WORK_TOKENS];
-    const int w = blockIdx.x;
-    if (w >= segs[SEG_N_WORK]) return;
-    const int* work = segs + lay.work() + 3 * w;
-    const int slot = work[0], p0 = work[1], cnt = work[2];
-    const plora_desc& d = table[slot];
-    const int p = blockIdx.z, r = d.r[p];
-    if (r == 0) return;
-    const int rows = d.rows[p], c0 = blockIdx.y * 256;
-    if (c0 >= rows) return;
-    const int* perm = segs + lay.perm() + p0;
-    if (threadIdx.x < cnt) stok[threadIdx.x] = perm[threadIdx.x];
-    const int r_off = d.r_off[p];
-    for (int i = threadIdx.x; i < cnt * r; i += 128) {
-        const int t = i / r, j = i - t * r;
-        const float* sp = S + (size_t)perm[t] * lds + r_off + j;
-        float acc = sp[0];
-        for (int s = 1; s < nsplit; s++) acc += sp[(size_t)s * s_stride];
-        ss[i] = acc;
-    }
-    __syncthreads();
-    const int c = c0 + 2 * threadIdx.x;
-    if (c >= rows) return;
-    const bf16* b = reinterpret_cast<const bf16*>(d.b[p]) + (size_t)c * r;
-    const int col = d.off[p] + c;
-    if (cnt <= 4) expand_body<4>(ss, stok, cnt, r, b, Y, ldy, col, f32_out);
-    else expand_body<PLORA_WORK_TOKENS>(ss, stok, cnt, r, b, Y, ldy, col, f32_out);
+    TRACE(7);
 }
 
 }  // namespace
@@ -478,36 +647,76 @@ size_t plora_meta_group_smem(const SegLayout& lay) {
     return (size_t)(4 * lay.cap_tiles + 3 * (lay.max_slots + 1) + 32 * (lay.max_slots + 1)) * sizeof(int);
 }
 
+// One-time function attributes (dynamic shared memory above 48 KB). Called from plora_create, never from
+// the launch path, so launches stay legal inside a stream capture.
+cudaError_t plora_kernels_init(const SegLayout& lay) {
+    cudaError_t e = cudaFuncSetAttribute(plora_meta_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)plora_meta_group_smem(lay) > 48 * 1024 ? (int)plora_meta_group_smem(lay)
+                                                                                       : 48 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(plora_shrink_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 136 * 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(plora_expand_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+}
+
 cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status,
                                     cudaStream_t st) {
-    const size_t smem = plora_meta_group_smem(lay);
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(plora_meta_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
-        if (e != cudaSuccess) return e;
-    }
-    plora_meta_group_kernel<<<1, 1024, smem, st>>>(tiles, segs, lay, status);
+    plora_meta_group_kernel<<<1, 1024, plora_meta_group_smem(lay), st>>>(tiles, segs, lay, status);
     return cudaGetLastError();
+}
+
+namespace {
+template <typename... Params, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                       Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
+}
+}  // namespace
+
+// rows of A per block: 16 (one 4-row group per warp), so that a slot's rows spread over many blocks and
+// each block's copies are issued and consumed quickly
+int plora_shrink_rps(int kchunk) {
+    (void)kchunk;
+    return 16;
 }
 
 cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay,
                                 const plora_desc* table, float* S, size_t s_stride_elems, int lds, int kchunk,
-                                int nsplit, int work_cap, int max_rank_total, int* status, cudaStream_t st) {
-    (void)max_rank_total;
-    (void)status;
-    dim3 grid((unsigned)work_cap, (unsigned)nsplit, 1);
-    plora_shrink_gather_kernel<<<grid, 128, 0, st>>>(reinterpret_cast<const bf16*>(x), ldx, K, segs, lay, table, S,
-                                                     s_stride_elems, lds, kchunk);
-    return cudaGetLastError();
+                                int nsplit, int work_cap, int max_rank_total, int* status, bool pdl, cudaStream_t st) {
+    const int rps = plora_shrink_rps(kchunk);
+    const int rt_max = (max_rank_total + rps - 1) / rps;
+    dim3 grid((unsigned)(nsplit * rt_max), 1, (unsigned)work_cap);
+    const size_t smem = (size_t)(rps + PLORA_WORK_TOKENS) * (size_t)kchunk * 2;
+    return launch_pdl(plora_shrink_gather_kernel, grid, dim3(128), smem, st, pdl, reinterpret_cast<const bf16*>(x), ldx,
+                      K, segs, lay, table, S, s_stride_elems, lds, kchunk, rps, rt_max, status);
+}
+
+// output columns per block (two per thread): 512 for wide layers so the grid stays near one wave, 256
+// otherwise, fewer when a row of B is so long that the block's rows would pass 64 KB of shared memory
+int plora_expand_nc(int max_rank, int max_rows) {
+    int nc = max_rows >= 8192 ? 512 : 256;
+    while (nc > 32 && nc * max_rank * 2 > 64 * 1024) nc >>= 1;
+    return nc;
 }
 
 cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, int nsplit, const int32_t* segs,
                                 SegLayout lay, const plora_desc* table, void* y, int ldy, int f32_out, int parts,
-                                int max_rows, int work_cap, int* status, cudaStream_t st) {
-    (void)status;
-    dim3 grid((unsigned)work_cap, (unsigned)((max_rows + 255) / 256), (unsigned)parts);
-    const size_t smem = (size_t)PLORA_WORK_TOKENS * (size_t)(lds / PLORA_MAX_PARTS) * sizeof(float);
-    plora_expand_gather_kernel<<<grid, 128, smem, st>>>(S, s_stride_elems, lds, nsplit, segs, lay, table, y, ldy,
-                                                        f32_out);
-    return cudaGetLastError();
+                                int max_rows, int work_cap, int* status, bool pdl, cudaStream_t st) {
+    const int max_rank = lds / PLORA_MAX_PARTS;
+    const int nc = plora_expand_nc(max_rank, max_rows);
+    const int bs_bytes = nc * max_rank * 2;
+    dim3 grid((unsigned)((max_rows + nc - 1) / nc), (unsigned)parts, (unsigned)work_cap);
+    const size_t smem = (size_t)bs_bytes + (size_t)PLORA_WORK_TOKENS * (size_t)(max_rank / 8) * EXP_SPAD * sizeof(float);
+    return launch_pdl(plora_expand_gather_kernel, grid, dim3((unsigned)(nc / 2)), smem, st, pdl, S, s_stride_elems, lds, nsplit, segs,
+                      lay, table, y, ldy, f32_out, nc, bs_bytes, status);
 }

@@ -226,7 +226,9 @@ int plora_site_apply_static(uint64_t x, int rows, int cols, uint64_t tiles, int 
     if (rows < 0 || max_tiles < 0 || parts < 1 || parts > PLORA_MAX_PARTS || max_rows <= 0 || lds <= 0 || (lds & 63))
         return sfail(PLORA_ERR_ARG, "rows, max_tiles, parts, max_rows or lds out of range");
     // the same K-split rule the handle-based path fixes per layer: chunks of at least 512 inputs, at most 16
-    const int want = cols + 511 < 512 * 16 ? (cols + 511) / 512 : 16;
+    // of them, but never wider than 2048
+    const int few = cols + 511 < 512 * 16 ? (cols + 511) / 512 : 16;
+    const int want = (cols + 2047) / 2048 > few ? (cols + 2047) / 2048 : few;
     const int kchunk = ((cols + want - 1) / want + 255) / 256 * 256;
     const int nsplit = (cols + kchunk - 1) / kchunk;
     const size_t need = (size_t)nsplit * (size_t)rows * (size_t)lds * 4;

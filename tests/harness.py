@@ -173,14 +173,16 @@ class SegView:
         ms, mt, cap = loras.max_slots, loras.max_tokens, loras.max_lora_tiles()
         act, seg_off = 8, 8 + ms
         perm = seg_off + ms + 1
-        work = perm + mt
-        mma = work + 3 * cap
+        work = (perm + mt + 31) // 32 * 32
+        mma = work + 32 * cap
         words = dev_read(step.segs, (mma + 3 * cap) * 4).view(np.int32)
         self.n_act, self.n_work, self.n_mma, self.n_gather, self.n_tiles, self.status = words[:6]
         self.act = words[act:act + self.n_act]
         self.seg_off = words[seg_off:seg_off + self.n_act + 1]
         self.perm = words[perm:perm + self.n_gather]
-        self.work = words[work:work + 3 * self.n_work].reshape(-1, 3)
+        items = words[work:work + 32 * self.n_work].reshape(-1, 32)
+        self.work = items[:, :3]
+        self.work_tokens = [list(it[4:4 + it[2]]) for it in items]
         self.mma = words[mma:mma + 3 * self.n_mma].reshape(-1, 3)
 
 

@@ -76,6 +76,7 @@ def test_grouping_is_a_stable_sort_by_slot(pe):
         # work items: each slot's segment cut into pieces of at most 16 tokens, in order
         want = [(s, o + k, min(16, c - k)) for s, o, c in zip(present, seg.seg_off, counts) for k in range(0, c, 16)]
         assert [tuple(w) for w in seg.work] == want
+        assert seg.work_tokens == [list(order[o:o + c]) for _, o, c in want]
     loras.device_status()
     loras.close()
 
