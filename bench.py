@@ -129,10 +129,16 @@ def run_ours(args, rank, world, local_rank):
     pool_bytes = probe.slot_bytes * wl.n_adapters
     probe.close()
     copies = int(min(32, max(2, -(-512 * 2 ** 20 // pool_bytes))))
+    if work["bytes"] > 4 * 126 * 2 ** 20:
+        copies = 1  # one step already streams several times the L2 size
     if args.copies:
         copies = args.copies
     main = torch.cuda.Stream(device=dev)
     side = torch.cuda.Stream(device=dev)
+    decode = int(wl.row_n.max()) == 1  # a decoding step: only one-token sequences
+    # streams == 1: shrink and expand in stream order on one stream (consecutive kernels overlap through
+    # programmatic dependent launch); streams == 2: the engine's fork/join with the shrink on a side stream
+    side_h = side.cuda_stream if args.streams == 2 else None
     facs = [wl.factors(i) for i in range(wl.n_adapters)]
     sets = []
     xs_host = [torch.from_numpy(wl.x_bits(si).view(np.int16)).pin_memory() for si in range(ns)]
@@ -150,7 +156,7 @@ def run_ours(args, rank, world, local_rank):
         cu = cu_host.to(dev)
         ss = ss_host.to(dev)
         L.meta_build(cu.data_ptr(), ss.data_ptr(), wl.n_seqs, main.cuda_stream)
-        step = L.lora_step(L.max_lora_tiles(), main.cuda_stream)
+        step = L.lora_step(L.max_lora_tiles(), main.cuda_stream, decode=decode)
         lins = [pe.Linear(L, si) for si in range(ns)]
         sets.append({"L": L, "x": x, "y": y, "cu": cu, "ss": ss, "step": step, "lins": lins})
     torch.cuda.synchronize()
@@ -164,12 +170,12 @@ def run_ours(args, rank, world, local_rank):
     graphs = []
     with torch.cuda.stream(main):
         for S in sets:
-            block(S, main.cuda_stream, side.cuda_stream)  # warm every kernel before capture
+            block(S, main.cuda_stream, side_h)  # warm every kernel before capture
         torch.cuda.synchronize()
         for S in sets:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=main):
-                block(S, main.cuda_stream, side.cuda_stream)
+                block(S, main.cuda_stream, side_h)
             graphs.append(g)
     torch.cuda.synchronize()
 
@@ -218,10 +224,10 @@ def run_ours(args, rank, world, local_rank):
             S["cu"].copy_(cu_host, non_blocking=True)
             S["ss"].copy_(ss_host, non_blocking=True)
             S["L"].meta_build(S["cu"].data_ptr(), S["ss"].data_ptr(), wl.n_seqs, m)
-            st = S["L"].lora_step(S["L"].max_lora_tiles(), m)
+            st = S["L"].lora_step(S["L"].max_lora_tiles(), m, decode=decode)
             for si in range(ns):
                 S["lins"][si].forward(S["x"][si].data_ptr(), wl.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1],
-                                      False, lora=st, main=m, side=side.cuda_stream)
+                                      False, lora=st, main=m, side=side_h)
             for si in range(ns):
                 y_out[si].copy_(S["y"][si].view(torch.int16), non_blocking=True)
         main.synchronize()
@@ -264,7 +270,7 @@ def run_ours(args, rank, world, local_rank):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(main)
             S["L"].meta_build(S["cu"].data_ptr(), S["ss"].data_ptr(), wl.n_seqs, m)
-            S["L"].lora_step(S["L"].max_lora_tiles(), m)
+            S["L"].lora_step(S["L"].max_lora_tiles(), m, decode=decode)
             b.record(main)
             evs.append((a, b))
         torch.cuda.synchronize()
@@ -291,10 +297,11 @@ def run_ours(args, rank, world, local_rank):
                    "adapters": wl.n_adapters, "slots_present": work["slots_present"], "sites": ns,
                    "l2": f"inputs larger than L2: {copies} rotating copies of pool+x+y = "
                          f"{copies * (pool_bytes + d2h + h2d // 2) / 2 ** 20:.0f} MiB",
-                   "partitioning": "adapter-affine, one batch per GPU, no collective", "graph": "one CUDA graph per copy"},
+                   "partitioning": "adapter-affine, one batch per GPU, no collective",
+                   "graph": f"one CUDA graph per copy, {args.streams} stream(s)"},
         "e2e": {"value": world * wl.tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": 8 * args.steps,
+        "gpu_launches": (8 if decode else 16) * args.steps,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                      "peak_kind": peak_kind, "traffic": None, "us_per_launch": kern[dom]["us"],
                      "algorithmic_bytes_per_launch": kern[dom]["bytes"]},
@@ -311,10 +318,15 @@ def run_ours(args, rank, world, local_rank):
 
 def cpu_port(wl_name, seconds, seed=0, threads=0, steps=None, warmup=0):
     """The oracle's multithreaded C restatement of the path, timed on the host cores. Returns
-    (tokens/s, cores, sample description, ms per step)."""
+    (tokens/s, cores, sample description, ms per step). The prefill workload is sampled: one of its eight
+    sequences (same shapes, one adapter), tokens/s counted on the tokens actually processed."""
     orc = entry.load_oracle()
     pe = entry.load_package()  # only the synthetic inputs and the tile rule (host arithmetic)
     wl = make_workload(wl_name, seed)
+    full_name = wl.name
+    if wl_name == "prefill":
+        from pocket_engine_b200 import workloads
+        wl = workloads.config3(seed=seed, seqs=1)
     table = orc.OracleTable(wl.sites, wl.n_adapters)
     for i in range(wl.n_adapters):
         table.upload(i + 1, orc.OracleAdapter(wl.sites, wl.factors(i), wl.max_rank))
@@ -328,7 +340,7 @@ def cpu_port(wl_name, seconds, seed=0, threads=0, steps=None, warmup=0):
         for si, site in enumerate(wl.sites):
             orc.site_mt(xs[si], site.cols, tiles, table.tables[si], s, ys[si], False, threads)
 
-    for _ in range(max(1, warmup)):
+    for _ in range(max(1, warmup) if wl.name == full_name else 0):
         one()
     n, t0 = 0, time.perf_counter()
     while True:
@@ -337,7 +349,8 @@ def cpu_port(wl_name, seconds, seed=0, threads=0, steps=None, warmup=0):
         el = time.perf_counter() - t0
         if (steps is not None and n >= steps) or (steps is None and el >= seconds):
             break
-    return wl.tokens * n / el, threads, f"{n} full steps of {wl.name} in {el:.1f} s", 1e3 * el / n, wl
+    what = "full steps" if wl.name == full_name else f"steps of a 1-of-8-sequences sample ({wl.name}) of {full_name}:"
+    return wl.tokens * n / el, threads, f"{n} {what} in {el:.1f} s", 1e3 * el / n, wl
 
 
 def run_reference(args, rank, world):
@@ -449,14 +462,18 @@ def reference_gpu(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=0, help="default: 200 (decode), 10 (prefill)")
+    ap.add_argument("--warmup", type=int, default=0, help="default: 20 (decode), 3 (prefill)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "plumbing"])
     ap.add_argument("--copies", type=int, default=0, help="override the number of rotating pool copies")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--streams", type=int, default=1, choices=[1, 2],
+                    help="1: one stream, kernels chained by programmatic dependent launch; 2: the engine's "
+                         "side-stream shrink with fork/join events")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3)
+    args.steps = args.steps or (10 if args.workload == "prefill" else 200)
+    args.warmup = max(args.warmup or (3 if args.workload == "prefill" else 20), 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -112,6 +112,8 @@ typedef struct {
     uint64_t segs;
     int32_t max_tiles;
     int32_t lds;
+    int32_t run_min; /* runs at least this long were routed to the tensor-core tile kernels in this step */
+    int32_t pad_;
 } plora_step;
 
 /* ---- registry: src/lora.rs ---- */
@@ -187,9 +189,11 @@ int plora_fill_tiles(const int32_t* row_n, const int32_t* row_slot, int n_rows, 
 int plora_meta_build(plora_t* h, uint64_t cu_dev, uint64_t seq_slot_dev, int n_seqs, void* stream);
 /* The engine's own route: tile words written on the host (pinned or pageable), copied stream-ordered. */
 int plora_meta_upload(plora_t* h, const int32_t* words, void* stream);
-/* Act::lora_step: regroups the handle's tile words by slot on the device (once per step, before the
- * first layer) and returns the per-step handle. max_tiles bounds the launch grids (src/engine.rs:448-451). */
-int plora_step_begin(plora_t* h, int max_tiles, void* stream, plora_step* out);
+/* Act::lora_step(l, max_tiles, decode): regroups the handle's tile words by slot on the device (once per
+ * step, before the first layer) and returns the per-step handle. max_tiles bounds the launch grids
+ * (src/engine.rs:448-451). decode != 0 says the step holds only tiles of a few tokens (the decoding graphs),
+ * so the tensor-core tile kernels are neither fed nor launched. */
+int plora_step_begin(plora_t* h, int max_tiles, int decode, void* stream, plora_step* out);
 uint64_t plora_tiles_ptr(const plora_t* h);
 
 /* ---- Linear::forward's bracket: src/linear.rs:428-443,844-921 ---- */

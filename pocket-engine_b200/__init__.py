@@ -67,7 +67,7 @@ class Hook(C.Structure):
 class StepLora(C.Structure):
     """src/lora.rs:455-467"""
     _fields_ = [("tiles", C.c_uint64), ("s", C.c_uint64), ("s_stride", C.c_uint64), ("segs", C.c_uint64),
-                ("max_tiles", C.c_int32), ("lds", C.c_int32)]
+                ("max_tiles", C.c_int32), ("lds", C.c_int32), ("run_min", C.c_int32), ("pad_", C.c_int32)]
 
 
 assert C.sizeof(Desc) == 112
@@ -116,7 +116,7 @@ SYMBOLS = {
     "plora_fill_tiles": (_I, [_I32P, _I32P, _I, _I32P, _I]),
     "plora_meta_build": (_I, [_P, _U64, _U64, _I, _P]),
     "plora_meta_upload": (_I, [_P, _I32P, _P]),
-    "plora_step_begin": (_I, [_P, _I, _P, C.POINTER(StepLora)]),
+    "plora_step_begin": (_I, [_P, _I, _I, _P, C.POINTER(StepLora)]),
     "plora_tiles_ptr": (_U64, [_P]),
     "plora_shrink": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _U64, _I, _P]),
     "plora_expand": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _U64, _I, _I, _P]),
@@ -392,10 +392,11 @@ class Loras:
         self._check(lib.plora_meta_upload(self._h, w.ctypes.data_as(_I32P), _P(stream)))
         return w
 
-    def lora_step(self, max_tiles, stream=0):
-        """Act::lora_step: groups the step's tiles by slot on the device and returns the StepLora."""
+    def lora_step(self, max_tiles, stream=0, decode=False):
+        """Act::lora_step(l, max_tiles, decode): groups the step's tiles by slot on the device and returns the
+        StepLora. ``decode`` marks a step of few-token tiles only (no tensor-core tile kernels)."""
         st = StepLora()
-        self._check(lib.plora_step_begin(self._h, max_tiles, _P(stream), C.byref(st)))
+        self._check(lib.plora_step_begin(self._h, max_tiles, int(decode), _P(stream), C.byref(st)))
         return st
 
     def set_run_min(self, tokens):

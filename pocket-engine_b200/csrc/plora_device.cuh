@@ -1,0 +1,103 @@
+// Device-side helpers shared by the kernels: bf16 unpacking, mbarriers, bulk async copies, programmatic
+// dependent launch, and the bounded waits every spin in this library goes through.
+#pragma once
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/plora.h"
+
+#ifdef PLORA_TRACE
+// Debug build only: per-block time stamps from the global nanosecond timer, 16 slots per block.
+static __device__ unsigned long long* g_plora_trace = nullptr;
+#define PLORA_TRACE_SETTER(name)                                                  \
+    extern "C" int name(unsigned long long* buf) {                                \
+        return (int)cudaMemcpyToSymbol(g_plora_trace, &buf, sizeof(buf));         \
+    }
+#define TRACE(i)                                                                                         \
+    do {                                                                                                 \
+        if (threadIdx.x == 0 && g_plora_trace) {                                                         \
+            unsigned long long gt_;                                                                      \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                                      \
+            const size_t b_ = ((size_t)blockIdx.z * gridDim.y * gridDim.x + blockIdx.y * gridDim.x + blockIdx.x) * 16; \
+            g_plora_trace[b_ + (i)] = gt_;                                                               \
+        }                                                                                                \
+    } while (0)
+#else
+#define PLORA_TRACE_SETTER(name)
+#define TRACE(i)
+#endif
+
+namespace {
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    // a bf16 is the upper half of an f32
+    f[0] = __uint_as_float(v.x << 16);
+    f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16);
+    f[3] = __uint_as_float(v.y & 0xffff0000u);
+    f[4] = __uint_as_float(v.z << 16);
+    f[5] = __uint_as_float(v.z & 0xffff0000u);
+    f[6] = __uint_as_float(v.w << 16);
+    f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+// ---- bulk async copies into shared memory, mbarriers, programmatic dependent launch ----
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Waits for a phase of the barrier with an iteration limit; on running out it records PLORA_ERR_TIMEOUT in
+// the status word and returns false, so the kernel can leave instead of hanging.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
+    for (int i = 0; i < (1 << 20); i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicMax(status, PLORA_ERR_TIMEOUT);
+    return false;
+}
+
+// global -> shared bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned), completion
+// counted on `bar`
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Programmatic dependent launch. Every kernel of the path waits for the kernels before it and only then
+// lets the next one start its prologue, so a prologue may read anything written two or more kernels back
+// (slabs, descriptors, the step's grouping) but nothing the kernel right before it writes.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// A block that has nothing to do leaves at once, except block 0, which first waits for the kernels before:
+// a grid completes only when all its blocks have, so every grid of the path outlasts its predecessors and
+// "the kernel before me is done" keeps meaning "everything before me is done".
+__device__ __forceinline__ void pdl_exit_idle() {
+    if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0) pdl_wait();
+}
+
+__device__ __forceinline__ uint4 lds16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+
+}  // namespace

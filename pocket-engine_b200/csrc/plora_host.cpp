@@ -152,7 +152,7 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
     h->seg.max_slots = max_slots;
     h->seg.max_tokens = max_tokens;
     h->seg.cap_tiles = h->cap_tiles;
-    h->seg.run_min = 1 << 30;  // every run takes the gather path until a tile path is enabled
+    h->seg.run_min = 1 << 30;  // every run takes the gather path unless the tile path can run (set below)
     if (max_slots > 1023 || h->max_rank > 512 || plora_meta_group_smem(h->seg) > 200 * 1024) {
         delete h;
         return fail(nullptr, PLORA_ERR_CAPACITY,
@@ -192,6 +192,9 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
             check("pinned meta", cudaMallocHost((void**)&h->host_meta, (size_t)(1 + 3 * h->cap_tiles) * 4));
             check("alloc status", cudaMalloc((void**)&h->status, 64));
             check("kernel attributes", plora_kernels_init(h->seg));
+            if (rc == PLORA_OK && h->max_rank <= 128) h->mma_ok = plora_mma_init() == cudaSuccess;
+            // runs of 64 or more contiguous tokens of one slot take the tensor-core tile kernels
+            if (h->mma_ok) h->seg.run_min = PLORA_RUN_MIN_DEFAULT;
             if (const char* e = getenv("PLORA_PDL")) h->pdl = e[0] != '0';
             if (rc == PLORA_OK) {
                 memset(h->host_tables, 0, h->table_bytes);
@@ -612,13 +615,17 @@ int plora_meta_upload(plora_t* h, const int32_t* words, void* stream) {
     return PLORA_OK;
 }
 
-int plora_step_begin(plora_t* h, int max_tiles, void* stream, plora_step* out) {
+int plora_step_begin(plora_t* h, int max_tiles, int decode, void* stream, plora_step* out) {
     if (!h || !out) return PLORA_ERR_ARG;
     if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
     if (max_tiles < 0) return fail(h, PLORA_ERR_ARG, "max_tiles is negative");
     int32_t* segs = h->meta + (1 + 3 * h->cap_tiles);
     h->pdl_armed = false;
-    CU(h, "meta_group", plora_launch_meta_group(h->meta, segs, h->seg, h->status, as_stream(stream)));
+    SegLayout lay = h->seg;
+    if (decode) lay.run_min = 1 << 30;
+    CU(h, "meta_group", plora_launch_meta_group(h->meta, segs, lay, h->status, as_stream(stream)));
+    out->run_min = lay.run_min;
+    out->pad_ = 0;
     out->tiles = (uint64_t)(uintptr_t)h->meta;
     out->s = (uint64_t)(uintptr_t)h->s;
     out->s_stride = (uint64_t)h->s_stride;
@@ -648,6 +655,11 @@ int plora_shrink(plora_t* h, const plora_hook* hook, const plora_step* step, uin
                            h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s,
                            (size_t)(step->s_stride / 4), step->lds, site.kchunk, site.nsplit, work_cap,
                            hook->parts * h->max_rank, h->status, pdl, as_stream(stream)));
+    if (h->mma_ok && rows >= step->run_min)
+        CU(h, "shrink (tile path)",
+           plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
+                                   h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s, step->lds,
+                                   hook->parts * h->max_rank, std::max(1, rows / 64), h->status, h->pdl, as_stream(stream)));
     return PLORA_OK;
 }
 
@@ -669,6 +681,11 @@ int plora_expand(plora_t* h, const plora_hook* hook, const plora_step* step, int
                            (const int32_t*)(uintptr_t)step->segs, h->seg, (const plora_desc*)(uintptr_t)hook->table,
                            (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap, h->status, pdl,
                            as_stream(stream)));
+    if (h->mma_ok && rows >= step->run_min)
+        CU(h, "expand (tile path)",
+           plora_launch_expand_mma((const float*)(uintptr_t)step->s, step->lds, (const int32_t*)(uintptr_t)step->segs, h->seg,
+                                   (const plora_desc*)(uintptr_t)hook->table, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
+                                   hook->max_rows, std::max(1, rows / 64), h->status, h->pdl, as_stream(stream)));
     return PLORA_OK;
 }
 
@@ -691,7 +708,9 @@ int plora_join(plora_t* h, void* main_stream, void* side_stream) {
 }
 
 int plora_set_run_min(plora_t* h, int tokens) {
-    if (!h || tokens < 1) return PLORA_ERR_ARG;
+    if (!h || tokens < 64) return fail(h, PLORA_ERR_ARG, "run_min must be at least 64 tokens");
+    if (!h->mma_ok && tokens < (1 << 30))
+        return fail(h, PLORA_ERR_CONFIG, "the tile path needs a device handle and max_rank <= 128");
     h->seg.run_min = tokens;
     return PLORA_OK;
 }

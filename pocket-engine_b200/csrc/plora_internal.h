@@ -100,6 +100,7 @@ struct plora {
     mutable std::string err;
     int sm_count = 148;
     bool pdl = true;        // launch with programmatic stream serialization
+    bool mma_ok = false;    // the tensor-core tile kernels can run (max_rank <= 128 and the driver entry point exists)
     bool pdl_armed = false;  // false right after the step's grouping kernel: the next launch is a plain one
 };
 
@@ -111,6 +112,13 @@ cudaError_t plora_launch_meta_tiles(const int32_t* cu, const int32_t* seq_slot, 
 cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status,
                                     cudaStream_t st);
 cudaError_t plora_kernels_init(const SegLayout& lay);
+cudaError_t plora_mma_init();
+cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, const int32_t* segs, SegLayout lay,
+                                    const plora_desc* table, float* S, int lds, int max_rank_total, int tile_cap,
+                                    int* status, bool pdl, cudaStream_t st);
+cudaError_t plora_launch_expand_mma(const float* S, int lds, const int32_t* segs, SegLayout lay,
+                                    const plora_desc* table, void* y, int ldy, int f32_out, int parts, int max_rows,
+                                    int tile_cap, int* status, bool pdl, cudaStream_t st);
 cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay,
                                 const plora_desc* table, float* S, size_t s_stride_elems, int lds, int kchunk,
                                 int nsplit, int work_cap, int max_rank_total, int* status, bool pdl, cudaStream_t st);

@@ -11,41 +11,13 @@
 #include <cuda_bf16.h>
 
 #include "plora_internal.h"
+#include "plora_device.cuh"
 
 typedef __nv_bfloat16 bf16;
 
-#ifdef PLORA_TRACE
-// Debug build only: per-block time stamps (SM cycle counter and the global nanosecond timer).
-__device__ unsigned long long* g_plora_trace = nullptr;
-extern "C" int plora_trace_set(unsigned long long* buf) {
-    return (int)cudaMemcpyToSymbol(g_plora_trace, &buf, sizeof(buf));
-}
-#define TRACE(i)                                                                                         \
-    do {                                                                                                 \
-        if (threadIdx.x == 0 && g_plora_trace) {                                                         \
-            unsigned long long gt_;                                                                      \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                                      \
-            const size_t b_ = ((size_t)blockIdx.z * gridDim.y * gridDim.x + blockIdx.y * gridDim.x + blockIdx.x) * 16; \
-            g_plora_trace[b_ + (i)] = gt_;                                                               \
-        }                                                                                                \
-    } while (0)
-#else
-#define TRACE(i)
-#endif
+PLORA_TRACE_SETTER(plora_trace_set)
 
 namespace {
-
-__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
-    // a bf16 is the upper half of an f32
-    f[0] = __uint_as_float(v.x << 16);
-    f[1] = __uint_as_float(v.x & 0xffff0000u);
-    f[2] = __uint_as_float(v.y << 16);
-    f[3] = __uint_as_float(v.y & 0xffff0000u);
-    f[4] = __uint_as_float(v.z << 16);
-    f[5] = __uint_as_float(v.z & 0xffff0000u);
-    f[6] = __uint_as_float(v.w << 16);
-    f[7] = __uint_as_float(v.w & 0xffff0000u);
-}
 
 // Exclusive scan of one int per thread over a block of 1024 threads. `sh` holds 33 ints.
 __device__ __forceinline__ int block_scan_excl(int v, int& total, int* sh) {
@@ -351,58 +323,6 @@ __device__ __forceinline__ float reduce16(float (&v)[16], int lane) {
     return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
 }
 
-// ---- bulk async copies into shared memory, mbarriers, programmatic dependent launch ----
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Waits for a phase of the barrier with an iteration limit; on running out it records PLORA_ERR_TIMEOUT in
-// the status word and returns false, so the kernel can leave instead of hanging.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
-    for (int i = 0; i < (1 << 22); i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    atomicMax(status, PLORA_ERR_TIMEOUT);
-    return false;
-}
-
-// global -> shared bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned), completion
-// counted on `bar`
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
-// Programmatic dependent launch. Every kernel of the path waits for the kernels before it and only then
-// lets the next one start its prologue, so a prologue may read anything written two or more kernels back
-// (slabs, descriptors, the step's grouping) but nothing the kernel right before it writes.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-__device__ __forceinline__ uint4 lds16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
-
 // Shrink over gather work items. Grid (K-splits x row tiles, 1, work items); 128 threads. A work item is up
 // to 16 tokens of one slot, described by one 128-byte record. The block's rows of the slot's stacked A (one
 // K-chunk wide) arrive in shared memory by bulk async copies issued before the dependency wait; the tokens'
@@ -431,13 +351,13 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
         mbar_init(&bars[1], 1);
         mbar_fence_init();
     }
-    if (w >= n_work) return;
+    if (w >= n_work) return pdl_exit_idle();
     TRACE(1);
     const plora_desc& d = table[slot];
     const int rank = d.rank;
     const int split = blockIdx.x / rt_max, rt = blockIdx.x - split * rt_max;
     const int row0 = rt * rps;
-    if (row0 >= rank) return;
+    if (row0 >= rank) return pdl_exit_idle();
     TRACE(2);
     const int rows = min(rps, rank - row0);
     const int k0 = split * kchunk, klen = min(kchunk, K - k0);
@@ -518,14 +438,14 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
     const int slot = work[0], cnt = work[2];
     const int mytok = work[4 + (threadIdx.x & 15)];
     TRACE(0);
-    if (w >= n_work) return;
+    if (w >= n_work) return pdl_exit_idle();
     TRACE(1);
     const plora_desc& d = table[slot];
     const int p = blockIdx.y, r = d.r[p];
-    if (r == 0) return;
+    if (r == 0) return pdl_exit_idle();
     TRACE(2);
     const int rows = d.rows[p], c0 = blockIdx.x * nc;
-    if (c0 >= rows) return;
+    if (c0 >= rows) return pdl_exit_idle();
     const int ncols = min(nc, rows - c0);
     unsigned char* Bs = dsm;
     float* ss = reinterpret_cast<float*>(dsm + bs_bytes);

@@ -1,0 +1,534 @@
+// Tensor-core tile path for long runs of contiguous tokens of one slot (prefill segments): tcgen05.mma with
+// the accumulator in tensor memory, 128 tokens per tile.
+//
+//   plora_shrink_mma_kernel  S[128, R] = X[128, K] . A_slot[R, K]^T   x tiles by TMA (128-byte swizzle), slab tiles
+//                            by 16-byte async copies into the same swizzle, a ring of stages, f32 in TMEM
+//   plora_expand_mma_kernel  y[128, 128-column block] += S[128, r] . B_p[block, r]^T   S split into a bf16 high
+//                            and low part (two accumulating MMAs, so S keeps ~16 bits of mantissa), operands in
+//                            the unswizzled core-matrix layout, y read-modify-written from registers
+//
+// Every wait is bounded (mbar_wait); on a timeout the block records PLORA_ERR_TIMEOUT, frees its tensor
+// memory and leaves. Replaces the reference's mma.sync tiles of 16 tokens (src/kernels/lora.cuh:23-126).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "plora_internal.h"
+#include "plora_device.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+PLORA_TRACE_SETTER(plora_trace_set_mma)
+
+namespace {
+
+// ---- tcgen05 ----
+
+__device__ __forceinline__ bool elect_one() {
+    uint32_t p;
+    asm volatile("{\n.reg .pred e;\nelect.sync _|e, 0xffffffff;\nselp.u32 %0, 1, 0, e;\n}\n" : "=r"(p));
+    return p != 0;
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D (tensor memory) (+)= A (shared) . B (shared), bf16 inputs, f32 accumulate
+__device__ __forceinline__ void umma_bf16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d),
+        "l"(a), "l"(b), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+// arrives on `bar` once this thread's earlier MMAs are complete
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+// 32 consecutive columns of this warp's 32 lanes: v[j] = column (col + j) of lane (32 * (warp % 4) + lane)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor: start address, leading (K direction) and stride (8-row group) byte
+// offsets, descriptor version 1, swizzle mode in bits 61-63 (0 none, 2 = 128 bytes).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo, uint32_t swizzle) {
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46) | ((uint64_t)swizzle << 61);
+}
+
+// Instruction descriptor, kind::f16: f32 accumulator, bf16 A and B, both K-major, M rows by N columns.
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const uint32_t n = valid ? 16u : 0u;  // a zero source size fills the 16 bytes with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// 2-D tiled TMA load (no cluster-wide delivery: this block's shared memory only)
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+
+#define MMA_M 128
+#define EXP_TPAD 66  // floats per row of the epilogue's transpose tile (64 columns + 2 of padding)
+
+// ------------------------------------------------------------------------------------------------------
+// Shrink of one 128-token tile. Grid (1, 1, tiles); 128 threads. K is walked in steps of 64 inputs through a
+// ring of stages; thread 0 issues the x tile by TMA, all threads copy the slab's rows for the same 64
+// inputs into the 128-byte-swizzled layout the MMA reads; one elected thread issues the MMAs; the stage is
+// refilled one step later, after its MMAs have been committed. The f32 result leaves tensor memory one
+// token row per thread.
+#define SHR_KSTEP 64
+#define SHR_X_BYTES (MMA_M * SHR_KSTEP * 2)
+
+__global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_constant__ CUtensorMap xmap, int K,
+                                                                const int* __restrict__ segs, SegLayout lay,
+                                                                const plora_desc* __restrict__ table,
+                                                                float* __restrict__ S, int lds, int nstage,
+                                                                int stage_bytes, int* __restrict__ status) {
+    extern __shared__ unsigned char dsm_raw[];
+    __shared__ __align__(8) uint64_t full[4], done[4], acc_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_fail;
+    const int tile = blockIdx.z;
+    const int n_mma = segs[SEG_N_MMA];
+    const int* mt = segs + lay.mma() + 3 * tile;
+    const int start = mt[0], len = mt[1], slot = mt[2];
+    if (tile >= n_mma) return pdl_exit_idle();
+    const plora_desc& d = table[slot];
+    const int R = d.rank;
+    if (R == 0) return pdl_exit_idle();
+    const bf16* A = reinterpret_cast<const bf16*>(d.a);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    // 1024-byte aligned stage ring: [x tile 16 KB][slab rows R x 128 B]
+    unsigned char* ring = dsm_raw + ((1024u - (smem_u32(dsm_raw) & 1023u)) & 1023u);
+    const uint32_t ncols = R <= 32 ? 32u : R <= 64 ? 64u : R <= 128 ? 128u : R <= 256 ? 256u : 512u;
+    if (tid == 0) {
+        for (int i = 0; i < nstage; i++) {
+            mbar_init(&full[i], 1);
+            mbar_init(&done[i], 1);
+        }
+        mbar_init(&acc_bar, 1);
+        mbar_fence_init();
+        s_fail = 0;
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, ncols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const int nk = (K + SHR_KSTEP - 1) / SHR_KSTEP;
+    const int chunks = R * 8;  // 16-byte chunks of the slab per step
+    pdl_wait();  // x comes from the kernels before
+    pdl_trigger();
+
+    auto issue = [&](int ks) {
+        const int st = ks % nstage;
+        unsigned char* xs = ring + (size_t)st * stage_bytes;
+        unsigned char* as = xs + SHR_X_BYTES;
+        const int k0 = ks * SHR_KSTEP;
+        if (tid == 0) {
+            mbar_expect_tx(&full[st], SHR_X_BYTES);
+            tma_load_2d(xs, &xmap, k0, start, &full[st]);
+        }
+        for (int c = tid; c < chunks; c += 128) {
+            const int n = c >> 3, q = c & 7;
+            const int k = k0 + q * 8;
+            cp_async16(as + n * 128 + ((q ^ (n & 7)) << 4), A + (size_t)n * K + (k < K ? k : 0), k < K);
+        }
+    };
+
+    for (int ks = 0; ks < nstage; ks++) {
+        if (ks < nk) issue(ks);
+        cp_async_commit();
+    }
+    const uint32_t idesc_lo = umma_idesc_bf16(MMA_M, R > 256 ? 256 : R);
+    const uint32_t idesc_hi = umma_idesc_bf16(MMA_M, R > 256 ? R - 256 : 16);
+    bool ok = true;
+    for (int it = 0; it < nk; it++) {
+        const int st = it % nstage;
+        // the copies of this step's slab rows sit at most nstage - 2 groups back
+        if (nstage >= 4) cp_async_wait<2>();
+        else if (nstage == 3) cp_async_wait<1>();
+        else cp_async_wait<0>();
+        fence_async_smem();
+        __syncthreads();
+        if (warp == 0) {
+            if (elect_one()) {
+                if (mbar_wait(&full[st], (it / nstage) & 1, status)) {
+                    tc_fence_after();
+                    const uint32_t xs = smem_u32(ring + (size_t)st * stage_bytes);
+                    const uint32_t as = xs + SHR_X_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < SHR_KSTEP / 16; kk++) {
+                        const uint64_t da = umma_desc(xs + kk * 32, 16, 1024, 2);
+                        const uint64_t db = umma_desc(as + kk * 32, 16, 1024, 2);
+                        umma_bf16(tmem, da, db, idesc_lo, (it | kk) != 0);
+                        if (R > 256) {
+                            const uint64_t db2 = umma_desc(as + 256 * 128 + kk * 32, 16, 1024, 2);
+                            umma_bf16(tmem + 256, da, db2, idesc_hi, (it | kk) != 0);
+                        }
+                    }
+                    umma_commit(&done[st]);
+                    if (it == nk - 1) umma_commit(&acc_bar);
+                } else {
+                    s_fail = 1;
+                }
+            }
+            __syncwarp();
+        }
+        // refill the stage used one step ago, now that its MMAs had a whole step to finish
+        if (it >= 1 && it - 1 + nstage < nk) {
+            const int pst = (it - 1) % nstage;
+            ok = mbar_wait(&done[pst], ((it - 1) / nstage) & 1, status);
+            if (ok) issue(it - 1 + nstage);
+        }
+        cp_async_commit();
+        if (!ok) break;
+    }
+    if (ok) ok = mbar_wait(&acc_bar, 0, status);
+    __syncthreads();
+    if (ok && !s_fail) {
+        tc_fence_after();
+        const int row = tid;
+        float* out = S + (size_t)(start + row) * lds;
+        for (int c = 0; c < R; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
+            if (row < len) {
+#pragma unroll
+                for (int q = 0; q < 32; q += 4)
+                    if (c + q < R)
+                        *reinterpret_cast<float4*>(out + c + q) =
+                            make_float4(__uint_as_float(v[q]), __uint_as_float(v[q + 1]), __uint_as_float(v[q + 2]),
+                                        __uint_as_float(v[q + 3]));
+            }
+        }
+    }
+    cp_async_wait<0>();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, ncols);
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Expand of one 128-token tile over `nb_per_cta` blocks of 128 output columns of one part. Grid (column
+// groups, parts, tiles); 128 threads, thread t owns token row t. Operand layout: 8 x 16-byte core matrices,
+// K direction 128 bytes apart, 8-row groups r * 16 bytes apart.
+// 32 row segments of this lane's two columns, all requested before any is used
+__device__ __forceinline__ void load_rows_bf16(uint32_t (&raw)[32], const bf16* y, int ldy, int nrows, bool colok) {
+#pragma unroll
+    for (int rr = 0; rr < 32; rr++)
+        if (colok && rr < nrows) raw[rr] = *reinterpret_cast<const uint32_t*>(y + (size_t)rr * ldy);
+}
+__device__ __forceinline__ void load_rows_f32(float2 (&raw)[32], const float* y, int ldy, int nrows, bool colok) {
+#pragma unroll
+    for (int rr = 0; rr < 32; rr++)
+        if (colok && rr < nrows) raw[rr] = *reinterpret_cast<const float2*>(y + (size_t)rr * ldy);
+}
+
+template <bool F32>
+__global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __restrict__ S, int lds,
+                                                                const int* __restrict__ segs, SegLayout lay,
+                                                                const plora_desc* __restrict__ table, void* Y,
+                                                                int ldy, int nb_per_cta, int op_bytes,
+                                                                int* __restrict__ status) {
+    extern __shared__ __align__(128) unsigned char dsm[];
+    __shared__ __align__(8) uint64_t done;
+    __shared__ uint32_t tmem_slot;
+    const int tile = blockIdx.z;
+    const int n_mma = segs[SEG_N_MMA];
+    const int* mt = segs + lay.mma() + 3 * tile;
+    const int start = mt[0], len = mt[1], slot = mt[2];
+    if (tile >= n_mma) return pdl_exit_idle();
+    const plora_desc& d = table[slot];
+    const int p = blockIdx.y, r = d.r[p];
+    if (r == 0) return pdl_exit_idle();
+    const int rows = d.rows[p];
+    const int cb0 = blockIdx.x * nb_per_cta;
+    if (cb0 * 128 >= rows) return pdl_exit_idle();
+    const int nblk = min(nb_per_cta, (rows - cb0 * 128 + 127) / 128);
+    TRACE(0);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    unsigned char* Ahi = dsm;
+    unsigned char* Alo = dsm + op_bytes;
+    unsigned char* Bs[2] = {dsm + 2 * (size_t)op_bytes, dsm + 3 * (size_t)op_bytes};
+    const bf16* B = reinterpret_cast<const bf16*>(d.b[p]);
+    const uint32_t sbo = (uint32_t)r * 16u;  // 8-row group stride
+    const int P = r >> 3;
+
+    auto load_b = [&](int cb, unsigned char* dst) {
+        const int n = tid;  // row of B = output column of the block
+        const bool valid = cb * 128 + n < rows;
+        const bf16* src = B + (size_t)(valid ? cb * 128 + n : 0) * r;
+        unsigned char* drow = dst + (size_t)(n >> 3) * sbo + (n & 7) * 16;
+        for (int j = 0; j < P; j++) cp_async16(drow + j * 128, src + j * 8, valid);
+    };
+
+    if (tid == 0) {
+        mbar_init(&done, 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 128);
+    load_b(cb0, Bs[0]);  // B is a slab: it may be fetched before the kernels ahead have finished
+    cp_async_commit();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    pdl_wait();
+    TRACE(1);
+    pdl_trigger();
+
+    // this thread's token row of S, split into a bf16 high part and the bf16 of what is left
+    {
+        const int row = tid;
+        const bool valid = row < len;
+        const float* sp = S + (size_t)(start + (valid ? row : 0)) * lds + d.r_off[p];
+        unsigned char* ahi = Ahi + (size_t)(row >> 3) * sbo + (row & 7) * 16;
+        unsigned char* alo = Alo + (size_t)(row >> 3) * sbo + (row & 7) * 16;
+        for (int j = 0; j < P; j++) {
+            float f[8];
+            if (valid) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(sp + j * 8));
+                const float4 b = __ldcg(reinterpret_cast<const float4*>(sp + j * 8 + 4));
+                f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; e++) f[e] = 0.f;
+            }
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+                const float2 hf = __bfloat1622float2(h);
+                const __nv_bfloat162 l = __floats2bfloat162_rn(f[2 * e] - hf.x, f[2 * e + 1] - hf.y);
+                hi[e] = *reinterpret_cast<const uint32_t*>(&h);
+                lo[e] = *reinterpret_cast<const uint32_t*>(&l);
+            }
+            *reinterpret_cast<uint4*>(ahi + j * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4*>(alo + j * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+    }
+    const uint32_t idesc = umma_idesc_bf16(MMA_M, 128);
+    TRACE(2);
+    const int lane = tid & 31;
+    // Epilogue layout: the accumulator leaves tensor memory one token row per thread, is transposed through a
+    // warp-private shared-memory tile, and meets y with one 128-byte (bf16) or 256-byte (f32) row segment per
+    // warp instruction: lane l owns columns 2l and 2l+1 of a 64-column chunk for each of the warp's 32 rows.
+    float* T = reinterpret_cast<float*>(dsm + 4 * (size_t)op_bytes) + (size_t)warp * 32 * EXP_TPAD;
+    const int wrow0 = warp * 32;
+    const int nrows = max(0, min(32, len - wrow0));  // live rows of this warp
+    const size_t ybase = (size_t)(start + wrow0) * ldy + d.off[p] + 2 * lane;
+    bool ok = true;
+    for (int nb = 0; nb < nblk; nb++) {
+        const int cb = cb0 + nb;
+        if (nb + 1 < nblk) load_b(cb + 1, Bs[(nb + 1) & 1]);
+        cp_async_commit();
+        cp_async_wait<1>();  // everything but the block just requested has landed
+        fence_async_smem();
+        __syncthreads();
+        if (nb == 0) TRACE(3);
+        if (warp == 0) {
+            if (elect_one()) {
+                tc_fence_after();
+                const uint32_t a_hi = smem_u32(Ahi), a_lo = smem_u32(Alo), b = smem_u32(Bs[nb & 1]);
+                for (int kk = 0; kk < r / 16; kk++)
+                    umma_bf16(tmem, umma_desc(a_hi + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc,
+                              kk != 0);
+                for (int kk = 0; kk < r / 16; kk++)
+                    umma_bf16(tmem, umma_desc(a_lo + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, 1);
+                umma_commit(&done);
+            }
+            __syncwarp();
+        }
+        const int ncols = min(128, rows - cb * 128);
+        // y is requested before the MMAs are waited for, as raw words so that all of a chunk's 32 row
+        // segments are in flight together: both 64-column chunks for bf16, the first one for f32
+        const size_t yblk = ybase + (size_t)cb * 128;
+        uint32_t yb0[32], yb1[32];
+        float2 yf[32];
+        if (nb == 0) TRACE(4);
+        if (F32) {
+            load_rows_f32(yf, reinterpret_cast<const float*>(Y) + yblk, ldy, nrows, 2 * lane < ncols);
+        } else {
+            load_rows_bf16(yb0, reinterpret_cast<const bf16*>(Y) + yblk, ldy, nrows, 2 * lane < ncols);
+            load_rows_bf16(yb1, reinterpret_cast<const bf16*>(Y) + yblk + 64, ldy, nrows, 64 + 2 * lane < ncols);
+        }
+        if (nb == 0) TRACE(8);
+        ok = mbar_wait(&done, nb & 1, status);
+        if (nb == 0) TRACE(9);
+        if (!__syncthreads_and(ok)) {
+            ok = false;
+            break;
+        }
+        if (nb == 0) TRACE(5);
+        tc_fence_after();
+#pragma unroll
+        for (int ch = 0; ch < 2; ch++) {
+            if (ch * 64 >= ncols) break;
+            {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)wrow0 << 16) + ch * 64, v);
+#pragma unroll
+                for (int q = 0; q < 32; q++) T[lane * EXP_TPAD + q] = __uint_as_float(v[q]);
+                tmem_ld32(tmem + ((uint32_t)wrow0 << 16) + ch * 64 + 32, v);
+#pragma unroll
+                for (int q = 0; q < 32; q++) T[lane * EXP_TPAD + 32 + q] = __uint_as_float(v[q]);
+            }
+            __syncwarp();
+            const bool colok = ch * 64 + 2 * lane < ncols;
+            if (F32) {
+                if (ch == 1) load_rows_f32(yf, reinterpret_cast<const float*>(Y) + yblk + 64, ldy, nrows, colok);
+                float* yo = reinterpret_cast<float*>(Y) + yblk + ch * 64;
+#pragma unroll
+                for (int rr = 0; rr < 32; rr++) {
+                    if (colok && rr < nrows) {
+                        const float2 a = *reinterpret_cast<const float2*>(T + rr * EXP_TPAD + 2 * lane);
+                        *reinterpret_cast<float2*>(yo + (size_t)rr * ldy) = make_float2(yf[rr].x + a.x, yf[rr].y + a.y);
+                    }
+                }
+            } else {
+                bf16* yo = reinterpret_cast<bf16*>(Y) + yblk + ch * 64;
+#pragma unroll
+                for (int rr = 0; rr < 32; rr++) {
+                    if (colok && rr < nrows) {
+                        const float2 a = *reinterpret_cast<const float2*>(T + rr * EXP_TPAD + 2 * lane);
+                        const uint32_t raw = ch == 0 ? yb0[rr] : yb1[rr];
+                        const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw));
+                        *reinterpret_cast<__nv_bfloat162*>(yo + (size_t)rr * ldy) = __floats2bfloat162_rn(y.x + a.x, y.y + a.y);
+                    }
+                }
+            }
+            __syncwarp();
+        }
+        tc_fence_before();
+        __syncthreads();  // the accumulator and this B buffer are free again
+        if (nb == 0) TRACE(6);
+    }
+    cp_async_wait<0>();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 128);
+    TRACE(7);
+}
+
+// cuTensorMapEncodeTiled, fetched from the driver once (no link-time dependency on libcuda)
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+encode_tiled_fn g_encode = nullptr;
+
+}  // namespace
+
+cudaError_t plora_mma_init() {
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess) return e;
+        if (!fn || q != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
+        g_encode = reinterpret_cast<encode_tiled_fn>(fn);
+    }
+    cudaError_t e = cudaFuncSetAttribute(plora_shrink_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(plora_expand_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 172 * 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(plora_expand_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 172 * 1024);
+}
+
+namespace {
+template <typename... Params, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                       Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
+}
+}  // namespace
+
+cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, const int32_t* segs, SegLayout lay,
+                                    const plora_desc* table, float* S, int lds, int max_rank_total, int tile_cap,
+                                    int* status, bool pdl, cudaStream_t st) {
+    if (!g_encode) return cudaErrorNotSupported;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+    const cuuint32_t box[2] = {SHR_KSTEP, MMA_M};
+    const cuuint32_t es[2] = {1, 1};
+    if (g_encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, es,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    const int stage_bytes = SHR_X_BYTES + ((max_rank_total * 128 + 1023) / 1024) * 1024;
+    int nstage = (190 * 1024) / stage_bytes;
+    nstage = nstage > 4 ? 4 : nstage;
+    if (nstage < 2) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)nstage * stage_bytes + 1024;
+    return launch_pdl(plora_shrink_mma_kernel, dim3(1, 1, (unsigned)tile_cap), dim3(128), smem, st, pdl, map, K, segs, lay,
+                      table, S, lds, nstage, stage_bytes, status);
+}
+
+cudaError_t plora_launch_expand_mma(const float* S, int lds, const int32_t* segs, SegLayout lay,
+                                    const plora_desc* table, void* y, int ldy, int f32_out, int parts, int max_rows,
+                                    int tile_cap, int* status, bool pdl, cudaStream_t st) {
+    const int max_rank = lds / PLORA_MAX_PARTS;
+    const int op_bytes = MMA_M * max_rank * 2;
+    const int nblocks = (max_rows + 127) / 128;
+    // each block walks up to 8 column blocks with one staging of its S tile
+    const int nb_per_cta = nblocks < 8 ? nblocks : 8;
+    dim3 grid((unsigned)((nblocks + nb_per_cta - 1) / nb_per_cta), (unsigned)parts, (unsigned)tile_cap);
+    // at least 48 KB of shared memory per block: no more than four blocks, 128 tensor-memory columns each,
+    // share an SM's 512 columns
+    size_t smem = (size_t)4 * op_bytes + (size_t)4 * 32 * EXP_TPAD * sizeof(float);
+    if (smem < 48 * 1024) smem = 48 * 1024;
+    if (f32_out)
+        return launch_pdl(plora_expand_mma_kernel<true>, grid, dim3(128), smem, st, pdl, S, lds, segs, lay, table, y, ldy,
+                          nb_per_cta, op_bytes, status);
+    return launch_pdl(plora_expand_mma_kernel<false>, grid, dim3(128), smem, st, pdl, S, lds, segs, lay, table, y, ldy,
+                      nb_per_cta, op_bytes, status);
+}

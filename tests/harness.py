@@ -130,9 +130,11 @@ def bf16_ulp_diff(a, b, pe, floor=2.0 ** -20):
     return d
 
 
-def run_and_check(pe, wl, device=0, f32_out=True, meta="host"):
+def run_and_check(pe, wl, device=0, f32_out=True, meta="host", run_min=None):
     table, _ = oracle_registry(wl)
     loras = product_registry(pe, wl, device)
+    if run_min is not None:
+        loras.set_run_min(run_min)  # runs at least this long take the tensor-core tile kernels
     tiles = tiles_of(pe, wl)
     ys = run_gpu(pe, loras, wl, f32_out, meta=meta, device=device)
     res = {}
@@ -144,10 +146,17 @@ def run_and_check(pe, wl, device=0, f32_out=True, meta="host"):
             res[si] = (mx, mn)
     else:
         yr = oracle_rounded(wl, table, tiles, False, pe)
+        # The tile path feeds S to the tensor cores as a bf16 high part plus a bf16 low part (about 16 bits of
+        # mantissa instead of f32's 24) and the tensor cores' f32 accumulation over thousands of inputs is not
+        # correctly rounded, so its y may sit about 1e-5 (of RMS(y) ~ 1) away from the rounded oracle: still a
+        # thousand times inside the stated tolerance, but enough to move a value that lies within 1e-5 of a
+        # bf16 rounding boundary (about 2 * 1e-5 / 2^-8 = 0.5% of the elements) to the neighbouring bf16.
+        tile = run_min is not None and run_min < (1 << 30)
+        floor, max_frac = (3e-5, 1e-2) if tile else (2.0 ** -20, 2e-3)
         for si, (y, r) in enumerate(zip(ys, yr)):
-            ulp = bf16_ulp_diff(y, r, pe)
+            ulp = bf16_ulp_diff(y, r, pe, floor)
             frac = float((ulp > 0).mean())
-            assert ulp.max() <= 1 and frac < 2e-3, (wl.name, si, int(ulp.max()), frac)
+            assert ulp.max() <= 1 and frac < max_frac, (wl.name, si, int(ulp.max()), frac)
             res[si] = (int(ulp.max()), frac)
     loras.close()
     return res

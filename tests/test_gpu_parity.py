@@ -55,6 +55,7 @@ def test_grouping_is_a_stable_sort_by_slot(pe):
     rng = np.random.default_rng(22)
     sites = [pe.Site.fused(0, 64, [("q", 32)])]
     loras = pe.Loras(sites, 9, 16, 4096, 1500, device=0)
+    loras.set_run_min(1 << 30)  # everything through the gather grouping
     for trial in range(25):
         n = int(rng.integers(1, 1400 if trial % 8 == 0 else 70))
         rows = rng.choice([1, 1, 1, 3, 16, 17, 40], n).astype(np.int32)
@@ -188,15 +189,40 @@ def test_reference_kernels_agree(pe, wls, oracle):
         refb = harness.run_reference_kernels(pe, loras, wl, False)
         emb = harness.oracle_rounded(wl, table, tiles, False, pe, mode="emul")
         for si in range(len(wl.sites)):
-            ulp = harness.bf16_ulp_diff(refb[si], emb[si], pe)
+            # the reference's float atomics can round an S value to the other bf16 neighbour than the oracle's
+            # fp64 sum does; that moves y by up to ~5e-4 (of RMS 1), many bf16 steps when y is next to zero
+            ulp = harness.bf16_ulp_diff(refb[si], emb[si], pe, floor=5e-4)
             assert ulp.max() <= 1 and (ulp > 0).mean() < 5e-3, (wl.name, si, int(ulp.max()), float((ulp > 0).mean()))
         loras.close()
 
 
 def test_prefill_segments_reduced(pe, wls):
     wl = wls.config3(seqs=3, seq_len=160, rank=64)
-    harness.run_and_check(pe, wl, f32_out=True, meta="device")
-    harness.run_and_check(pe, wl, f32_out=False, meta="device")
+    for run_min in (64, 1 << 30):  # through the tensor-core tile kernels, and through the gather kernels alone
+        harness.run_and_check(pe, wl, f32_out=True, meta="device", run_min=run_min)
+        harness.run_and_check(pe, wl, f32_out=False, meta="device", run_min=run_min)
+
+
+TILE_CASES = [
+    # name, rows per sequence, slot per sequence, ranks, K, parts
+    ("three-prompts-r64", [160, 160, 160], [1, 2, 3], [64, 64, 64], 4096, [("a", 1024), ("b", 256)]),
+    ("ragged-lengths-r16", [64, 65, 127, 129, 300, 5, 1], [1, 2, 1, 3, 2, 3, 1], [16, 16, 16], 512, [("a", 384)]),
+    ("decode-then-prompts-r32", [1] * 20 + [128, 128], list(range(1, 5)) * 5 + [2, 3], [32] * 4, 5120,
+     [("q", 768)]),
+    ("odd-k-odd-width-r128", [200, 70], [1, 2], [128, 8], 1096, [("a", 1000), ("b", 130), ("c", 2)]),
+    ("wide-rank-total", [256], [1], [128], 256, [("a", 128), ("b", 128), ("c", 128), ("d", 128)]),
+]
+
+
+@pytest.mark.parametrize("case", TILE_CASES, ids=[c[0] for c in TILE_CASES])
+def test_tensor_core_tile_path(pe, wls, case):
+    """Runs of 64 or more contiguous tokens of one slot go through the tcgen05 kernels; everything else in the
+    same step through the gather kernels."""
+    name, rows, slots, ranks, K, mods = case
+    sites = [pe.Site.fused(0, K, mods)]
+    wl = wls.Workload(name, sites, ranks, 1.0, rows, slots, 7)
+    for f32_out in (True, False):
+        harness.run_and_check(pe, wl, f32_out=f32_out, meta="device", run_min=64)
 
 
 def test_heterogeneous_ranks_reduced(pe, wls):
