@@ -205,6 +205,23 @@ int plora_shrink(plora_t* h, const plora_hook* hook, const plora_step* step, uin
  * of f32(y)+acc) or f32 in place. */
 int plora_expand(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
                  int f32_out, void* stream);
+/* FP8 layer with the adapter expand fused into its epilogue (builder-defined layout: e4m3 activations with one
+ * f32 scale per token, e4m3 weights [width, cols] with one f32 scale per output channel). The engine's own FP8
+ * layers go through cuBLASLt and are followed by lora_expand as a separate pass over y
+ * (src/linear.rs:428-849, src/gpu.rs:1183-1277); here y is written once:
+ *   y[t, n] = st[t] * sn[n] * sum_k xq[t,k] * wq[n,k]  +  the adapter term of token t's slot.
+ * Call plora_shrink on the bf16 activations first (as Linear::forward does: src/linear.rs:440-443). */
+int plora_fp8_quant_rows(plora_t* h, uint64_t x, int rows, int cols, uint64_t xq, uint64_t st, void* stream);
+int plora_linear_fp8_fused(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t xq, uint64_t st,
+                           uint64_t wq, uint64_t sn, int rows, uint64_t y, int ldy, int f32_out, void* stream);
+
+/* Tensor-parallel row-parallel layers (no counterpart in the single-GPU engine): plora_s_reduce adds the
+ * shrink's K-split partials into plane 0 of S ([max_tokens, lds] f32 at plora_s_ptr), the caller all-reduces
+ * the first `rows` rows of that plane over its ranks, and plora_expand_reduced expands from plane 0 alone. */
+int plora_s_reduce(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, void* stream);
+int plora_expand_reduced(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
+                         int f32_out, void* stream);
+
 /* Gpu::fork / Gpu::join (src/gpu.rs:849-901): order `side` after `main`, and `main` after `side`. */
 int plora_fork(plora_t* h, void* main_stream, void* side_stream);
 int plora_join(plora_t* h, void* main_stream, void* side_stream);

@@ -232,3 +232,22 @@ class Slots:
         ids = (C.c_uint32 * cap)()
         n = lib().po_slots_take_loads(self._s, sl, ids, cap)
         return [(sl[i], ids[i]) for i in range(n)]
+
+
+def fp8_quant_rows(x_bits):
+    """Per-token quantisation: returns (xq uint8 [T, K], st float32 [T])."""
+    T, K = x_bits.shape
+    xq = np.zeros((T, K), np.uint8)
+    st = np.zeros(T, np.float32)
+    lib().po_fp8_quant_rows(_p(x_bits, C.c_uint16), K, T, K, _p(xq, C.c_uint8), _p(st, C.c_float))
+    return xq, st
+
+
+def fp8_base_f64(xq, st, wq, sn, threads=0):
+    """Y64[t, n] = st[t] * sn[n] * sum_k e4m3(xq[t,k]) * e4m3(wq[n,k])."""
+    T, K = xq.shape
+    N = wq.shape[0]
+    y = np.zeros((T, N), np.float64)
+    lib().po_fp8_base_f64(_p(xq, C.c_uint8), _p(st, C.c_float), _p(wq, C.c_uint8), _p(sn, C.c_float), T, K, N,
+                          _p(y, C.c_double), N, threads)
+    return y

@@ -120,6 +120,11 @@ SYMBOLS = {
     "plora_tiles_ptr": (_U64, [_P]),
     "plora_shrink": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _U64, _I, _P]),
     "plora_expand": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _U64, _I, _I, _P]),
+    "plora_fp8_quant_rows": (_I, [_P, _U64, _I, _I, _U64, _U64, _P]),
+    "plora_linear_fp8_fused": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _U64, _U64, _U64, _U64, _I, _U64, _I, _I,
+                                    _P]),
+    "plora_s_reduce": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _P]),
+    "plora_expand_reduced": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _U64, _I, _I, _P]),
     "plora_fork": (_I, [_P, _P, _P]),
     "plora_join": (_I, [_P, _P, _P]),
     "plora_set_run_min": (_I, [_P, _I]),
@@ -412,6 +417,24 @@ class Loras:
 
     def expand(self, hook, step, rows, y, ldy, f32_out=False, stream=0):  # src/linear.rs:889-921
         self._check(lib.plora_expand(self._h, C.byref(hook), C.byref(step), rows, y, ldy, int(f32_out), _P(stream)))
+
+    def fp8_quant_rows(self, x, rows, cols, xq, st, stream=0):
+        """Per-token e4m3 quantisation of bf16 activations: st[t] = amax_t / 448, xq = e4m3(x / st)."""
+        self._check(lib.plora_fp8_quant_rows(self._h, x, rows, cols, xq, st, _P(stream)))
+
+    def linear_fp8_fused(self, hook, step, xq, st, wq, sn, rows, y, ldy, f32_out=False, stream=0):
+        """FP8 base layer + adapter expand in one kernel; plora_shrink on the bf16 activations goes first."""
+        self._check(lib.plora_linear_fp8_fused(self._h, C.byref(hook), C.byref(step), xq, st, wq, sn, rows, y, ldy,
+                                               int(f32_out), _P(stream)))
+
+    def s_reduce(self, hook, step, rows, stream=0):
+        """Adds the shrink's K-split partials into plane 0 of S (before a tensor-parallel all-reduce)."""
+        self._check(lib.plora_s_reduce(self._h, C.byref(hook), C.byref(step), rows, _P(stream)))
+
+    def expand_reduced(self, hook, step, rows, y, ldy, f32_out=False, stream=0):
+        """expand() from plane 0 of S alone (after s_reduce and the all-reduce)."""
+        self._check(lib.plora_expand_reduced(self._h, C.byref(hook), C.byref(step), rows, y, ldy, int(f32_out),
+                                             _P(stream)))
 
     def fork(self, main=0, side=0):  # src/gpu.rs:849-858
         self._check(lib.plora_fork(self._h, _P(main), _P(side)))

@@ -1,0 +1,450 @@
+// FP8 base layer with the adapter expand fused into its epilogue.
+//
+//   y[t, n] = s_t[t] * s_n[n] * sum_k e4m3(xq[t,k]) * e4m3(wq[n,k])  +  sum_j S[t, r_off_p + j] * B_slot(t),p[n - off_p, j]
+//
+// xq: per-token dynamically scaled activations, wq: per-output-channel scaled weights, both e4m3. The
+// reference runs its FP8 layers through cuBLASLt (block-scaled layouts) and then lora_expand as a separate
+// kernel that reads y back (src/linear.rs:428-849, src/kernels/lora.cuh:74-126); here y is written once.
+//
+//   plora_fp8_quant_rows_kernel  x (bf16) -> xq, s_t = amax_t / 448
+//   plora_s_reduce_kernel        adds the shrink's K-split partials of the gather tokens into plane 0
+//   plora_fp8_fused_kernel       128 tokens x 64 output columns per block: a TMA-fed ring of (x, W) stages,
+//                                tcgen05.mma kind::f8f6f4 into tensor memory; meanwhile four warps build the
+//                                adapter term for the tile on CUDA cores (tokens of the tile grouped by slot,
+//                                every slot's rows of B streamed once through a ring of async copies); the
+//                                same warps then scale the accumulator, add the adapter term and store y
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include "plora_internal.h"
+#include "plora_device.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+__device__ __forceinline__ bool elect_one() {
+    uint32_t p;
+    asm volatile("{\n.reg .pred e;\nelect.sync _|e, 0xffffffff;\nselp.u32 %0, 1, 0, e;\n}\n" : "=r"(p));
+    return p != 0;
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D (tensor memory) (+)= A (shared) . B (shared), 8-bit float inputs, f32 accumulate
+__device__ __forceinline__ void umma_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(d),
+        "l"(a), "l"(b), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// K-major operand in 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// barrier among the 128 threads of the four adapter/epilogue warps only
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------------------
+// Per-token dynamic quantisation: s_t = amax / 448 (1 for an all-zero row), xq = e4m3_satfinite(x / s_t).
+// One block per token row.
+__global__ void __launch_bounds__(256) plora_fp8_quant_rows_kernel(const bf16* __restrict__ X, int ldx, int K,
+                                                                    uint8_t* __restrict__ Xq, float* __restrict__ st) {
+    __shared__ float red[8];
+    const int t = blockIdx.x;
+    const bf16* x = X + (size_t)t * ldx;
+    float amax = 0.f;
+    for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(x + k), f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(f[e]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
+    const float s = amax > 0.f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+    if (threadIdx.x == 0) st[t] = s;
+    uint8_t* q = Xq + (size_t)t * K;
+    for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(x + k), f);
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            lo |= (uint32_t)__nv_cvt_float_to_fp8(__fdiv_rn(f[e], s), __NV_SATFINITE, __NV_E4M3) << (8 * e);
+            hi |= (uint32_t)__nv_cvt_float_to_fp8(__fdiv_rn(f[4 + e], s), __NV_SATFINITE, __NV_E4M3) << (8 * e);
+        }
+        *reinterpret_cast<uint2*>(q + k) = make_uint2(lo, hi);
+    }
+}
+
+// Adds the K-split partial planes of every gather token into plane 0, in split order. Grid (work items).
+__global__ void __launch_bounds__(128) plora_s_reduce_kernel(float* __restrict__ S, size_t s_stride, int lds, int nsplit,
+                                                              const int* __restrict__ segs, SegLayout lay,
+                                                              const plora_desc* __restrict__ table) {
+    const int w = blockIdx.x;
+    const int n_work = segs[SEG_N_WORK];
+    const int* work = segs + lay.work() + PLORA_WORK_WORDS * w;
+    if (w >= n_work) return pdl_exit_idle();
+    const int slot = work[0], cnt = work[2];
+    const int rank = table[slot].rank;
+    pdl_wait();
+    pdl_trigger();
+    for (int i = threadIdx.x; i < cnt * rank; i += 128) {
+        const int t = i / rank, j = i - t * rank;
+        float* sp = S + (size_t)work[4 + t] * lds + j;
+        float acc = sp[0];
+        for (int s = 1; s < nsplit; s++) acc += __ldcg(sp + (size_t)s * s_stride);
+        sp[0] = acc;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+#define F8_BM 128
+#define F8_BN 64
+#define F8_BK 128  // bytes = e4m3 elements per stage row
+#define F8_STAGES 3
+#define F8_STAGE_BYTES (F8_BM * F8_BK + F8_BN * F8_BK)
+#define F8_DPITCH (F8_BN + 1)  // floats per row of the adapter-term tile
+#define F8_RING 3              // slots' rows of B in flight
+
+struct Fp8Parts {
+    int n;
+    int off[PLORA_MAX_PARTS];
+    int rows[PLORA_MAX_PARTS];
+};
+
+template <bool F32>
+__global__ void __launch_bounds__(192) plora_fp8_fused_kernel(const __grid_constant__ CUtensorMap xmap,
+                                                               const __grid_constant__ CUtensorMap wmap,
+                                                               const float* __restrict__ st,
+                                                               const float* __restrict__ sn, int T, int N, int K,
+                                                               const int* __restrict__ segs, SegLayout lay,
+                                                               const plora_desc* __restrict__ table, Fp8Parts parts,
+                                                               const float* __restrict__ S, int lds, void* Y, int ldy,
+                                                               int bpitch, int* __restrict__ status) {
+    extern __shared__ unsigned char dsm_raw[];
+    __shared__ __align__(8) uint64_t full[F8_STAGES], empty[F8_STAGES], acc_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_slot[F8_BM], o_row[F8_BM], o_slot[F8_BM], g_start[F8_BM + 1];
+    __shared__ int s_ngroups;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * F8_BN, m0 = blockIdx.y * F8_BM;
+    unsigned char* ring = dsm_raw + ((1024u - (smem_u32(dsm_raw) & 1023u)) & 1023u);
+    float* delta = reinterpret_cast<float*>(ring + F8_STAGES * F8_STAGE_BYTES);
+    unsigned char* bring = reinterpret_cast<unsigned char*>(delta + F8_BM * F8_DPITCH);
+    if (tid == 0) {
+        for (int i = 0; i < F8_STAGES; i++) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        mbar_init(&acc_bar, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(&tmem_slot, F8_BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const int nk = (K + F8_BK - 1) / F8_BK;
+    pdl_wait();  // S, xq and the scales come from the kernels before
+    pdl_trigger();
+
+    if (warp == 0) {
+        // ---- producer: one lane feeds the ring with TMA
+        if (lane == 0) {
+            for (int ks = 0; ks < nk; ks++) {
+                const int stg = ks % F8_STAGES;
+                if (ks >= F8_STAGES && !mbar_wait(&empty[stg], ((ks / F8_STAGES) - 1) & 1, status)) break;
+                unsigned char* xs = ring + (size_t)stg * F8_STAGE_BYTES;
+                mbar_expect_tx(&full[stg], F8_STAGE_BYTES);
+                tma_load_2d(xs, &xmap, ks * F8_BK, m0, &full[stg]);
+                tma_load_2d(xs + F8_BM * F8_BK, &wmap, ks * F8_BK, n0, &full[stg]);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (elect_one()) {
+            // kind::f8f6f4: f32 accumulator, e4m3 A and B (format 0), K-major, M 128, N 64
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(F8_BN >> 3) << 17) | ((uint32_t)(F8_BM >> 4) << 24);
+            for (int ks = 0; ks < nk; ks++) {
+                const int stg = ks % F8_STAGES;
+                if (!mbar_wait(&full[stg], (ks / F8_STAGES) & 1, status)) break;
+                tc_fence_after();
+                const uint32_t xs = smem_u32(ring + (size_t)stg * F8_STAGE_BYTES);
+                const uint32_t ws = xs + F8_BM * F8_BK;
+#pragma unroll
+                for (int kk = 0; kk < F8_BK / 32; kk++)
+                    umma_f8(tmem, umma_desc_sw128(xs + kk * 32), umma_desc_sw128(ws + kk * 32), idesc, (ks | kk) != 0);
+                umma_commit(&empty[stg]);
+            }
+            umma_commit(&acc_bar);
+        }
+        __syncwarp();
+    } else {
+        // ---- adapter term of the tile, then the epilogue (threads 0..127 of this group)
+        const int et = tid - 64;
+        const int row = m0 + et;
+        // tokens of the tile sorted by slot (stable); slot 0 (no adapter) and rows past T first
+        const int myslot = row < T ? segs[lay.tslot() + row] : 0;
+        s_slot[et] = myslot;
+        for (int i = et; i < F8_BM * F8_DPITCH; i += 128) delta[i] = 0.f;
+        epi_sync();
+        int rank = 0;
+        for (int j = 0; j < F8_BM; j++) {
+            const int sj = s_slot[j];
+            rank += (sj < myslot) || (sj == myslot && j < et);
+        }
+        o_row[rank] = et;
+        o_slot[rank] = myslot;
+        epi_sync();
+        const bool head = o_slot[et] != 0 && (et == 0 || o_slot[et - 1] != o_slot[et]);
+        // group starts, in order (a serial scan by one thread: at most 128 entries)
+        if (et == 0) {
+            int g = 0;
+            for (int i = 0; i < F8_BM; i++)
+                if (o_slot[i] != 0 && (i == 0 || o_slot[i - 1] != o_slot[i])) g_start[g++] = i;
+            g_start[g] = F8_BM;
+            s_ngroups = g;
+        }
+        (void)head;
+        epi_sync();
+        const int ngroups = s_ngroups;
+        // two half-groups of 64 threads: each thread owns one output column and every second slot group
+        const int half = et >> 6, c = et & 63;
+        const int n = n0 + c;
+        int p = -1;
+        for (int q = 0; q < parts.n; q++)
+            if (n >= parts.off[q] && n < parts.off[q] + parts.rows[q]) p = q;
+        const int nl = p >= 0 ? n - parts.off[p] : 0;
+        unsigned char* mybuf = bring + ((size_t)half * 64 + c) * bpitch;  // this thread's row in each ring slot
+        const size_t ring_stride = (size_t)128 * bpitch;
+        auto fetch = [&](int g) {  // group g's row of B for this column into ring slot (g / 2) % F8_RING
+            if (g < ngroups && p >= 0) {
+                const plora_desc& d = table[o_slot[g_start[g]]];
+                const int r = d.r[p];
+                const bf16* src = reinterpret_cast<const bf16*>(d.b[p]) + (size_t)nl * r;
+                unsigned char* dst = mybuf + (size_t)((g >> 1) % F8_RING) * ring_stride;
+                for (int j = 0; j < (r >> 3); j++) cp_async16(dst + j * 16, src + j * 8);
+            }
+            cp_async_commit();
+        };
+        for (int i = 0; i < F8_RING - 1; i++) fetch(half + 2 * i);
+        for (int g = half; g < ngroups; g += 2) {
+            fetch(g + 2 * (F8_RING - 1));
+            cp_async_wait<F8_RING - 1>();
+            if (p >= 0) {
+                const plora_desc& d = table[o_slot[g_start[g]]];
+                const int r = d.r[p], r_off = d.r_off[p];
+                const unsigned char* src = mybuf + (size_t)((g >> 1) % F8_RING) * ring_stride;
+                for (int i = g_start[g]; i < g_start[g + 1]; i++) {
+                    const int lr = o_row[i];
+                    const float* sp = S + (size_t)(m0 + lr) * lds + r_off;
+                    float acc = 0.f;
+                    for (int j = 0; j < r; j += 8) {
+                        float bf[8];
+                        unpack8(*reinterpret_cast<const uint4*>(src + j * 2), bf);
+                        const float4 s0 = __ldg(reinterpret_cast<const float4*>(sp + j));
+                        const float4 s1 = __ldg(reinterpret_cast<const float4*>(sp + j + 4));
+                        acc = fmaf(s0.x, bf[0], acc);
+                        acc = fmaf(s0.y, bf[1], acc);
+                        acc = fmaf(s0.z, bf[2], acc);
+                        acc = fmaf(s0.w, bf[3], acc);
+                        acc = fmaf(s1.x, bf[4], acc);
+                        acc = fmaf(s1.y, bf[5], acc);
+                        acc = fmaf(s1.z, bf[6], acc);
+                        acc = fmaf(s1.w, bf[7], acc);
+                    }
+                    delta[lr * F8_DPITCH + c] = acc;  // one group per token row: written once
+                }
+            }
+        }
+        cp_async_wait<0>();
+        epi_sync();
+        // ---- epilogue: accumulator row by row out of tensor memory, scaled, plus the adapter term
+        const bool ok = mbar_wait(&acc_bar, 0, status);
+        tc_fence_after();
+        const int q4 = warp & 3;  // this warp's quarter of the 128 tensor-memory lanes
+        const int lrow = q4 * 32 + lane;
+        const float srow = (m0 + lrow) < T ? st[m0 + lrow] : 0.f;
+        if (ok) {
+#pragma unroll
+            for (int cc = 0; cc < F8_BN; cc += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + cc, v);
+#pragma unroll
+                for (int q = 0; q < 32; q++) {
+                    const int col = n0 + cc + q;
+                    const float sc = col < N ? __ldg(sn + col) : 0.f;
+                    float* dp = delta + lrow * F8_DPITCH + cc + q;
+                    *dp = fmaf(__uint_as_float(v[q]), srow * sc, *dp);
+                }
+            }
+        }
+        __syncwarp();
+        // coalesced store: the warp's 32 rows, lane l writes columns 2l and 2l + 1
+        if (ok) {
+            const int col = n0 + 2 * lane;
+            if (col < N) {
+                for (int rr = 0; rr < 32; rr++) {
+                    const int grow = m0 + q4 * 32 + rr;
+                    if (grow >= T) break;
+                    const float a = delta[(q4 * 32 + rr) * F8_DPITCH + 2 * lane];
+                    const float b = delta[(q4 * 32 + rr) * F8_DPITCH + 2 * lane + 1];
+                    const size_t at = (size_t)grow * ldy + col;
+                    if (F32) *reinterpret_cast<float2*>(reinterpret_cast<float*>(Y) + at) = make_float2(a, b);
+                    else *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<bf16*>(Y) + at) = __floats2bfloat162_rn(a, b);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, F8_BN);
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+encode_tiled_fn g_encode = nullptr;
+
+template <typename... Params, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                       Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
+}
+
+size_t fused_smem(int max_rank) {
+    const int bpitch = max_rank * 2 + 16;
+    return 1024 + (size_t)F8_STAGES * F8_STAGE_BYTES + (size_t)F8_BM * F8_DPITCH * 4 + (size_t)F8_RING * 128 * bpitch;
+}
+
+}  // namespace
+
+cudaError_t plora_fp8_init(int max_rank) {
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess) return e;
+        if (!fn || q != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
+        g_encode = reinterpret_cast<encode_tiled_fn>(fn);
+    }
+    const size_t smem = fused_smem(max_rank);
+    if (smem > 227 * 1024) return cudaErrorInvalidValue;
+    cudaError_t e = cudaFuncSetAttribute(plora_fp8_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(plora_fp8_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+}
+
+cudaError_t plora_launch_fp8_quant(const void* x, int rows, int ldx, int K, void* xq, float* st, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    plora_fp8_quant_rows_kernel<<<rows, 256, 0, stream>>>(reinterpret_cast<const bf16*>(x), ldx, K,
+                                                          reinterpret_cast<uint8_t*>(xq), st);
+    return cudaGetLastError();
+}
+
+cudaError_t plora_launch_s_reduce(float* S, size_t s_stride_elems, int lds, int nsplit, const int32_t* segs,
+                                  SegLayout lay, const plora_desc* table, int work_cap, bool pdl, cudaStream_t st) {
+    if (nsplit <= 1 || work_cap == 0) return cudaSuccess;
+    return launch_pdl(plora_s_reduce_kernel, dim3((unsigned)work_cap), dim3(128), 0, st, pdl, S, s_stride_elems, lds, nsplit,
+                      segs, lay, table);
+}
+
+cudaError_t plora_launch_fp8_fused(const void* xq, const float* st_, const void* wq, const float* sn, int T, int N, int K,
+                                   const int32_t* segs, SegLayout lay, const plora_desc* table, int n_parts,
+                                   const int* part_off, const int* part_rows, const float* S, int lds, void* y, int ldy,
+                                   int f32_out, int max_rank, int* status, bool pdl, cudaStream_t stream) {
+    if (!g_encode) return cudaErrorNotSupported;
+    CUtensorMap xmap, wmap;
+    const cuuint32_t es[2] = {1, 1};
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)T};
+        const cuuint64_t strides[1] = {(cuuint64_t)K};
+        const cuuint32_t box[2] = {F8_BK, F8_BM};
+        if (g_encode(&xmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(xq), dims, strides, box, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
+        const cuuint64_t strides[1] = {(cuuint64_t)K};
+        const cuuint32_t box[2] = {F8_BK, F8_BN};
+        if (g_encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(wq), dims, strides, box, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    Fp8Parts parts;
+    parts.n = n_parts;
+    for (int i = 0; i < PLORA_MAX_PARTS; i++) {
+        parts.off[i] = i < n_parts ? part_off[i] : 0;
+        parts.rows[i] = i < n_parts ? part_rows[i] : 0;
+    }
+    const int bpitch = max_rank * 2 + 16;
+    dim3 grid((unsigned)((N + F8_BN - 1) / F8_BN), (unsigned)((T + F8_BM - 1) / F8_BM));
+    const size_t smem = fused_smem(max_rank);
+    if (f32_out)
+        return launch_pdl(plora_fp8_fused_kernel<true>, grid, dim3(192), smem, stream, pdl, xmap, wmap, st_, sn, T, N, K,
+                          segs, lay, table, parts, S, lds, y, ldy, bpitch, status);
+    return launch_pdl(plora_fp8_fused_kernel<false>, grid, dim3(192), smem, stream, pdl, xmap, wmap, st_, sn, T, N, K, segs,
+                      lay, table, parts, S, lds, y, ldy, bpitch, status);
+}

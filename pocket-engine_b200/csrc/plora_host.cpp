@@ -193,6 +193,7 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
             check("alloc status", cudaMalloc((void**)&h->status, 64));
             check("kernel attributes", plora_kernels_init(h->seg));
             if (rc == PLORA_OK && h->max_rank <= 128) h->mma_ok = plora_mma_init() == cudaSuccess;
+            if (rc == PLORA_OK && h->max_rank <= 128) h->fp8_ok = plora_fp8_init(h->max_rank) == cudaSuccess;
             // runs of 64 or more contiguous tokens of one slot take the tensor-core tile kernels
             if (h->mma_ok) h->seg.run_min = PLORA_RUN_MIN_DEFAULT;
             if (const char* e = getenv("PLORA_PDL")) h->pdl = e[0] != '0';
@@ -663,8 +664,36 @@ int plora_shrink(plora_t* h, const plora_hook* hook, const plora_step* step, uin
     return PLORA_OK;
 }
 
+static int expand_impl(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
+                       int f32_out, bool reduced, void* stream);
+
 int plora_expand(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
                  int f32_out, void* stream) {
+    return expand_impl(h, hook, step, rows, y, ldy, f32_out, false, stream);
+}
+
+int plora_expand_reduced(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
+                         int f32_out, void* stream) {
+    return expand_impl(h, hook, step, rows, y, ldy, f32_out, true, stream);
+}
+
+int plora_s_reduce(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, void* stream) {
+    if (!h || !hook || !step) return PLORA_ERR_ARG;
+    if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
+    if (hook->site < 0 || hook->site >= (int)h->sites.size()) return fail(h, PLORA_ERR_ARG, "hook names no site");
+    if (rows < 0 || rows > h->max_tokens) return fail(h, PLORA_ERR_CAPACITY, "more rows than max_tokens");
+    const SiteInfo& site = h->sites[(size_t)hook->site];
+    int work_cap = std::min(std::min(step->max_tiles, rows), h->max_slots + rows / PLORA_WORK_TOKENS);
+    const bool pdl = h->pdl && h->pdl_armed;
+    h->pdl_armed = true;
+    CU(h, "S reduce", plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
+                                            (const int32_t*)(uintptr_t)step->segs, h->seg,
+                                            (const plora_desc*)(uintptr_t)hook->table, work_cap, pdl, as_stream(stream)));
+    return PLORA_OK;
+}
+
+static int expand_impl(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
+                       int f32_out, bool reduced, void* stream) {
     if (!h || !hook || !step) return PLORA_ERR_ARG;
     if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
     if (hook->site < 0 || hook->site >= (int)h->sites.size()) return fail(h, PLORA_ERR_ARG, "hook names no site");
@@ -677,7 +706,8 @@ int plora_expand(plora_t* h, const plora_hook* hook, const plora_step* step, int
     const bool pdl = h->pdl && h->pdl_armed;
     h->pdl_armed = true;
     CU(h, "expand",
-       plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
+       plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds,
+                           reduced ? 1 : site.nsplit,
                            (const int32_t*)(uintptr_t)step->segs, h->seg, (const plora_desc*)(uintptr_t)hook->table,
                            (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap, h->status, pdl,
                            as_stream(stream)));
@@ -686,6 +716,50 @@ int plora_expand(plora_t* h, const plora_hook* hook, const plora_step* step, int
            plora_launch_expand_mma((const float*)(uintptr_t)step->s, step->lds, (const int32_t*)(uintptr_t)step->segs, h->seg,
                                    (const plora_desc*)(uintptr_t)hook->table, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
                                    hook->max_rows, std::max(1, rows / 64), h->status, h->pdl, as_stream(stream)));
+    return PLORA_OK;
+}
+
+int plora_fp8_quant_rows(plora_t* h, uint64_t x, int rows, int cols, uint64_t xq, uint64_t st, void* stream) {
+    if (!h) return PLORA_ERR_ARG;
+    if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
+    if (!x || !xq || !st || (x & 15) || (xq & 7) || cols <= 0 || (cols & 7) || rows < 0)
+        return fail(h, PLORA_ERR_ARG, "x, xq, st must be aligned device addresses and cols a multiple of 8");
+    CU(h, "fp8 quantise", plora_launch_fp8_quant((const void*)(uintptr_t)x, rows, cols, cols, (void*)(uintptr_t)xq,
+                                                 (float*)(uintptr_t)st, as_stream(stream)));
+    h->pdl_armed = false;
+    return PLORA_OK;
+}
+
+int plora_linear_fp8_fused(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t xq, uint64_t st,
+                           uint64_t wq, uint64_t sn, int rows, uint64_t y, int ldy, int f32_out, void* stream) {
+    if (!h || !hook || !step) return PLORA_ERR_ARG;
+    if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
+    if (!h->fp8_ok) return fail(h, PLORA_ERR_CONFIG, "the fused FP8 layer needs max_rank <= 128");
+    if (hook->site < 0 || hook->site >= (int)h->sites.size()) return fail(h, PLORA_ERR_ARG, "hook names no site");
+    if (rows < 0 || rows > h->max_tokens) return fail(h, PLORA_ERR_CAPACITY, "more rows than max_tokens");
+    const SiteInfo& site = h->sites[(size_t)hook->site];
+    if (!xq || !st || !wq || !sn || (xq & 15) || (wq & 15) || (site.cols & 15))
+        return fail(h, PLORA_ERR_ARG, "xq and wq must be 16-byte aligned and cols a multiple of 16");
+    if (!y || (y & (f32_out ? 7 : 3)) || (ldy & 1)) return fail(h, PLORA_ERR_ARG, "y must be aligned to two elements and ldy even");
+    if (rows == 0) return PLORA_OK;
+    int off[PLORA_MAX_PARTS] = {0, 0, 0, 0}, prow[PLORA_MAX_PARTS] = {0, 0, 0, 0}, width = 0;
+    for (size_t p = 0; p < site.parts.size(); p++) {
+        off[p] = site.parts[p].off;
+        prow[p] = site.parts[p].rows;
+        width = std::max(width, off[p] + prow[p]);
+    }
+    int work_cap = std::min(std::min(step->max_tiles, rows), h->max_slots + rows / PLORA_WORK_TOKENS);
+    const bool pdl = h->pdl && h->pdl_armed;
+    h->pdl_armed = true;
+    CU(h, "S reduce", plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
+                                            (const int32_t*)(uintptr_t)step->segs, h->seg,
+                                            (const plora_desc*)(uintptr_t)hook->table, work_cap, pdl, as_stream(stream)));
+    CU(h, "fused fp8 layer",
+       plora_launch_fp8_fused((const void*)(uintptr_t)xq, (const float*)(uintptr_t)st, (const void*)(uintptr_t)wq,
+                              (const float*)(uintptr_t)sn, rows, width, site.cols, (const int32_t*)(uintptr_t)step->segs,
+                              h->seg, (const plora_desc*)(uintptr_t)hook->table, (int)site.parts.size(), off, prow,
+                              (const float*)(uintptr_t)step->s, step->lds, (void*)(uintptr_t)y, ldy, f32_out, h->max_rank,
+                              h->status, h->pdl, as_stream(stream)));
     return PLORA_OK;
 }
 

@@ -38,7 +38,8 @@ struct SegLayout {
     // one 128-byte line tells a block everything about its work item
     __host__ __device__ int work() const { return (perm() + max_tokens + 31) / 32 * 32; }
     __host__ __device__ int mma() const { return work() + PLORA_WORK_WORDS * cap_tiles; }  // [cap_tiles][3] start, len, slot
-    __host__ __device__ int words() const { return mma() + 3 * cap_tiles; }
+    __host__ __device__ int tslot() const { return mma() + 3 * cap_tiles; }  // [max_tokens] slot of every token row, 0 = none
+    __host__ __device__ int words() const { return tslot() + max_tokens; }
 };
 
 struct SiteInfo {
@@ -100,6 +101,7 @@ struct plora {
     mutable std::string err;
     int sm_count = 148;
     bool pdl = true;        // launch with programmatic stream serialization
+    bool fp8_ok = false;    // the fused FP8 layer can run
     bool mma_ok = false;    // the tensor-core tile kernels can run (max_rank <= 128 and the driver entry point exists)
     bool pdl_armed = false;  // false right after the step's grouping kernel: the next launch is a plain one
 };
@@ -113,6 +115,14 @@ cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayo
                                     cudaStream_t st);
 cudaError_t plora_kernels_init(const SegLayout& lay);
 cudaError_t plora_mma_init();
+cudaError_t plora_fp8_init(int max_rank);
+cudaError_t plora_launch_fp8_quant(const void* x, int rows, int ldx, int K, void* xq, float* st, cudaStream_t stream);
+cudaError_t plora_launch_s_reduce(float* S, size_t s_stride_elems, int lds, int nsplit, const int32_t* segs,
+                                  SegLayout lay, const plora_desc* table, int work_cap, bool pdl, cudaStream_t st);
+cudaError_t plora_launch_fp8_fused(const void* xq, const float* st_, const void* wq, const float* sn, int T, int N, int K,
+                                   const int32_t* segs, SegLayout lay, const plora_desc* table, int n_parts,
+                                   const int* part_off, const int* part_rows, const float* S, int lds, void* y, int ldy,
+                                   int f32_out, int max_rank, int* status, bool pdl, cudaStream_t stream);
 cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, const int32_t* segs, SegLayout lay,
                                     const plora_desc* table, float* S, int lds, int max_rank_total, int tile_cap,
                                     int* status, bool pdl, cudaStream_t st);

@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(1024) plora_meta_group_kernel(const int* __res
         bad = true;
     }
     for (int i = tid; i < n_tiles; i += 1024) run_len[i] = 0;
+    for (int i = tid; i < lay.max_tokens; i += 1024) segs[lay.tslot() + i] = 0;
     for (int i = tid; i < S1; i += 1024) {
         cnt[i] = 0;
         fill[i] = 0;
@@ -167,6 +168,7 @@ __global__ void __launch_bounds__(1024) plora_meta_group_kernel(const int* __res
                 run_slot[rid] = slot;
             }
             atomicAdd(&run_len[rid], len);
+            for (int k = 0; k < len; k++) segs[lay.tslot() + start + k] = slot;
         }
         n_runs += total;
         __syncthreads();

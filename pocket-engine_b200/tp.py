@@ -1,0 +1,101 @@
+"""Tensor-parallel mode for the adapter path (no counterpart in pocket-engine, which is single-GPU).
+
+One process per GPU. A layer is sharded the way its base weights are:
+
+* column-parallel (q, k, v, gate, up): every rank holds the whole A (the shrink is computed redundantly,
+  it is cheap) and the rows ``[rank * N/P, (rank + 1) * N/P)`` of B; x is replicated, y is the local column
+  slice. No collective.
+* row-parallel (o, down): every rank holds the input-column slice ``A[:, rank * K/P : (rank + 1) * K/P]``
+  and, of B, only the rows of the output slice it will write; x arrives sharded ``[T, K/P]``. Each rank's
+  shrink gives a partial S; the partials are all-reduced (sum) over NVLink with NCCL; then each rank expands
+  its own N/P slice of output columns into its partial y (whose reduction afterwards, the base layer's own,
+  therefore receives exactly one copy of the adapter term).
+
+Sharding is expressed with the registry's own vocabulary: a shard is just a ``Site`` with the local sizes, a
+row-parallel part carrying ``off = rank * N/P`` so the expand lands in the right columns of the full-width
+partial y.
+"""
+import numpy as np
+
+from . import Factors, Site, SitePart
+
+COLUMN, ROW = "column", "row"
+
+
+def shard_site(site, mode, world, rank):
+    """The rank's view of a full-size site."""
+    parts = []
+    off = 0
+    for p in site.parts:
+        if p.rows % world:
+            raise ValueError(f"{p.module}: {p.rows} output features do not split over {world} ranks")
+        n = p.rows // world
+        if mode == COLUMN:
+            parts.append(SitePart(p.module, n, off))  # local y holds only this rank's slices, back to back
+            off += n
+        else:
+            parts.append(SitePart(p.module, n, p.off + rank * n))  # a slice of the full-width partial y
+    cols = site.cols
+    if mode == ROW:
+        if site.cols % (8 * world):
+            raise ValueError(f"{site.cols} input features do not split over {world} ranks in multiples of 8")
+        cols = site.cols // world
+    return Site(site.layer, cols, parts)
+
+
+def shard_factors(f, site, mode, world, rank):
+    """The rank's slice of one module's factors (scale already folded into B)."""
+    part = next(p for p in site.parts if p.module == f.module)
+    n = part.rows // world
+    b = f.b[rank * n:(rank + 1) * n]
+    a = f.a
+    if mode == ROW:
+        k = site.cols // world
+        a = f.a[:, rank * k:(rank + 1) * k]
+    return Factors(f.layer, f.module, np.ascontiguousarray(a), np.ascontiguousarray(b))
+
+
+def shard_x(x, mode, world, rank):
+    """Row-parallel layers take the rank's input-column slice of x; column-parallel ones all of it."""
+    if mode == COLUMN:
+        return x
+    k = x.shape[1] // world
+    return np.ascontiguousarray(x[:, rank * k:(rank + 1) * k])
+
+
+class _DevView:
+    """A raw device address as something torch.as_tensor understands (CUDA array interface, f32)."""
+
+    def __init__(self, ptr, shape):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (int(ptr), False),
+                                         "version": 2, "strides": None}
+
+
+class TPLinear:
+    """Linear::forward's adapter bracket for one shard. ``group`` is a torch.distributed process group (NCCL
+    on GPUs); for row-parallel layers the shrink's partial sums are all-reduced between shrink and expand."""
+
+    def __init__(self, loras, site, mode, group=None, base=None):
+        import torch
+        self.loras, self.site, self.mode, self.group, self.base = loras, site, mode, group, base
+        self.lora = loras.hook(site)
+        # plane 0 of the f32 intermediate as a tensor, for the collective
+        self._s = torch.as_tensor(_DevView(loras.s, (loras.max_tokens, loras.lds)), device=f"cuda:{loras.device}") \
+            if mode == ROW else None
+
+    def forward(self, x, rows, y, ldy, f32_out=False, lora=None, main=0):
+        import torch
+        import torch.distributed as dist
+        L = self.loras
+        if lora is not None:
+            L.shrink(self.lora, lora, x, rows, main)
+        if self.base is not None:
+            self.base(x, rows, y, ldy, f32_out)
+        if lora is None:
+            return
+        if self.mode == ROW:
+            L.s_reduce(self.lora, lora, rows, main)  # K-split partials -> plane 0
+            dist.all_reduce(self._s[:rows], op=dist.ReduceOp.SUM, group=self.group)
+            L.expand_reduced(self.lora, lora, rows, y, ldy, f32_out, main)
+        else:
+            L.expand(self.lora, lora, rows, y, ldy, f32_out, main)
