@@ -63,6 +63,58 @@ def shard_x(x, mode, world, rank):
     return np.ascontiguousarray(x[:, rank * k:(rank + 1) * k])
 
 
+class ShardedWorkload:
+    """A rank's share of a full-size workload (see workloads.config5): sharded sites, factors and inputs.
+    ``y_base(si)`` is this rank's base output: its column slice for column-parallel layers, a full-width
+    partial (the true base divided evenly over the ranks) for row-parallel ones."""
+
+    def __init__(self, wl, world, rank):
+        self.full, self.world, self.rank = wl, world, rank
+        self.modes = list(wl.modes)
+        self.sites = [shard_site(s, m, world, rank) for s, m in zip(wl.sites, wl.modes)]
+        for name in ("ranks", "scale", "row_n", "row_slot", "max_rank", "n_adapters", "tokens", "n_seqs", "seed"):
+            setattr(self, name, getattr(wl, name))
+        self.name = f"{wl.name}-tp{world}r{rank}"
+        self.token_slot, self.cu = wl.token_slot, wl.cu
+
+    def factors(self, i):
+        by_module = {p.module: (si, s) for si, s in enumerate(self.full.sites) for p in s.parts}
+        out = []
+        for f in self.full.factors(i):
+            si, site = by_module[f.module]
+            out.append(shard_factors(f, site, self.modes[si], self.world, self.rank))
+        return out
+
+    def x_bits(self, si):
+        return shard_x(self.full.x_bits(si), self.modes[si], self.world, self.rank)
+
+    def y_base(self, si):
+        yb = self.full.y_base(si)
+        site = self.full.sites[si]
+        if self.modes[si] == ROW:
+            return (yb / np.float32(self.world)).astype(np.float32)
+        cols = []
+        for p in site.parts:
+            n = p.rows // self.world
+            cols.append(yb[:, p.off + self.rank * n:p.off + (self.rank + 1) * n])
+        return np.ascontiguousarray(np.concatenate(cols, axis=1))
+
+    def assemble(self, si, outs):
+        """The full layer output from every rank's y (list indexed by rank): row-parallel partials add up,
+        column-parallel slices interleave back into the parts."""
+        site = self.full.sites[si]
+        if self.modes[si] == ROW:
+            return np.sum(np.stack(outs, 0).astype(np.float64), 0)
+        full = np.zeros((self.tokens, site.width()), np.float64)
+        for r, y in enumerate(outs):
+            at = 0
+            for p in site.parts:
+                n = p.rows // self.world
+                full[:, p.off + r * n:p.off + (r + 1) * n] = y[:, at:at + n]
+                at += n
+        return full
+
+
 class _DevView:
     """A raw device address as something torch.as_tensor understands (CUDA array interface, f32)."""
 

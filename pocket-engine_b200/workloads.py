@@ -130,21 +130,21 @@ def config4(seed=0, tokens=256, adapters=128, two_part=False):
                     max_rank=128)
 
 
-def config5(seed=0, world=1, rank_id=0, adapters=32, rank=32):
-    """27B-shaped layer (hidden 5120, intermediate 17408, q width 6144), 512 tokens = 256 decode sequences
-    then 2 prompt chunks of 128; column-parallel q and gate/up, row-parallel o and down over `world` GPUs.
-    The sites describe THIS rank's shard: column-parallel sites keep cols and split rows, row-parallel
-    sites split cols and keep rows."""
-    P = world
+def config5(seed=0, adapters=32, rank=32, hidden=5120, inter=17408, q_width=6144, decode=256, chunks=(128, 128)):
+    """27B-shaped layer (hidden 5120, intermediate 17408, q width 6144), 512 tokens = 256 one-token decode
+    sequences first, then 2 prompt chunks of 128; 32 adapters of rank 32, uniform per sequence. The sites are
+    the FULL layers; ``modes`` says how each is sharded in tensor-parallel mode (column-parallel q and
+    gate/up, row-parallel o and down): see tp.shard_workload."""
     sites = [
-        Site.fused(0, 5120, [("self_attn.q_proj", 6144 // P)]),
-        Site.fused(0, 6144 // P, [("self_attn.o_proj", 5120)]),
-        Site.fused(0, 5120, [("mlp.gate_proj", 17408 // P), ("mlp.up_proj", 17408 // P)]),
-        Site.fused(0, 17408 // P, [("mlp.down_proj", 5120)]),
+        Site.fused(0, hidden, [("self_attn.q_proj", q_width)]),
+        Site.fused(0, q_width, [("self_attn.o_proj", hidden)]),
+        Site.fused(0, hidden, [("mlp.gate_proj", inter), ("mlp.up_proj", inter)]),
+        Site.fused(0, inter, [("mlp.down_proj", hidden)]),
     ]
     rng = np.random.default_rng([seed, 11])
-    row_n = [1] * 256 + [128, 128]
+    row_n = [1] * decode + list(chunks)
     slot = rng.integers(1, adapters + 1, len(row_n))
-    wl = Workload(f"tp{P}-5120x17408-512tok-32xr32", sites, [rank] * adapters, 1.0, row_n, slot, seed)
-    wl.world, wl.rank_id = P, rank_id
+    wl = Workload(f"tp-{hidden}x{inter}-{sum(row_n)}tok-{adapters}xr{rank}", sites, [rank] * adapters, 1.0, row_n, slot,
+                  seed)
+    wl.modes = ["column", "row", "column", "row"]
     return wl
