@@ -314,6 +314,221 @@ def run_ours(args, rank, world, local_rank):
     return out
 
 
+# ------------------------------------------------------------------- FP8 fused layer, TP layer
+
+def _event_time(torch, stream, fn, steps, warmup, barrier):
+    with torch.cuda.stream(stream):
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record(stream)
+        barrier()
+    return e0.elapsed_time(e1)
+
+
+def run_fp8(args, rank, world, local_rank):
+    """Heterogeneous adapters over an FP8 base layer (4096 -> 12288, 256 decode tokens, 128 adapters of rank
+    8..128, Zipf popularity): a step = row quantisation of x, shrink on the bf16 x, then the FP8 GEMM with the
+    adapter expand fused into its epilogue. --tokens N runs the same layer at a prefill-sized M."""
+    import torch
+    pe = entry.load_package()
+    from pocket_engine_b200 import workloads
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    if args.tokens:
+        seqs = max(1, args.tokens // 2048)
+        wl = workloads.Workload(f"fp8-prefill-4096x12288-{seqs}x2048-r64", workloads.config4().sites, [64] * seqs, 1.0,
+                                [2048] * seqs, list(range(1, seqs + 1)), 1000 * rank, max_rank=128)
+    else:
+        wl = workloads.config4(seed=1000 * rank)
+    site = wl.sites[0]
+    K, N, T = site.cols, site.width(), wl.tokens
+    main = torch.cuda.Stream(device=dev)
+    rng = np.random.default_rng([wl.seed, 77])
+    w = np.clip(rng.standard_normal((N, K), dtype=np.float32), -448, 448)
+    wq_h = torch.from_numpy(w).to(torch.float8_e4m3fn).view(torch.uint8)
+    sn_h = torch.from_numpy((rng.uniform(0.5, 2.0, N) / 448.0).astype(np.float32))
+    x_h = torch.from_numpy(wl.x_bits(0).view(np.int16)).pin_memory()
+    copies = args.copies or 2
+    sets = []
+    used = sorted(set(int(s) for s in wl.row_slot if s))
+    for c in range(copies):
+        L = pe.Loras(wl.sites, wl.n_adapters, wl.max_rank, T, wl.n_seqs, device=local_rank)
+        prep = L.prep()
+        for i in range(wl.n_adapters):
+            L.upload(i + 1, L.insert(prep.prepare(f"a{i}", wl.factors(i))), main.cuda_stream)
+        S = {"L": L, "x": x_h.to(dev).view(torch.bfloat16), "xq": torch.zeros(T, K, dtype=torch.uint8, device=dev),
+             "st": torch.zeros(T, dtype=torch.float32, device=dev), "wq": wq_h.to(dev), "sn": sn_h.to(dev),
+             "y": torch.zeros(T, N, dtype=torch.bfloat16, device=dev), "cu": torch.from_numpy(wl.cu()).to(dev),
+             "ss": torch.from_numpy(wl.row_slot.copy()).to(dev), "hook": L.hook(0)}
+        L.meta_build(S["cu"].data_ptr(), S["ss"].data_ptr(), wl.n_seqs, main.cuda_stream)
+        S["step"] = L.lora_step(L.max_lora_tiles(), main.cuda_stream, decode=int(wl.row_n.max()) == 1)
+        sets.append(S)
+    torch.cuda.synchronize()
+
+    def block(S, m):
+        L = S["L"]
+        L.fp8_quant_rows(S["x"].data_ptr(), T, K, S["xq"].data_ptr(), S["st"].data_ptr(), m)
+        L.shrink(S["hook"], S["step"], S["x"].data_ptr(), T, m)
+        L.linear_fp8_fused(S["hook"], S["step"], S["xq"].data_ptr(), S["st"].data_ptr(), S["wq"].data_ptr(),
+                           S["sn"].data_ptr(), T, S["y"].data_ptr(), N, False, m)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms = _event_time(torch, main, lambda i: block(sets[i % copies], main.cuda_stream), args.steps, args.warmup, barrier)
+    # the fused kernel alone
+    evs = []
+    with torch.cuda.stream(main):
+        for i in range(12):
+            S = sets[i % copies]
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            S["L"].shrink(S["hook"], S["step"], S["x"].data_ptr(), T, main.cuda_stream)
+            a.record(main)
+            S["L"].linear_fp8_fused(S["hook"], S["step"], S["xq"].data_ptr(), S["st"].data_ptr(), S["wq"].data_ptr(),
+                                    S["sn"].data_ptr(), T, S["y"].data_ptr(), N, False, main.cuda_stream)
+            b.record(main)
+            evs.append((a, b))
+        torch.cuda.synchronize()
+    fused_us = 1e3 * float(np.mean([a.elapsed_time(b) for a, b in evs[2:]]))
+    clocks = sampler.stop() if sampler is not None else None
+    # end to end with host buffers: x in, y out
+    y_out = torch.empty(T, N, dtype=torch.int16).pin_memory()
+
+    def e2e(i):
+        S = sets[i % copies]
+        S["x"].view(torch.int16).copy_(x_h, non_blocking=True)
+        block(S, main.cuda_stream)
+        y_out.copy_(S["y"].view(torch.int16), non_blocking=True)
+
+    with torch.cuda.stream(main):
+        for i in range(args.warmup):
+            e2e(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            e2e(i)
+            main.synchronize()
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+    for S in sets:
+        S["L"].device_status()
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    if rank != 0:
+        return None
+    tslot = wl.token_slot()
+    t_l = int((tslot > 0).sum())
+    slab = sum(2 * wl.ranks[s - 1] * (K + N) for s in used)
+    s_bytes = sum(int((tslot == s).sum()) * wl.ranks[s - 1] * 8 for s in used)
+    fused_bytes = K * N + 4 * N + T * K + 4 * T + sum(2 * wl.ranks[s - 1] * N for s in used) + s_bytes // 2 + 2 * T * N
+    step_bytes = fused_bytes + sum(2 * wl.ranks[s - 1] * K for s in used) + 2 * t_l * K + s_bytes // 2 + 2 * T * K + T * K
+    flops = 2.0 * T * K * N + sum(int((tslot == s).sum()) * 2.0 * wl.ranks[s - 1] * (K + N) for s in used)
+    peak, kind, pk = peaks()
+    fp8_peak = 2 * pk.get("bf16_tflops", 1590.0)
+    us = 1e3 * ms / args.steps
+    return {"metric": METRIC, "value": world * T * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp8 e4m3 base + bf16 adapters, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": wl.name, "tokens_per_step": T, "lora_tokens": t_l, "adapters": wl.n_adapters,
+                       "slots_present": len(used), "layer": f"{K}->{N}", "l2": f"{copies} rotating copies of pool+W",
+                       "step": "row quantisation + shrink + FP8 GEMM with fused adapter expand"},
+            "e2e": {"value": world * T * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 2 * T * K,
+                    "d2h_bytes_per_step": 2 * T * N, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": 4 * args.steps,
+            "roofline": {"bound": "hbm" if step_bytes / (peak * 1e9) > flops / (fp8_peak * 1e12) else "tensor",
+                         "kernel": "plora_fp8_fused_kernel", "achieved": fused_bytes / (fused_us * 1e-6) / 1e9, "peak": peak,
+                         "unit": "GB/s", "frac": fused_bytes / (fused_us * 1e-6) / 1e9 / peak, "peak_kind": kind,
+                         "traffic": None, "us_per_launch": fused_us, "algorithmic_bytes_per_launch": fused_bytes,
+                         "tflops": flops / (fused_us * 1e-6) / 1e12,
+                         "tensor_frac_of_2x_bf16_peak": flops / (fused_us * 1e-6) / 1e12 / fp8_peak},
+            "step_roofline": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (us * 1e-6) / 1e9,
+                              "frac": step_bytes / (us * 1e-6) / 1e9 / peak, "us_per_step": us,
+                              "tflops": flops / (us * 1e-6) / 1e12},
+            "clocks": clocks}
+
+
+def run_tp(args, rank, world, local_rank):
+    """Tensor-parallel 27B-shaped layer set (q, o, gate/up, down; hidden 5120, intermediate 17408), 512 tokens,
+    32 rank-32 adapters: column-parallel q and gate/up, row-parallel o and down with an NCCL all-reduce of the
+    [512, 32] shrink partials. Strong scaling: the same batch over more GPUs."""
+    import torch
+    pe = entry.load_package()
+    from pocket_engine_b200 import tp, workloads
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    wl = workloads.config5()
+    sh = tp.ShardedWorkload(wl, world, rank)
+    ns = len(sh.sites)
+    copies = args.copies or 4
+    sets = []
+    for c in range(copies):
+        L = pe.Loras(sh.sites, sh.n_adapters, sh.max_rank, sh.tokens, sh.n_seqs, device=local_rank)
+        prep = L.prep()
+        for i in range(sh.n_adapters):
+            L.upload(i + 1, L.insert(prep.prepare(f"a{i}", sh.factors(i))))
+        x = [torch.from_numpy(sh.x_bits(si).view(np.int16)).to(dev).view(torch.bfloat16) for si in range(ns)]
+        y = [torch.from_numpy(pe.bf16_bits(sh.y_base(si)).reshape(sh.tokens, -1).view(np.int16)).to(dev).view(torch.bfloat16)
+             for si in range(ns)]
+        L.meta_upload(pe.fill_tiles(sh.row_n, sh.row_slot, L.max_lora_tiles()))
+        step = L.lora_step(L.max_lora_tiles())
+        lins = [tp.TPLinear(L, si, sh.modes[si]) for si in range(ns)]
+        sets.append({"L": L, "x": x, "y": y, "step": step, "lins": lins})
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream()
+
+    def block(i):
+        S = sets[i % copies]
+        for si in range(ns):
+            S["lins"][si].forward(S["x"][si].data_ptr(), sh.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1], False,
+                                  lora=S["step"], main=stream.cuda_stream)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms = _event_time(torch, stream, block, args.steps, args.warmup, barrier)
+    # the collective alone: all-reduce of one [512, lds] plane
+    s0 = sets[0]["lins"][1]._s[:sh.tokens]
+    ar = _event_time(torch, stream, lambda i: torch.distributed.all_reduce(s0), 50, 5, barrier) / 50 if world > 1 else 0.0
+    clocks = sampler.stop() if sampler is not None else None
+    for S in sets:
+        S["L"].device_status()
+    t = torch.tensor([ms, ar], device=dev, dtype=torch.float64)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms, ar = float(t[0]), float(t[1])
+    if rank != 0:
+        return None
+    # per-GPU algorithmic bytes of the rank's shard
+    shw = workloads.Workload(sh.name, sh.sites, sh.ranks, sh.scale, sh.row_n, sh.row_slot, sh.seed).work()
+    peak, kind, _ = peaks()
+    us = 1e3 * ms / args.steps
+    return {"metric": METRIC, "value": sh.tokens * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl.name, "tokens_per_step": sh.tokens, "adapters": sh.n_adapters,
+                       "parallelism": f"tp{world}: column-parallel q, gate/up; row-parallel o, down",
+                       "collective": "NCCL all-reduce(sum) of the f32 shrink partials, 2 per step",
+                       "l2": f"{copies} rotating copies"},
+            "gpu_launches": (2 * ns + 2) * 2 * args.steps,
+            "step_roofline": {"algorithmic_bytes_per_step_per_gpu": shw["bytes"], "achieved_gbs_per_gpu": shw["bytes"] / (us * 1e-6) / 1e9,
+                              "frac": shw["bytes"] / (us * 1e-6) / 1e9 / peak, "us_per_step": us},
+            "collective_us": 1e3 * ar, "collective_bytes": int(sh.tokens * sets[0]["L"].lds * 4),
+            "clocks": clocks}
+
+
 # -------------------------------------------------------------------------------- CPU port
 
 def cpu_port(wl_name, seconds, seed=0, threads=0, steps=None, warmup=0):
@@ -465,7 +680,8 @@ def main():
     ap.add_argument("--steps", type=int, default=0, help="default: 200 (decode), 10 (prefill)")
     ap.add_argument("--warmup", type=int, default=0, help="default: 20 (decode), 3 (prefill)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "plumbing"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "plumbing", "fp8", "tp"])
+    ap.add_argument("--tokens", type=int, default=0, help="fp8 workload only: run the layer at this prefill-sized M")
     ap.add_argument("--copies", type=int, default=0, help="override the number of rotating pool copies")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--streams", type=int, default=1, choices=[1, 2],
@@ -474,6 +690,8 @@ def main():
     args = ap.parse_args()
     args.steps = args.steps or (10 if args.workload == "prefill" else 200)
     args.warmup = max(args.warmup or (3 if args.workload == "prefill" else 20), 3)
+    if args.workload == "fp8" and args.tokens:
+        args.steps, args.warmup = min(args.steps, 10), 3
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -485,8 +703,19 @@ def main():
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU fallback")
-    if world > 1:
-        torch.distributed.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    if world > 1 or args.workload == "tp":
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        torch.distributed.init_process_group("nccl", rank=rank, world_size=world,
+                                             device_id=torch.device(f"cuda:{local_rank}"))
+    if args.workload in ("fp8", "tp"):
+        out = (run_fp8 if args.workload == "fp8" else run_tp)(args, rank, world, local_rank)
+        if rank == 0:
+            print(json.dumps(out))
+        if torch.distributed.is_initialized():
+            torch.distributed.barrier()
+            torch.distributed.destroy_process_group()
+        return
     out = run_ours(args, rank, world, local_rank)
     if rank == 0:
         v, cores, sample, _, _ = cpu_port(args.workload, args.cpu_seconds)
