@@ -39,12 +39,15 @@ def peaks():
     return 6650.0, "fallback", {}
 
 
+PREFILL_SEQS = 8
+
+
 def make_workload(name, seed):
     from pocket_engine_b200 import workloads
     if name == "decode":
         return workloads.config2(seed=seed)
     if name == "prefill":
-        return workloads.config3(seed=seed)
+        return workloads.config3(seed=seed, seqs=PREFILL_SEQS)
     if name == "plumbing":
         return workloads.config1(seed=seed)
     raise SystemExit(f"unknown workload {name}")
@@ -682,12 +685,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "plumbing", "fp8", "tp"])
     ap.add_argument("--tokens", type=int, default=0, help="fp8 workload only: run the layer at this prefill-sized M")
+    ap.add_argument("--seqs", type=int, default=8, help="prefill workload only: sequences of 2048 tokens (8 = the "
+                                                        "benchmark configuration; fewer for profiler captures)")
     ap.add_argument("--copies", type=int, default=0, help="override the number of rotating pool copies")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--streams", type=int, default=1, choices=[1, 2],
                     help="1: one stream, kernels chained by programmatic dependent launch; 2: the engine's "
                          "side-stream shrink with fork/join events")
     args = ap.parse_args()
+    global PREFILL_SEQS
+    PREFILL_SEQS = args.seqs
     args.steps = args.steps or (10 if args.workload == "prefill" else 200)
     args.warmup = max(args.warmup or (3 if args.workload == "prefill" else 20), 3)
     if args.workload == "fp8" and args.tokens:
