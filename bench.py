@@ -164,10 +164,14 @@ def run_ours(args, rank, world, local_rank):
         sets.append({"L": L, "x": x, "y": y, "cu": cu, "ss": ss, "step": step, "lins": lins})
     torch.cuda.synchronize()
 
+    fused = args.path != "pair"
+    for S in sets:
+        S["L"].set_apply_mode(1 if args.path == "cluster" else 0)
+
     def block(S, m, s):
         for si in range(ns):
             S["lins"][si].forward(S["x"][si].data_ptr(), wl.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1], False,
-                                  lora=S["step"], main=m, side=s)
+                                  lora=S["step"], main=m, side=s, fused=fused)
 
     # one CUDA graph per copy: the block's 8 launches with the engine's fork/join choreography
     graphs = []
@@ -230,7 +234,7 @@ def run_ours(args, rank, world, local_rank):
             st = S["L"].lora_step(S["L"].max_lora_tiles(), m, decode=decode)
             for si in range(ns):
                 S["lins"][si].forward(S["x"][si].data_ptr(), wl.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1],
-                                      False, lora=st, main=m, side=side_h)
+                                      False, lora=st, main=m, side=side_h, fused=fused)
             for si in range(ns):
                 y_out[si].copy_(S["y"][si].view(torch.int16), non_blocking=True)
         main.synchronize()
@@ -301,7 +305,7 @@ def run_ours(args, rank, world, local_rank):
                    "l2": f"inputs larger than L2: {copies} rotating copies of pool+x+y = "
                          f"{copies * (pool_bytes + d2h + h2d // 2) / 2 ** 20:.0f} MiB",
                    "partitioning": "adapter-affine, one batch per GPU, no collective",
-                   "graph": f"one CUDA graph per copy, {args.streams} stream(s)"},
+                   "graph": f"one CUDA graph per copy, {args.streams} stream(s)", "path": args.path},
         "e2e": {"value": world * wl.tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": (8 if decode else 16) * args.steps,
@@ -689,6 +693,10 @@ def main():
                                                         "benchmark configuration; fewer for profiler captures)")
     ap.add_argument("--copies", type=int, default=0, help="override the number of rotating pool copies")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--path", default="apply", choices=["apply", "cluster", "pair"],
+                    help="apply: plora_apply after the layer's own matrix multiply (shrink and expand fetch x and y "
+                         "ahead of their dependency waits); cluster: plora_apply as one cluster kernel per layer; "
+                         "pair: the engine's shrink-before / expand-after bracket")
     ap.add_argument("--streams", type=int, default=1, choices=[1, 2],
                     help="1: one stream, kernels chained by programmatic dependent launch; 2: the engine's "
                          "side-stream shrink with fork/join events")

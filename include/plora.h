@@ -215,6 +215,18 @@ int plora_fp8_quant_rows(plora_t* h, uint64_t x, int rows, int cols, uint64_t xq
 int plora_linear_fp8_fused(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t xq, uint64_t st,
                            uint64_t wq, uint64_t sn, int rows, uint64_t y, int ldy, int f32_out, void* stream);
 
+/* Shrink and expand of one layer in one call, for callers whose x and y are both ready (that is, after the
+ * layer's own matrix multiply, where Linear::forward issues lora_expand: src/linear.rs:844-847). Same results
+ * as plora_shrink + plora_expand (bitwise in mode 0; within the stated tolerance in mode 1, whose summation
+ * order differs); deterministic. */
+int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, int rows, uint64_t y, int ldy,
+                int f32_out, void* stream);
+/* How plora_apply runs the few-token work items: 0 (default) = the shrink / expand pair, each fetching its
+ * activations ahead of its dependency wait (x and y must not be outputs of the kernel launched right before
+ * plora_apply on the same stream: true after the layer's own matrix multiply, whose kernels do not write x, and
+ * y is only read by the second of the two kernels); 1 = one cluster kernel per layer where the shapes fit. */
+int plora_set_apply_mode(plora_t* h, int mode);
+
 /* Tensor-parallel row-parallel layers (no counterpart in the single-GPU engine): plora_s_reduce adds the
  * shrink's K-split partials into plane 0 of S ([max_tokens, lds] f32 at plora_s_ptr), the caller all-reduces
  * the first `rows` rows of that plane over its ranks, and plora_expand_reduced expands from plane 0 alone. */

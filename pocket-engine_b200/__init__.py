@@ -123,6 +123,8 @@ SYMBOLS = {
     "plora_fp8_quant_rows": (_I, [_P, _U64, _I, _I, _U64, _U64, _P]),
     "plora_linear_fp8_fused": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _U64, _U64, _U64, _U64, _I, _U64, _I, _I,
                                     _P]),
+    "plora_apply": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _U64, _I, _U64, _I, _I, _P]),
+    "plora_set_apply_mode": (_I, [_P, _I]),
     "plora_s_reduce": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _P]),
     "plora_expand_reduced": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _U64, _I, _I, _P]),
     "plora_fork": (_I, [_P, _P, _P]),
@@ -427,6 +429,15 @@ class Loras:
         self._check(lib.plora_linear_fp8_fused(self._h, C.byref(hook), C.byref(step), xq, st, wq, sn, rows, y, ldy,
                                                int(f32_out), _P(stream)))
 
+    def apply(self, hook, step, x, rows, y, ldy, f32_out=False, stream=0):
+        """Shrink + expand of one layer in one call (x and y both ready): one cluster kernel per layer where the
+        shapes fit, else the shrink / expand pair."""
+        self._check(lib.plora_apply(self._h, C.byref(hook), C.byref(step), x, rows, y, ldy, int(f32_out), _P(stream)))
+
+    def set_apply_mode(self, mode):
+        """0: apply() = shrink / expand pair with early activation loads; 1: one cluster kernel per layer."""
+        self._check(lib.plora_set_apply_mode(self._h, mode))
+
     def s_reduce(self, hook, step, rows, stream=0):
         """Adds the shrink's K-split partials into plane 0 of S (before a tensor-parallel all-reduce)."""
         self._check(lib.plora_s_reduce(self._h, C.byref(hook), C.byref(step), rows, _P(stream)))
@@ -453,8 +464,15 @@ class Linear:
         self.lora = loras.hook(site)  # Linear.lora, src/linear.rs:48-49
         self.cols = loras.sites[site].cols
 
-    def forward(self, x, rows, y, ldy, f32_out=False, lora=None, main=0, side=None):
+    def forward(self, x, rows, y, ldy, f32_out=False, lora=None, main=0, side=None, fused=False):
         L = self.loras
+        if fused:
+            # the whole adapter application after the layer's own matrix multiply, one kernel per layer
+            if self.base is not None:
+                self.base(x, rows, y, ldy, f32_out)
+            if lora is not None:
+                L.apply(self.lora, lora, x, rows, y, ldy, f32_out, main)
+            return
         if lora is not None:
             if side is not None and side != main:
                 L.fork(main, side)

@@ -7,24 +7,42 @@
 #include "../../include/plora.h"
 
 #ifdef PLORA_TRACE
-// Debug build only: per-block time stamps from the global nanosecond timer, 16 slots per block.
+// Debug build only: time stamps from the global nanosecond timer. Two sinks: 16 slots per block of one launch
+// (g_plora_trace), or an append-only ring of (time, kernel tag, point, block) records across launches
+// (g_plora_ring, first word = write position).
 static __device__ unsigned long long* g_plora_trace = nullptr;
+static __device__ unsigned long long* g_plora_ring = nullptr;
+#ifndef PLORA_TRACE_TAG
+#define PLORA_TRACE_TAG 0
+#endif
 #define PLORA_TRACE_SETTER(name)                                                  \
     extern "C" int name(unsigned long long* buf) {                                \
         return (int)cudaMemcpyToSymbol(g_plora_trace, &buf, sizeof(buf));         \
+    }                                                                             \
+    extern "C" int name##_ring(unsigned long long* buf) {                         \
+        return (int)cudaMemcpyToSymbol(g_plora_ring, &buf, sizeof(buf));          \
     }
-#define TRACE(i)                                                                                         \
+#define TRACE_K(tag, i)                                                                                  \
     do {                                                                                                 \
-        if (threadIdx.x == 0 && g_plora_trace) {                                                         \
+        if (threadIdx.x == 0 && (g_plora_trace || g_plora_ring)) {                                       \
             unsigned long long gt_;                                                                      \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                                      \
-            const size_t b_ = ((size_t)blockIdx.z * gridDim.y * gridDim.x + blockIdx.y * gridDim.x + blockIdx.x) * 16; \
-            g_plora_trace[b_ + (i)] = gt_;                                                               \
+            const size_t lb_ = (size_t)blockIdx.z * gridDim.y * gridDim.x + blockIdx.y * gridDim.x + blockIdx.x; \
+            if (g_plora_trace) g_plora_trace[lb_ * 16 + (i)] = gt_;                                      \
+            if (g_plora_ring) {                                                                          \
+                const unsigned long long at_ = atomicAdd(g_plora_ring, 1ull);                            \
+                if (at_ < (1ull << 20)) {                                                                \
+                    g_plora_ring[1 + 2 * at_] = gt_;                                                     \
+                    g_plora_ring[2 + 2 * at_] = ((unsigned long long)(tag) << 56) | ((unsigned long long)(i) << 48) | lb_; \
+                }                                                                                        \
+            }                                                                                            \
         }                                                                                                \
     } while (0)
+#define TRACE(i) TRACE_K(PLORA_TRACE_TAG, i)
 #else
 #define PLORA_TRACE_SETTER(name)
 #define TRACE(i)
+#define TRACE_K(tag, i)
 #endif
 
 namespace {

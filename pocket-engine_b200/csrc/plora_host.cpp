@@ -193,6 +193,12 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
             check("alloc status", cudaMalloc((void**)&h->status, 64));
             check("kernel attributes", plora_kernels_init(h->seg));
             if (rc == PLORA_OK && h->max_rank <= 128) h->mma_ok = plora_mma_init() == cudaSuccess;
+            if (rc == PLORA_OK) h->site_ok = plora_site_init() == cudaSuccess;
+            for (auto& s : h->sites) {
+                int a, b, c, d2, e, total = 0;
+                for (auto& p : s.parts) total += p.rows;
+                s.cluster_ok = h->site_ok && plora_site_plan(s.cols, (int)s.parts.size(), h->max_rank, total, &a, &b, &c, &d2, &e) > 0;
+            }
             if (rc == PLORA_OK && h->max_rank <= 128) h->fp8_ok = plora_fp8_init(h->max_rank) == cudaSuccess;
             // runs of 64 or more contiguous tokens of one slot take the tensor-core tile kernels
             if (h->mma_ok) h->seg.run_min = PLORA_RUN_MIN_DEFAULT;
@@ -638,7 +644,15 @@ int plora_step_begin(plora_t* h, int max_tiles, int decode, void* stream, plora_
 
 // ------------------------------------------------------------------ bracket
 
+static int shrink_impl(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, int rows, bool early,
+                       void* stream);
+
 int plora_shrink(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, int rows, void* stream) {
+    return shrink_impl(h, hook, step, x, rows, false, stream);
+}
+
+static int shrink_impl(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, int rows, bool early,
+                       void* stream) {
     if (!h || !hook || !step) return PLORA_ERR_ARG;
     if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
     if (hook->site < 0 || hook->site >= (int)h->sites.size()) return fail(h, PLORA_ERR_ARG, "hook names no site");
@@ -655,7 +669,7 @@ int plora_shrink(plora_t* h, const plora_hook* hook, const plora_step* step, uin
        plora_launch_shrink((const void*)(uintptr_t)x, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
                            h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s,
                            (size_t)(step->s_stride / 4), step->lds, site.kchunk, site.nsplit, work_cap,
-                           hook->parts * h->max_rank, h->status, pdl, as_stream(stream)));
+                           hook->parts * h->max_rank, h->status, pdl, early, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min)
         CU(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
@@ -665,16 +679,55 @@ int plora_shrink(plora_t* h, const plora_hook* hook, const plora_step* step, uin
 }
 
 static int expand_impl(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
-                       int f32_out, bool reduced, void* stream);
+                       int f32_out, bool reduced, bool early, void* stream);
 
 int plora_expand(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
                  int f32_out, void* stream) {
-    return expand_impl(h, hook, step, rows, y, ldy, f32_out, false, stream);
+    return expand_impl(h, hook, step, rows, y, ldy, f32_out, false, false, stream);
 }
 
 int plora_expand_reduced(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
                          int f32_out, void* stream) {
-    return expand_impl(h, hook, step, rows, y, ldy, f32_out, true, stream);
+    return expand_impl(h, hook, step, rows, y, ldy, f32_out, true, false, stream);
+}
+
+// Shrink and expand of one layer in one call, for callers whose x and y are both ready (after the layer's own
+// matrix multiply): the gather tokens go through the cluster kernel where the layer's shapes fit it.
+int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, int rows, uint64_t y, int ldy,
+                int f32_out, void* stream) {
+    if (!h || !hook || !step) return PLORA_ERR_ARG;
+    if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
+    if (hook->site < 0 || hook->site >= (int)h->sites.size()) return fail(h, PLORA_ERR_ARG, "hook names no site");
+    const SiteInfo& site = h->sites[(size_t)hook->site];
+    if (!site.cluster_ok || h->apply_mode == 0) {
+        // x and y are both older than the kernel before each launch: fetch them ahead of the dependency waits
+        int rc = shrink_impl(h, hook, step, x, rows, true, stream);
+        return rc != PLORA_OK ? rc : expand_impl(h, hook, step, rows, y, ldy, f32_out, false, true, stream);
+    }
+    if (rows < 0 || rows > h->max_tokens) return fail(h, PLORA_ERR_CAPACITY, "more rows than max_tokens");
+    if (!x || (x & 15)) return fail(h, PLORA_ERR_ARG, "x must be a 16-byte aligned device address");
+    if (!y || (y & (f32_out ? 7 : 3)) || (ldy & 1)) return fail(h, PLORA_ERR_ARG, "y must be aligned to two elements and ldy even");
+    int work_cap = std::min(std::min(step->max_tiles, rows), h->max_slots + rows / PLORA_WORK_TOKENS);
+    if (work_cap == 0) return PLORA_OK;
+    const bool pdl = h->pdl && h->pdl_armed;
+    h->pdl_armed = true;
+    int total = 0;
+    for (auto& p : site.parts) total += p.rows;
+    CU(h, "site kernel",
+       plora_launch_site((const void*)(uintptr_t)x, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs, h->seg,
+                         (const plora_desc*)(uintptr_t)hook->table, (void*)(uintptr_t)y, ldy, f32_out, (int)site.parts.size(),
+                         h->max_rank, total, work_cap, h->status, pdl, as_stream(stream)));
+    if (h->mma_ok && rows >= step->run_min) {
+        CU(h, "shrink (tile path)",
+           plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
+                                   h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s, step->lds,
+                                   hook->parts * h->max_rank, std::max(1, rows / 64), h->status, h->pdl, as_stream(stream)));
+        CU(h, "expand (tile path)",
+           plora_launch_expand_mma((const float*)(uintptr_t)step->s, step->lds, (const int32_t*)(uintptr_t)step->segs, h->seg,
+                                   (const plora_desc*)(uintptr_t)hook->table, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
+                                   hook->max_rows, std::max(1, rows / 64), h->status, h->pdl, as_stream(stream)));
+    }
+    return PLORA_OK;
 }
 
 int plora_s_reduce(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, void* stream) {
@@ -693,7 +746,7 @@ int plora_s_reduce(plora_t* h, const plora_hook* hook, const plora_step* step, i
 }
 
 static int expand_impl(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
-                       int f32_out, bool reduced, void* stream) {
+                       int f32_out, bool reduced, bool early, void* stream) {
     if (!h || !hook || !step) return PLORA_ERR_ARG;
     if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
     if (hook->site < 0 || hook->site >= (int)h->sites.size()) return fail(h, PLORA_ERR_ARG, "hook names no site");
@@ -710,7 +763,7 @@ static int expand_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
                            reduced ? 1 : site.nsplit,
                            (const int32_t*)(uintptr_t)step->segs, h->seg, (const plora_desc*)(uintptr_t)hook->table,
                            (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap, h->status, pdl,
-                           as_stream(stream)));
+                           early, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min)
         CU(h, "expand (tile path)",
            plora_launch_expand_mma((const float*)(uintptr_t)step->s, step->lds, (const int32_t*)(uintptr_t)step->segs, h->seg,
@@ -778,6 +831,12 @@ int plora_join(plora_t* h, void* main_stream, void* side_stream) {
     if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
     CU(h, "join record", cudaEventRecord(h->join_ev, as_stream(side_stream)));
     CU(h, "join wait", cudaStreamWaitEvent(as_stream(main_stream), h->join_ev, 0));
+    return PLORA_OK;
+}
+
+int plora_set_apply_mode(plora_t* h, int mode) {
+    if (!h || mode < 0 || mode > 1) return PLORA_ERR_ARG;
+    h->apply_mode = mode;
     return PLORA_OK;
 }
 

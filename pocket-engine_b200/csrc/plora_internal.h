@@ -57,6 +57,7 @@ struct SiteInfo {
     }
     // K-split of the shrink: fixed per site so results do not depend on the batch
     int kchunk = 0, nsplit = 1;
+    bool cluster_ok = false;  // the one-kernel-per-layer cluster path fits this layer's shapes
 };
 
 struct SiteData {  // src/lora.rs:74-79
@@ -101,6 +102,8 @@ struct plora {
     mutable std::string err;
     int sm_count = 148;
     bool pdl = true;        // launch with programmatic stream serialization
+    int apply_mode = 0;     // plora_apply: 0 = shrink/expand pair with early loads, 1 = one cluster kernel per layer
+    bool site_ok = false;   // the cluster kernel's attributes were set
     bool fp8_ok = false;    // the fused FP8 layer can run
     bool mma_ok = false;    // the tensor-core tile kernels can run (max_rank <= 128 and the driver entry point exists)
     bool pdl_armed = false;  // false right after the step's grouping kernel: the next launch is a plain one
@@ -114,6 +117,12 @@ cudaError_t plora_launch_meta_tiles(const int32_t* cu, const int32_t* seq_slot, 
 cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status,
                                     cudaStream_t st);
 cudaError_t plora_kernels_init(const SegLayout& lay);
+cudaError_t plora_site_init();
+size_t plora_site_plan(int K, int parts, int max_rank, int total_rows, int* kchunk, int* rmax, int* a_bytes,
+                       int* x_bytes, int* b_bytes);
+cudaError_t plora_launch_site(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay, const plora_desc* table,
+                              void* y, int ldy, int f32_out, int parts, int max_rank, int total_rows, int work_cap,
+                              int* status, bool pdl, cudaStream_t st);
 cudaError_t plora_mma_init();
 cudaError_t plora_fp8_init(int max_rank);
 cudaError_t plora_launch_fp8_quant(const void* x, int rows, int ldx, int K, void* xq, float* st, cudaStream_t stream);
@@ -131,7 +140,8 @@ cudaError_t plora_launch_expand_mma(const float* S, int lds, const int32_t* segs
                                     int tile_cap, int* status, bool pdl, cudaStream_t st);
 cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay,
                                 const plora_desc* table, float* S, size_t s_stride_elems, int lds, int kchunk,
-                                int nsplit, int work_cap, int max_rank_total, int* status, bool pdl, cudaStream_t st);
+                                int nsplit, int work_cap, int max_rank_total, int* status, bool pdl, bool early,
+                                cudaStream_t st);
 cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, int nsplit, const int32_t* segs,
                                 SegLayout lay, const plora_desc* table, void* y, int ldy, int f32_out, int parts,
-                                int max_rows, int work_cap, int* status, bool pdl, cudaStream_t st);
+                                int max_rows, int work_cap, int* status, bool pdl, bool early, cudaStream_t st);

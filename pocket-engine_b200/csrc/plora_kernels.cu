@@ -335,32 +335,41 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
                                                                    const int* __restrict__ segs, SegLayout lay,
                                                                    const plora_desc* __restrict__ table,
                                                                    float* __restrict__ S, size_t s_stride, int lds,
-                                                                   int kchunk, int rps, int rt_max,
+                                                                   int kchunk, int rps, int rt_max, int early,
                                                                    int* __restrict__ status) {
+    // early != 0: the caller vouches that x was not written by the kernel right before this one, so x is
+    // fetched and the partial sums computed before the dependency wait; only the stores into S (which the
+    // expand before may still be reading) come after it.
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ __align__(8) uint64_t bars[2];
     __shared__ int stok[PLORA_WORK_TOKENS];
-    const int w = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int* work = segs + lay.work() + PLORA_WORK_WORDS * w;
-    // independent loads first: the header, the record's head, this lane's token
     const int n_work = segs[SEG_N_WORK];
-    const int slot = work[0], cnt = work[2];
-    const int mytok = work[4 + (lane & 15)];
-    TRACE(0);
     if (threadIdx.x == 0) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
         mbar_fence_init();
     }
-    if (w >= n_work) return pdl_exit_idle();
-    TRACE(1);
+    bool waited = false;
+    uint32_t phase = 0;
+    // In early mode the next kernels may start their own prologues at once: before their waits they touch only
+    // slabs, the step's grouping and activations that no kernel of this path writes; every store of the path
+    // comes after a wait, and every grid still waits for its predecessor before it completes.
+    if (early) pdl_trigger();
+    // the grid's z extent is capped: a block walks the work items z, z + gridDim.z, ...
+    for (int w = blockIdx.z; w < n_work; w += gridDim.z) {
+    const int* work = segs + lay.work() + PLORA_WORK_WORDS * w;
+    // independent loads first: the record's head, this lane's token
+    const int slot = work[0], cnt = work[2];
+    const int mytok = work[4 + (lane & 15)];
+    TRACE_K(1, 0);
+    TRACE_K(1, 1);
     const plora_desc& d = table[slot];
     const int rank = d.rank;
     const int split = blockIdx.x / rt_max, rt = blockIdx.x - split * rt_max;
     const int row0 = rt * rps;
-    if (row0 >= rank) return pdl_exit_idle();
-    TRACE(2);
+    if (row0 >= rank) continue;
+    TRACE_K(1, 2);
     const int rows = min(rps, rank - row0);
     const int k0 = split * kchunk, klen = min(kchunk, K - k0);
     const uint32_t kbytes = (uint32_t)klen * 2u;
@@ -374,23 +383,33 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
         __syncwarp();
         for (int r = lane; r < rows; r += 32) bulk_g2s(As + (size_t)r * kbytes, A + (size_t)r * K, kbytes, &bars[0]);
     }
-    TRACE(3);
-    pdl_wait();
-    TRACE(4);
-    pdl_trigger();
+    TRACE_K(1, 3);
+    if (!early && !waited) {
+        pdl_wait();
+        pdl_trigger();
+        waited = true;
+    }
+    TRACE_K(1, 4);
     if (warp == 0) {
         if (lane == 0) mbar_expect_tx(&bars[1], (uint32_t)cnt * kbytes);
         __syncwarp();
         if (lane < cnt) bulk_g2s(Xs + (size_t)lane * kbytes, X + (size_t)mytok * ldx + k0, kbytes, &bars[1]);
     }
-    if (!mbar_wait(&bars[0], 0, status)) return;
-    TRACE(5);
-    if (!mbar_wait(&bars[1], 0, status)) return;
-    TRACE(6);
+    if (!mbar_wait(&bars[0], phase, status)) return;
+    TRACE_K(1, 5);
+    if (!mbar_wait(&bars[1], phase, status)) return;
+    phase ^= 1;
+    TRACE_K(1, 6);
     float* Sout = S + (size_t)split * s_stride;
-    for (int tp = 0; tp < cnt; tp += 4) {
+    float res[PLORA_WORK_TOKENS / 4];  // rows == 16: one 4-row group per warp, one value per token pass
+#pragma unroll
+    for (int tq = 0; tq < PLORA_WORK_TOKENS / 4; tq++) {
+        const int tp = 4 * tq;
+        res[tq] = 0.f;
+        if (tp >= cnt) continue;
         const int nt = min(4, cnt - tp);
-        for (int n0 = warp * 4; n0 < rows; n0 += 16) {
+        {
+            const int n0 = warp * 4;
             float acc[16];
 #pragma unroll
             for (int i = 0; i < 16; i++) acc[i] = 0.f;
@@ -408,14 +427,24 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
                         for (int e = 0; e < 8; e++) acc[r * 4 + t] = fmaf(xf[t][e], af[e], acc[r * 4 + t]);
                 }
             }
-            const float v = reduce16(acc, lane);
-            if ((lane & 1) == 0) {
-                const int i = lane >> 1, r = i >> 2, t = i & 3;
-                if (t < nt) Sout[(size_t)stok[tp + t] * lds + row0 + n0 + r] = v;
-            }
+            res[tq] = reduce16(acc, lane);
         }
     }
-    TRACE(7);
+    if (!waited) {
+        pdl_wait();
+        pdl_trigger();
+        waited = true;
+    }
+    if ((lane & 1) == 0) {
+        const int i = lane >> 1, r = i >> 2, t = i & 3;
+#pragma unroll
+        for (int tq = 0; tq < PLORA_WORK_TOKENS / 4; tq++)
+            if (4 * tq + t < cnt) Sout[(size_t)stok[4 * tq + t] * lds + row0 + warp * 4 + r] = res[tq];
+    }
+    TRACE_K(1, 7);
+    __syncthreads();  // shared memory is reused by the next work item
+    }
+    if (!waited) pdl_exit_idle();
 }
 
 // Expand over gather work items. Grid (column blocks, parts, work items); 128 threads, two adjacent output
@@ -430,30 +459,38 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
                                                                       const int* __restrict__ segs, SegLayout lay,
                                                                       const plora_desc* __restrict__ table, void* Y,
                                                                       int ldy, int f32_out, int nc, int bs_bytes,
-                                                                      int* __restrict__ status) {
+                                                                      int early, int* __restrict__ status) {
+    // early != 0: the caller vouches that y was not written by the kernel right before this one, so the
+    // first tokens' y is fetched before the dependency wait.
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ __align__(8) uint64_t bar;
     __shared__ int stok[PLORA_WORK_TOKENS];
-    const int w = blockIdx.z;
-    const int* work = segs + lay.work() + PLORA_WORK_WORDS * w;
     const int n_work = segs[SEG_N_WORK];
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    bool waited = false;
+    uint32_t phase = 0;
+    // In early mode the next kernel may start its own prologue at once (see the shrink).
+    if (early) pdl_trigger();
+    // the grid's z extent is capped: a block walks the work items z, z + gridDim.z, ...
+    for (int w = blockIdx.z; w < n_work; w += gridDim.z) {
+    const int* work = segs + lay.work() + PLORA_WORK_WORDS * w;
     const int slot = work[0], cnt = work[2];
     const int mytok = work[4 + (threadIdx.x & 15)];
-    TRACE(0);
-    if (w >= n_work) return pdl_exit_idle();
-    TRACE(1);
+    TRACE_K(2, 0);
+    TRACE_K(2, 1);
     const plora_desc& d = table[slot];
     const int p = blockIdx.y, r = d.r[p];
-    if (r == 0) return pdl_exit_idle();
-    TRACE(2);
+    if (r == 0) continue;
+    TRACE_K(2, 2);
     const int rows = d.rows[p], c0 = blockIdx.x * nc;
-    if (c0 >= rows) return pdl_exit_idle();
+    if (c0 >= rows) continue;
     const int ncols = min(nc, rows - c0);
     unsigned char* Bs = dsm;
     float* ss = reinterpret_cast<float*>(dsm + bs_bytes);
     if (threadIdx.x == 0) {
-        mbar_init(&bar, 1);
-        mbar_fence_init();
         const uint32_t bytes = (uint32_t)ncols * (uint32_t)r * 2u;
         mbar_expect_tx(&bar, bytes);
         bulk_g2s(Bs, reinterpret_cast<const bf16*>(d.b[p]) + (size_t)c0 * r, bytes, &bar);
@@ -463,11 +500,13 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
     const int c = 2 * threadIdx.x;
     const bool mine = c < ncols;
     const size_t ycol = (size_t)d.off[p] + c0 + c;
-    TRACE(3);
-    pdl_wait();
-    TRACE(4);
-    pdl_trigger();
+    TRACE_K(2, 3);
     __syncthreads();
+    if (!early && !waited) {
+        pdl_wait();
+        pdl_trigger();
+        waited = true;
+    }
     // y of the first token group: on its way before anything else is waited for
     float2 yv[4];
     if (mine) {
@@ -480,6 +519,12 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
             }
         }
     }
+    if (!waited) {
+        pdl_wait();
+        pdl_trigger();
+        waited = true;
+    }
+    TRACE_K(2, 4);
     const int P = r >> 3;  // 16-byte pieces per row of B
     for (int i = threadIdx.x; i < cnt * r; i += blockDim.x) {
         const int t = i / r, j = i - t * r;
@@ -496,10 +541,11 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
         ss[t * P * EXP_SPAD + (j >> 3) * EXP_SPAD + (j & 7)] = acc;
     }
     __syncthreads();
-    TRACE(5);
-    if (!mbar_wait(&bar, 0, status)) return;
-    TRACE(6);
-    if (!mine) return;
+    TRACE_K(2, 5);
+    if (!mbar_wait(&bar, phase, status)) return;
+    phase ^= 1;
+    TRACE_K(2, 6);
+    if (mine) {
     const int rot = (P >= 8 ? threadIdx.x : threadIdx.x >> 1) % P;
     const unsigned char* b0 = Bs + (size_t)c * r * 2;
     const unsigned char* b1 = b0 + (size_t)r * 2;
@@ -552,7 +598,11 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
             }
         }
     }
-    TRACE(7);
+    }
+    TRACE_K(2, 7);
+    __syncthreads();  // shared memory is reused by the next work item
+    }
+    if (!waited) pdl_exit_idle();
 }
 
 }  // namespace
@@ -605,6 +655,8 @@ cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t 
 }
 }  // namespace
 
+#define PLORA_GRID_Z_CAP 256  // blocks along the work-item axis; more work items are walked in a loop
+
 // rows of A per block: 16 (one 4-row group per warp), so that a slot's rows spread over many blocks and
 // each block's copies are issued and consumed quickly
 int plora_shrink_rps(int kchunk) {
@@ -614,13 +666,14 @@ int plora_shrink_rps(int kchunk) {
 
 cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay,
                                 const plora_desc* table, float* S, size_t s_stride_elems, int lds, int kchunk,
-                                int nsplit, int work_cap, int max_rank_total, int* status, bool pdl, cudaStream_t st) {
+                                int nsplit, int work_cap, int max_rank_total, int* status, bool pdl, bool early,
+                                cudaStream_t st) {
     const int rps = plora_shrink_rps(kchunk);
     const int rt_max = (max_rank_total + rps - 1) / rps;
-    dim3 grid((unsigned)(nsplit * rt_max), 1, (unsigned)work_cap);
+    dim3 grid((unsigned)(nsplit * rt_max), 1, (unsigned)(work_cap < PLORA_GRID_Z_CAP ? work_cap : PLORA_GRID_Z_CAP));
     const size_t smem = (size_t)(rps + PLORA_WORK_TOKENS) * (size_t)kchunk * 2;
     return launch_pdl(plora_shrink_gather_kernel, grid, dim3(128), smem, st, pdl, reinterpret_cast<const bf16*>(x), ldx,
-                      K, segs, lay, table, S, s_stride_elems, lds, kchunk, rps, rt_max, status);
+                      K, segs, lay, table, S, s_stride_elems, lds, kchunk, rps, rt_max, early ? 1 : 0, status);
 }
 
 // output columns per block (two per thread): 512 for wide layers so the grid stays near one wave, 256
@@ -633,12 +686,13 @@ int plora_expand_nc(int max_rank, int max_rows) {
 
 cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, int nsplit, const int32_t* segs,
                                 SegLayout lay, const plora_desc* table, void* y, int ldy, int f32_out, int parts,
-                                int max_rows, int work_cap, int* status, bool pdl, cudaStream_t st) {
+                                int max_rows, int work_cap, int* status, bool pdl, bool early, cudaStream_t st) {
     const int max_rank = lds / PLORA_MAX_PARTS;
     const int nc = plora_expand_nc(max_rank, max_rows);
     const int bs_bytes = nc * max_rank * 2;
-    dim3 grid((unsigned)((max_rows + nc - 1) / nc), (unsigned)parts, (unsigned)work_cap);
+    dim3 grid((unsigned)((max_rows + nc - 1) / nc), (unsigned)parts,
+              (unsigned)(work_cap < PLORA_GRID_Z_CAP ? work_cap : PLORA_GRID_Z_CAP));
     const size_t smem = (size_t)bs_bytes + (size_t)PLORA_WORK_TOKENS * (size_t)(max_rank / 8) * EXP_SPAD * sizeof(float);
     return launch_pdl(plora_expand_gather_kernel, grid, dim3((unsigned)(nc / 2)), smem, st, pdl, S, s_stride_elems, lds, nsplit, segs,
-                      lay, table, y, ldy, f32_out, nc, bs_bytes, status);
+                      lay, table, y, ldy, f32_out, nc, bs_bytes, early ? 1 : 0, status);
 }

@@ -20,9 +20,10 @@ def test_plumbing_config_matches_the_oracle(pe, wls, meta, f32_out):
     harness.run_and_check(pe, wls.config1(), f32_out=f32_out, meta=meta)
 
 
+@pytest.mark.parametrize("fused", [False, "early", "cluster"], ids=["bracket", "apply-early", "apply-cluster"])
 @pytest.mark.parametrize("f32_out", [True, False])
-def test_decode_block_matches_the_oracle(pe, wls, f32_out):
-    res = harness.run_and_check(pe, wls.config2(), f32_out=f32_out, meta="device")
+def test_decode_block_matches_the_oracle(pe, wls, f32_out, fused):
+    res = harness.run_and_check(pe, wls.config2(), f32_out=f32_out, meta="device", fused=fused)
     assert len(res) == 4
 
 
@@ -117,22 +118,27 @@ def test_mixed_batch_equals_each_adapter_alone_bitwise(pe, wls):
     loras = harness.product_registry(pe, wl, max_tokens=64, max_seqs=64)
     xs = [wl.x_bits(si) for si in range(4)]
     yb = [wl.y_base(si) for si in range(4)]
-    mixed = harness.run_gpu(pe, loras, wl, False, xs=xs, y_base=yb)
+    for fused in (False, "early", "cluster"):
+        _mixed_equals_alone(pe, wls, wl, loras, xs, yb, fused=fused)
+    loras.close()
+
+
+def _mixed_equals_alone(pe, wls, wl, loras, xs, yb, fused):
+    mixed = harness.run_gpu(pe, loras, wl, False, xs=xs, y_base=yb, fused=fused)
     tslot = wl.token_slot()
     for s in range(1, 7):
         idx = np.nonzero(tslot == s)[0]
         if len(idx) == 0:
             continue
         alone = wls.Workload("alone", wl.sites, wl.ranks, wl.scale, [1] * len(idx), [s] * len(idx), wl.seed)
-        ya = harness.run_gpu(pe, loras, alone, False, xs=[x[idx] for x in xs], y_base=[y[idx] for y in yb])
+        ya = harness.run_gpu(pe, loras, alone, False, xs=[x[idx] for x in xs], y_base=[y[idx] for y in yb], fused=fused)
         for si in range(4):
-            assert np.array_equal(ya[si], mixed[si][idx]), (s, si)
+            assert np.array_equal(ya[si], mixed[si][idx]), (s, si, fused)
     # base-only tokens are untouched
     idx = np.nonzero(tslot == 0)[0]
     for si in range(4):
         want = pe.bf16_to_f32(pe.bf16_bits(yb[si][idx])).reshape(len(idx), -1)
         assert np.array_equal(mixed[si][idx], want)
-    loras.close()
 
 
 RAGGED = [
@@ -152,6 +158,8 @@ def test_ragged_and_edge_shapes(pe, wls, case):
     for f32_out in (True, False):
         for meta in ("host", "device"):
             harness.run_and_check(pe, wl, f32_out=f32_out, meta=meta)
+        harness.run_and_check(pe, wl, f32_out=f32_out, fused="early")
+        harness.run_and_check(pe, wl, f32_out=f32_out, fused="cluster")  # one cluster kernel per layer
 
 
 def test_untargeted_parts_and_sites_are_skipped(pe, wls, oracle):
@@ -162,6 +170,9 @@ def test_untargeted_parts_and_sites_are_skipped(pe, wls, oracle):
     res = harness.run_and_check(pe, wl, f32_out=True)
     assert set(res) == {0, 1}
     res = harness.run_and_check(pe, wl, f32_out=False)
+    for fused in ("early", "cluster"):
+        harness.run_and_check(pe, wl, f32_out=True, fused=fused)
+        harness.run_and_check(pe, wl, f32_out=False, fused=fused)
 
 
 def test_reference_kernels_agree(pe, wls, oracle):
@@ -223,6 +234,8 @@ def test_tensor_core_tile_path(pe, wls, case):
     wl = wls.Workload(name, sites, ranks, 1.0, rows, slots, 7)
     for f32_out in (True, False):
         harness.run_and_check(pe, wl, f32_out=f32_out, meta="device", run_min=64)
+        harness.run_and_check(pe, wl, f32_out=f32_out, meta="device", run_min=64, fused="early")
+        harness.run_and_check(pe, wl, f32_out=f32_out, meta="device", run_min=64, fused="cluster")
 
 
 def test_heterogeneous_ranks_reduced(pe, wls):
