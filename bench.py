@@ -592,18 +592,24 @@ def run_reference(args, rank, world):
         out["reference_gpu_kernels"] = reference_gpu(args)
     except Exception as e:  # no GPU, no fatbin, or a driver error: report, do not fail the arm
         out["reference_gpu_kernels"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    try:  # the same launcher and grids over the drop-in kernel image this repository builds
+        image = os.path.join(ROOT, "pocket-engine_b200", "plora_compat.fatbin")
+        out["drop_in_image_same_grids"] = reference_gpu(args, image) if os.path.exists(image) else {"unavailable": "not built"}
+    except Exception as e:
+        out["drop_in_image_same_grids"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
     return out
 
 
-def reference_gpu(args):
-    """pocket-engine's own lora_shrink / lora_expand (oracle/_ref fatbin) on the same workload and the same
-    rotation over pool copies, with the engine's grids and stream order; none of the product library runs."""
+def reference_gpu(args, image=None):
+    """pocket-engine's own lora_shrink / lora_expand (oracle/_ref fatbin; or another image with the same kernel
+    names) on the same workload and the same rotation over pool copies, with the engine's grids and stream order;
+    none of the product library's host code runs."""
     import importlib.util
     import torch
     spec = importlib.util.spec_from_file_location("plora_ref_kernels", os.path.join(ROOT, "oracle", "ref_kernels.py"))
     rk = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(rk)
-    if not rk.available():
+    if image is None and not rk.available():
         return {"unavailable": "oracle/_ref fatbin not built"}
     if not torch.cuda.is_available():
         return {"unavailable": "no GPU"}
@@ -611,7 +617,7 @@ def reference_gpu(args):
     pe = entry.load_package()  # synthetic inputs and bf16 helpers only
     wl = make_workload(args.workload, 0)
     torch.cuda.set_device(0)
-    ref = rk.RefKernels()
+    ref = rk.RefKernels(image)
     max_rank = (wl.max_rank + 15) // 16 * 16
     lds = 4 * max_rank
     adapters = [orc.OracleAdapter(wl.sites, wl.factors(i), wl.max_rank) for i in range(wl.n_adapters)]
@@ -678,7 +684,8 @@ def reference_gpu(args):
     peak, kind, _ = peaks()
     return {"value": wl.tokens * steps / (ms * 1e-3), "unit": UNIT, "us_per_step": 1e3 * ms / steps, "steps": steps,
             "achieved_gbs": work["bytes"] / (ms / steps * 1e-3) / 1e9, "frac_of_peak": work["bytes"] / (ms / steps * 1e-3) / 1e9 / peak,
-            "what": "pocket-engine's lora_shrink/lora_expand compiled for sm_100a, CUDA-graph replay, same rotation"}
+            "what": ("pocket-engine's lora_shrink/lora_expand compiled for sm_100a" if image is None else
+                     "plora_compat.fatbin (same kernel names and grids)") + ", CUDA-graph replay, same rotation"}
 
 
 def main():

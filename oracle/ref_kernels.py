@@ -15,10 +15,11 @@ def available():
 
 
 class RefKernels:
-    def __init__(self):
+    def __init__(self, path=None):
+        """path: another kernel image exporting lora_shrink / lora_expand with the reference's signatures."""
         from cuda.bindings import driver as drv
         self.drv = drv
-        with open(FATBIN, "rb") as f:
+        with open(path or FATBIN, "rb") as f:
             self._image = f.read()
         err, self.module = drv.cuModuleLoadData(self._image)
         self._ok(err, "cuModuleLoadData")

@@ -20,11 +20,29 @@ def stale():
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "plora.h")]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f != "plora_compat.cu"] + \
+        [os.path.join(HERE, "..", "include", "plora.h")]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+COMPAT = os.path.join(HERE, "plora_compat.fatbin")
+
+
+def build_compat(force=False):
+    """The drop-in kernel image under the reference's own kernel names (for POCKET_KERNELS=<fatbin>)."""
+    src = os.path.join(CSRC, "plora_compat.cu")
+    if not force and os.path.exists(COMPAT) and os.path.getmtime(COMPAT) >= os.path.getmtime(src):
+        return COMPAT
+    r = subprocess.run(["nvcc", "--fatbin", "-std=c++17", "-O3", "-lineinfo", "-gencode",
+                        "arch=compute_100a,code=sm_100a", src, "-o", COMPAT], capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("nvcc failed building plora_compat.fatbin")
+    return COMPAT
+
+
 def build(force=False, verbose=False):
+    build_compat(force)
     if not force and not stale():
         return LIB
     cmd = ["nvcc"] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + \

@@ -203,7 +203,7 @@ def read_tiles(loras):
     return w[:1 + 3 * int(w[0])]
 
 
-def run_reference_kernels(pe, loras, wl, f32_out, device=0, y_base=None, xs=None):
+def run_reference_kernels(pe, loras, wl, f32_out, device=0, y_base=None, xs=None, image=None):
     """pocket-engine's own lora_shrink / lora_expand (oracle/_ref) over the product's descriptor tables and
     tile words, with the engine's grids and its two-buffer S choreography (src/kernels/lora.cuh:69-73)."""
     import importlib.util
@@ -212,11 +212,11 @@ def run_reference_kernels(pe, loras, wl, f32_out, device=0, y_base=None, xs=None
     spec = importlib.util.spec_from_file_location("plora_ref_kernels", os.path.join(entry.ROOT, "oracle", "ref_kernels.py"))
     rk = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(rk)
-    if not rk.available():
+    if image is None and not rk.available():
         return None
     torch.cuda.set_device(device)
     dev = f"cuda:{device}"
-    ref = rk.RefKernels()
+    ref = rk.RefKernels(image)
     stream = torch.cuda.current_stream().cuda_stream
     loras.meta_upload(tiles_of(pe, wl, loras.max_lora_tiles()), stream)
     lds = loras.lds

@@ -207,6 +207,33 @@ def test_reference_kernels_agree(pe, wls, oracle):
         loras.close()
 
 
+def test_drop_in_kernel_image_under_the_engine_grids(pe, wls):
+    """plora_compat.fatbin exports lora_shrink / lora_expand with the reference's names, signatures and
+    two-buffer S contract; here it is driven exactly as the engine drives its own kernels
+    (src/linear.rs:853-921) and checked against the fp64 oracle."""
+    import os
+    image = os.path.join(os.path.dirname(pe.LIB_PATH), "plora_compat.fatbin")
+    assert os.path.exists(image)
+    ragged = wls.Workload("compat-ragged", [pe.Site.fused(0, 1024, [("a", 320), ("b", 130), ("c", 64)]),
+                                            pe.Site.fused(0, 1024, [("o", 200)])],
+                          [8, 40, 16], 1.5, [1, 15, 16, 17, 33, 2, 1], [1, 2, 0, 3, 1, 2, 3], 3)
+    for wl in (wls.config1(), wls.config2(), ragged):
+        loras = harness.product_registry(pe, wl)
+        table, _ = harness.oracle_registry(wl)
+        tiles = harness.tiles_of(pe, wl)
+        y64 = harness.oracle_f64(wl, table, tiles)
+        got = harness.run_reference_kernels(pe, loras, wl, True, image=image)
+        for si in range(len(wl.sites)):
+            mx, mn = harness.tolerance(got[si], y64[si])
+            assert mx <= 1e-5 and mn <= 1e-6, (wl.name, si, mx, mn)  # f32 S: far inside the stated tolerance
+        gotb = harness.run_reference_kernels(pe, loras, wl, False, image=image)
+        want = harness.oracle_rounded(wl, table, tiles, False, pe)
+        for si in range(len(wl.sites)):
+            ulp = harness.bf16_ulp_diff(gotb[si], want[si], pe)
+            assert ulp.max() <= 1 and (ulp > 0).mean() < 2e-3, (wl.name, si, int(ulp.max()))
+        loras.close()
+
+
 def test_prefill_segments_reduced(pe, wls):
     wl = wls.config3(seqs=3, seq_len=160, rank=64)
     for run_min in (64, 1 << 30):  # through the tensor-core tile kernels, and through the gather kernels alone
