@@ -39,10 +39,20 @@ static __device__ unsigned long long* g_plora_ring = nullptr;
         }                                                                                                \
     } while (0)
 #define TRACE(i) TRACE_K(PLORA_TRACE_TAG, i)
+#define TRACE_T(t, i)                                                                                    \
+    do {                                                                                                 \
+        if (threadIdx.x == (t) && g_plora_trace) {                                                       \
+            unsigned long long gt_;                                                                      \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                                      \
+            const size_t lb_ = (size_t)blockIdx.z * gridDim.y * gridDim.x + blockIdx.y * gridDim.x + blockIdx.x; \
+            g_plora_trace[lb_ * 16 + (i)] = gt_;                                                         \
+        }                                                                                                \
+    } while (0)
 #else
 #define PLORA_TRACE_SETTER(name)
 #define TRACE(i)
 #define TRACE_K(tag, i)
+#define TRACE_T(t, i)
 #endif
 
 namespace {

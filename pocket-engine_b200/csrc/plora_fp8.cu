@@ -23,6 +23,8 @@
 
 typedef __nv_bfloat16 bf16;
 
+PLORA_TRACE_SETTER(plora_trace_set_fp8)
+
 namespace {
 
 __device__ __forceinline__ bool elect_one() {
@@ -75,14 +77,6 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
             smem_u32(dst)),
         "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
         : "memory");
-}
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 // barrier among the 128 threads of the four adapter/epilogue warps only
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -153,7 +147,6 @@ __global__ void __launch_bounds__(128) plora_s_reduce_kernel(float* __restrict__
 #define F8_STAGES 3
 #define F8_STAGE_BYTES (F8_BM * F8_BK + F8_BN * F8_BK)
 #define F8_DPITCH (F8_BN + 1)  // floats per row of the adapter-term tile
-#define F8_RING 3              // slots' rows of B in flight
 
 struct Fp8Parts {
     int n;
@@ -161,20 +154,32 @@ struct Fp8Parts {
     int rows[PLORA_MAX_PARTS];
 };
 
+#define F8_NQ 8  // adapter work units in flight per block
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Warps: 0 = TMA producer of the GEMM ring, 1 = MMA issuer, 2..5 = adapter term + epilogue (128 threads, one
+// output column each in two halves of 64), 6 = producer of the adapter ring (bulk copies of each unit's rows of
+// B and S into a byte ring, first in first out).
 template <bool F32>
-__global__ void __launch_bounds__(192) plora_fp8_fused_kernel(const __grid_constant__ CUtensorMap xmap,
+__global__ void __launch_bounds__(224) plora_fp8_fused_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                const __grid_constant__ CUtensorMap wmap,
                                                                const float* __restrict__ st,
                                                                const float* __restrict__ sn, int T, int N, int K,
                                                                const int* __restrict__ segs, SegLayout lay,
                                                                const plora_desc* __restrict__ table, Fp8Parts parts,
                                                                const float* __restrict__ S, int lds, void* Y, int ldy,
-                                                               int bpitch, int* __restrict__ status) {
+                                                               int ring_bytes, int* __restrict__ status) {
     extern __shared__ unsigned char dsm_raw[];
-    __shared__ __align__(8) uint64_t full[F8_STAGES], empty[F8_STAGES], acc_bar;
+    __shared__ __align__(8) uint64_t full[F8_STAGES], empty[F8_STAGES], acc_bar, q_full[F8_NQ], q_empty[F8_NQ], lists_bar;
     __shared__ uint32_t tmem_slot;
-    __shared__ int s_slot[F8_BM], o_row[F8_BM], o_slot[F8_BM], g_start[F8_BM + 1];
-    __shared__ int s_ngroups;
+    __shared__ int s_slot[F8_BM], o_row[F8_BM], o_slot[F8_BM], u_first[F8_BM], u_n[F8_BM], u_rank[F8_BM];
+    __shared__ short u_r[F8_BM * PLORA_MAX_PARTS], u_roff[F8_BM * PLORA_MAX_PARTS];
+    __shared__ uint64_t u_b[F8_BM * PLORA_MAX_PARTS];
+    __shared__ int q_boff[F8_NQ * PLORA_MAX_PARTS], q_soff[F8_NQ];
+    __shared__ int s_nunits, s_wsum[4];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * F8_BN, m0 = blockIdx.y * F8_BM;
     unsigned char* ring = dsm_raw + ((1024u - (smem_u32(dsm_raw) & 1023u)) & 1023u);
@@ -185,7 +190,12 @@ __global__ void __launch_bounds__(192) plora_fp8_fused_kernel(const __grid_const
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
         }
+        for (int i = 0; i < F8_NQ; i++) {
+            mbar_init(&q_full[i], 1);
+            mbar_init(&q_empty[i], 2);  // one arrival per warp of the half that consumed the unit
+        }
         mbar_init(&acc_bar, 1);
+        mbar_init(&lists_bar, 128);
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(&tmem_slot, F8_BN);
@@ -196,9 +206,18 @@ __global__ void __launch_bounds__(192) plora_fp8_fused_kernel(const __grid_const
     const int nk = (K + F8_BK - 1) / F8_BK;
     pdl_wait();  // S, xq and the scales come from the kernels before
     pdl_trigger();
+    TRACE_T(0, 0);
+    // columns of this tile inside each part: [p_lo, p_hi) relative to the part
+    int p_lo[PLORA_MAX_PARTS], p_hi[PLORA_MAX_PARTS];
+#pragma unroll
+    for (int q = 0; q < PLORA_MAX_PARTS; q++) {
+        const int lo = max(n0, parts.off[q]), hi = min(n0 + F8_BN, parts.off[q] + parts.rows[q]);
+        p_lo[q] = q < parts.n && hi > lo ? lo - parts.off[q] : 0;
+        p_hi[q] = q < parts.n && hi > lo ? hi - parts.off[q] : 0;
+    }
 
     if (warp == 0) {
-        // ---- producer: one lane feeds the ring with TMA
+        // ---- producer: one lane feeds the GEMM ring with TMA
         if (lane == 0) {
             for (int ks = 0; ks < nk; ks++) {
                 const int stg = ks % F8_STAGES;
@@ -228,12 +247,84 @@ __global__ void __launch_bounds__(192) plora_fp8_fused_kernel(const __grid_const
             umma_commit(&acc_bar);
         }
         __syncwarp();
+    } else if (warp == 6) {
+        // ---- producer of the adapter ring: each unit's rows of B (one contiguous block per part) and of S
+        if (lane == 0 && mbar_wait(&lists_bar, 0, status)) {
+            const int nunits = s_nunits;
+            int head = 0, tail = 0, released = 0;
+            int ent_off[F8_NQ];
+            bool ok = true;
+            for (int u = 0; ok && u < nunits; u++) {
+                const int q = u % F8_NQ;
+                int bbytes[PLORA_MAX_PARTS], size = 0;
+#pragma unroll
+                for (int pp = 0; pp < PLORA_MAX_PARTS; pp++) {
+                    bbytes[pp] = (p_hi[pp] - p_lo[pp]) * (int)u_r[u * PLORA_MAX_PARTS + pp] * 2;
+                    size += bbytes[pp];
+                }
+                const int srow_bytes = u_rank[u] * 4;
+                size += u_n[u] * srow_bytes;
+                int pos = -1;
+                while (ok) {
+                    // release the oldest units while the queue slot is taken or the bytes do not fit
+                    const bool slot_free = u - released < F8_NQ;
+                    if (released == u) head = tail = 0;
+                    if (slot_free) {
+                        if (head >= tail) {
+                            if (head + size <= ring_bytes) pos = head;
+                            else if (size < tail) pos = 0;
+                        } else if (head + size < tail) {
+                            pos = head;
+                        }
+                    }
+                    if (pos >= 0) break;
+                    if (released == u) {  // a single unit larger than the ring: cannot happen by construction
+                        atomicMax(status, PLORA_ERR_CAPACITY);
+                        ok = false;
+                        break;
+                    }
+                    ok = mbar_wait(&q_empty[released % F8_NQ], (released / F8_NQ) & 1, status);
+                    released++;
+                    tail = released < u ? ent_off[released % F8_NQ] : head;
+                }
+                if (!ok) break;
+                ent_off[q] = pos;
+                head = pos + size;
+                unsigned char* dst = bring + pos;
+                int at = 0;
+#pragma unroll
+                for (int pp = 0; pp < PLORA_MAX_PARTS; pp++) {
+                    q_boff[q * PLORA_MAX_PARTS + pp] = pos + at;
+                    at += bbytes[pp];
+                }
+                q_soff[q] = pos + at;
+                if (size > 0) {
+                    mbar_expect_tx(&q_full[q], (uint32_t)size);
+                    at = 0;
+#pragma unroll
+                    for (int pp = 0; pp < PLORA_MAX_PARTS; pp++) {
+                        if (bbytes[pp] > 0) {
+                            const int r = u_r[u * PLORA_MAX_PARTS + pp];
+                            bulk_g2s(dst + at, reinterpret_cast<const bf16*>(u_b[u * PLORA_MAX_PARTS + pp]) + (size_t)p_lo[pp] * r,
+                                     (uint32_t)bbytes[pp], &q_full[q]);
+                            at += bbytes[pp];
+                        }
+                    }
+                    for (int rr = 0; rr < u_n[u]; rr++)
+                        bulk_g2s(dst + at + rr * srow_bytes, S + (size_t)(m0 + o_row[u_first[u] + rr]) * lds, (uint32_t)srow_bytes,
+                                 &q_full[q]);
+                } else {
+                    mbar_arrive(&q_full[q]);
+                }
+            }
+        }
     } else {
         // ---- adapter term of the tile, then the epilogue (threads 0..127 of this group)
         const int et = tid - 64;
         const int row = m0 + et;
         // tokens of the tile sorted by slot (stable); slot 0 (no adapter) and rows past T first
         const int myslot = row < T ? segs[lay.tslot() + row] : 0;
+        TRACE_T(64, 2);
         s_slot[et] = myslot;
         for (int i = et; i < F8_BM * F8_DPITCH; i += 128) delta[i] = 0.f;
         epi_sync();
@@ -245,75 +336,116 @@ __global__ void __launch_bounds__(192) plora_fp8_fused_kernel(const __grid_const
         o_row[rank] = et;
         o_slot[rank] = myslot;
         epi_sync();
-        const bool head = o_slot[et] != 0 && (et == 0 || o_slot[et - 1] != o_slot[et]);
-        // group starts, in order (a serial scan by one thread: at most 128 entries)
-        if (et == 0) {
-            int g = 0;
-            for (int i = 0; i < F8_BM; i++)
-                if (o_slot[i] != 0 && (i == 0 || o_slot[i - 1] != o_slot[i])) g_start[g++] = i;
-            g_start[g] = F8_BM;
-            s_ngroups = g;
+        // units of work: the rows of one slot, four at a time. Entry et of the sorted list starts a unit when it is
+        // the 1st, 5th, 9th ... row of its slot's group; unit numbers come from a prefix sum over the 128 entries.
+        {
+            const int sl = o_slot[et];
+            int g0 = et;
+            while (g0 > 0 && o_slot[g0 - 1] == sl) g0--;
+            const int uhead = sl != 0 && ((et - g0) & 3) == 0;
+            int incl = uhead;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const int w4 = (et >> 5);
+            if (lane == 31) s_wsum[w4] = incl;
+            epi_sync();
+            int base = 0;
+            for (int q = 0; q < w4; q++) base += s_wsum[q];
+            if (uhead) {
+                const int u = base + incl - 1;
+                int nrows = 1;
+                while (nrows < 4 && et + nrows < F8_BM && o_slot[et + nrows] == sl) nrows++;
+                u_first[u] = et;
+                u_n[u] = nrows;
+                // the unit's descriptor fields, fetched once
+                const plora_desc& d = table[sl];
+                u_rank[u] = d.rank;
+                for (int q = 0; q < PLORA_MAX_PARTS; q++) {
+                    u_r[u * PLORA_MAX_PARTS + q] = d.r[q];
+                    u_roff[u * PLORA_MAX_PARTS + q] = d.r_off[q];
+                    u_b[u * PLORA_MAX_PARTS + q] = d.b[q];
+                }
+            }
+            if (et == 127) s_nunits = base + incl;
         }
-        (void)head;
+        TRACE_T(64, 3);
+        mbar_arrive(&lists_bar);  // the ring's producer may start
         epi_sync();
-        const int ngroups = s_ngroups;
-        // two half-groups of 64 threads: each thread owns one output column and every second slot group
+        const int nunits = s_nunits;
+        // two halves of 64 threads: each thread owns one output column, each half every second unit
         const int half = et >> 6, c = et & 63;
         const int n = n0 + c;
         int p = -1;
         for (int q = 0; q < parts.n; q++)
             if (n >= parts.off[q] && n < parts.off[q] + parts.rows[q]) p = q;
-        const int nl = p >= 0 ? n - parts.off[p] : 0;
-        unsigned char* mybuf = bring + ((size_t)half * 64 + c) * bpitch;  // this thread's row in each ring slot
-        const size_t ring_stride = (size_t)128 * bpitch;
-        auto fetch = [&](int g) {  // group g's row of B for this column into ring slot (g / 2) % F8_RING
-            if (g < ngroups && p >= 0) {
-                const plora_desc& d = table[o_slot[g_start[g]]];
-                const int r = d.r[p];
-                const bf16* src = reinterpret_cast<const bf16*>(d.b[p]) + (size_t)nl * r;
-                unsigned char* dst = mybuf + (size_t)((g >> 1) % F8_RING) * ring_stride;
-                for (int j = 0; j < (r >> 3); j++) cp_async16(dst + j * 16, src + j * 8);
-            }
-            cp_async_commit();
-        };
-        for (int i = 0; i < F8_RING - 1; i++) fetch(half + 2 * i);
-        for (int g = half; g < ngroups; g += 2) {
-            fetch(g + 2 * (F8_RING - 1));
-            cp_async_wait<F8_RING - 1>();
-            if (p >= 0) {
-                const plora_desc& d = table[o_slot[g_start[g]]];
-                const int r = d.r[p], r_off = d.r_off[p];
-                const unsigned char* src = mybuf + (size_t)((g >> 1) % F8_RING) * ring_stride;
-                for (int i = g_start[g]; i < g_start[g + 1]; i++) {
-                    const int lr = o_row[i];
-                    const float* sp = S + (size_t)(m0 + lr) * lds + r_off;
-                    float acc = 0.f;
-                    for (int j = 0; j < r; j += 8) {
-                        float bf[8];
-                        unpack8(*reinterpret_cast<const uint4*>(src + j * 2), bf);
-                        const float4 s0 = __ldg(reinterpret_cast<const float4*>(sp + j));
-                        const float4 s1 = __ldg(reinterpret_cast<const float4*>(sp + j + 4));
-                        acc = fmaf(s0.x, bf[0], acc);
-                        acc = fmaf(s0.y, bf[1], acc);
-                        acc = fmaf(s0.z, bf[2], acc);
-                        acc = fmaf(s0.w, bf[3], acc);
-                        acc = fmaf(s1.x, bf[4], acc);
-                        acc = fmaf(s1.y, bf[5], acc);
-                        acc = fmaf(s1.z, bf[6], acc);
-                        acc = fmaf(s1.w, bf[7], acc);
+        const int cl = p >= 0 ? n - parts.off[p] - p_lo[p] : 0;  // column inside the tile's block of part p
+        TRACE_T(64, 4);
+        bool alive = true;
+        for (int u = half; u < nunits; u += 2) {
+            const int q = u % F8_NQ;
+            if (alive) alive = mbar_wait(&q_full[q], (u / F8_NQ) & 1, status);
+            if (alive && p >= 0) {
+                const int r = u_r[u * PLORA_MAX_PARTS + p], r_off = u_roff[u * PLORA_MAX_PARTS + p];
+                const unsigned char* src = bring + q_boff[q * PLORA_MAX_PARTS + p] + (size_t)cl * r * 2;
+                const int srow = u_rank[u];
+                const float* sbase = reinterpret_cast<const float*>(bring + q_soff[q]) + r_off;
+                const int nr = u_n[u];
+                // Four rows at once, two partial sums each: eight independent chains, because each of these warps
+                // runs alone on its scheduler and has nothing else to hide latencies with. Rows past nr repeat the
+                // last row (their sums are dropped).
+                float acc[4][2];
+#pragma unroll
+                for (int rr = 0; rr < 4; rr++) acc[rr][0] = acc[rr][1] = 0.f;
+                const float* srow_p[4];
+#pragma unroll
+                for (int rr = 0; rr < 4; rr++) srow_p[rr] = sbase + min(rr, nr - 1) * srow;
+                // Rows of B sit r * 2 bytes apart in the ring: walking them in step would put all lanes of a warp
+                // on the same banks, so each column starts at its own 16-byte piece and wraps around.
+                const int P = r >> 3;
+                int jp = P > 0 ? c % P : 0;
+#pragma unroll 2
+                for (int qq = 0; qq < P; qq++) {
+                    const int j = jp << 3;
+                    jp = jp + 1 == P ? 0 : jp + 1;
+                    float bf[8];
+                    unpack8(*reinterpret_cast<const uint4*>(src + j * 2), bf);
+                    float4 s0[4], s1[4];
+#pragma unroll
+                    for (int rr = 0; rr < 4; rr++) {
+                        s0[rr] = *reinterpret_cast<const float4*>(srow_p[rr] + j);
+                        s1[rr] = *reinterpret_cast<const float4*>(srow_p[rr] + j + 4);
                     }
-                    delta[lr * F8_DPITCH + c] = acc;  // one group per token row: written once
+#pragma unroll
+                    for (int rr = 0; rr < 4; rr++) {
+                        acc[rr][0] = fmaf(s0[rr].x, bf[0], acc[rr][0]);
+                        acc[rr][1] = fmaf(s0[rr].y, bf[1], acc[rr][1]);
+                        acc[rr][0] = fmaf(s0[rr].z, bf[2], acc[rr][0]);
+                        acc[rr][1] = fmaf(s0[rr].w, bf[3], acc[rr][1]);
+                        acc[rr][0] = fmaf(s1[rr].x, bf[4], acc[rr][0]);
+                        acc[rr][1] = fmaf(s1[rr].y, bf[5], acc[rr][1]);
+                        acc[rr][0] = fmaf(s1[rr].z, bf[6], acc[rr][0]);
+                        acc[rr][1] = fmaf(s1[rr].w, bf[7], acc[rr][1]);
+                    }
                 }
+#pragma unroll
+                for (int rr = 0; rr < 4; rr++)
+                    if (rr < nr && r > 0) delta[o_row[u_first[u] + rr] * F8_DPITCH + c] = acc[rr][0] + acc[rr][1];  // each row: one unit
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&q_empty[q]);  // this warp is done with the unit's bytes
         }
-        cp_async_wait<0>();
         epi_sync();
+        TRACE_T(64, 5);
         // ---- epilogue: accumulator row by row out of tensor memory, scaled, plus the adapter term
-        const bool ok = mbar_wait(&acc_bar, 0, status);
+        const bool ok = mbar_wait(&acc_bar, 0, status) && alive;
+        TRACE_T(64, 6);
         tc_fence_after();
         const int q4 = warp & 3;  // this warp's quarter of the 128 tensor-memory lanes
         const int lrow = q4 * 32 + lane;
-        const float srow = (m0 + lrow) < T ? st[m0 + lrow] : 0.f;
+        const float srow_scale = (m0 + lrow) < T ? st[m0 + lrow] : 0.f;
         if (ok) {
 #pragma unroll
             for (int cc = 0; cc < F8_BN; cc += 32) {
@@ -324,7 +456,7 @@ __global__ void __launch_bounds__(192) plora_fp8_fused_kernel(const __grid_const
                     const int col = n0 + cc + q;
                     const float sc = col < N ? __ldg(sn + col) : 0.f;
                     float* dp = delta + lrow * F8_DPITCH + cc + q;
-                    *dp = fmaf(__uint_as_float(v[q]), srow * sc, *dp);
+                    *dp = fmaf(__uint_as_float(v[q]), srow_scale * sc, *dp);
                 }
             }
         }
@@ -348,6 +480,7 @@ __global__ void __launch_bounds__(192) plora_fp8_fused_kernel(const __grid_const
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, F8_BN);
+    TRACE_T(64, 7);
 }
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -371,9 +504,11 @@ cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t 
     return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
 }
 
-size_t fused_smem(int max_rank) {
-    const int bpitch = max_rank * 2 + 16;
-    return 1024 + (size_t)F8_STAGES * F8_STAGE_BYTES + (size_t)F8_BM * F8_DPITCH * 4 + (size_t)F8_RING * 128 * bpitch;
+// Shared memory: GEMM stages, the adapter-term tile, and whatever is left (up to the launch limit) as the byte
+// ring of the adapter units.
+size_t fused_smem() { return (size_t)212 * 1024; }
+int fused_ring_bytes() {
+    return (int)(fused_smem() - 1024 - (size_t)F8_STAGES * F8_STAGE_BYTES - (size_t)F8_BM * F8_DPITCH * 4);
 }
 
 }  // namespace
@@ -387,11 +522,13 @@ cudaError_t plora_fp8_init(int max_rank) {
         if (!fn || q != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
         g_encode = reinterpret_cast<encode_tiled_fn>(fn);
     }
-    const size_t smem = fused_smem(max_rank);
-    if (smem > 227 * 1024) return cudaErrorInvalidValue;
-    cudaError_t e = cudaFuncSetAttribute(plora_fp8_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // the largest unit (64 columns x 4 parts' worst rank + 4 rows of S) must fit the ring a few times over
+    if ((size_t)F8_BN * max_rank * 2 + (size_t)4 * PLORA_MAX_PARTS * max_rank * 4 > (size_t)fused_ring_bytes() / 2)
+        return cudaErrorInvalidValue;
+    const int smem = (int)fused_smem();
+    cudaError_t e = cudaFuncSetAttribute(plora_fp8_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(plora_fp8_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return cudaFuncSetAttribute(plora_fp8_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
 }
 
 cudaError_t plora_launch_fp8_quant(const void* x, int rows, int ldx, int K, void* xq, float* st, cudaStream_t stream) {
@@ -439,12 +576,13 @@ cudaError_t plora_launch_fp8_fused(const void* xq, const float* st_, const void*
         parts.off[i] = i < n_parts ? part_off[i] : 0;
         parts.rows[i] = i < n_parts ? part_rows[i] : 0;
     }
-    const int bpitch = max_rank * 2 + 16;
+    (void)max_rank;
     dim3 grid((unsigned)((N + F8_BN - 1) / F8_BN), (unsigned)((T + F8_BM - 1) / F8_BM));
-    const size_t smem = fused_smem(max_rank);
+    const size_t smem = fused_smem();
+    const int ring_bytes = fused_ring_bytes();
     if (f32_out)
-        return launch_pdl(plora_fp8_fused_kernel<true>, grid, dim3(192), smem, stream, pdl, xmap, wmap, st_, sn, T, N, K,
-                          segs, lay, table, parts, S, lds, y, ldy, bpitch, status);
-    return launch_pdl(plora_fp8_fused_kernel<false>, grid, dim3(192), smem, stream, pdl, xmap, wmap, st_, sn, T, N, K, segs,
-                      lay, table, parts, S, lds, y, ldy, bpitch, status);
+        return launch_pdl(plora_fp8_fused_kernel<true>, grid, dim3(224), smem, stream, pdl, xmap, wmap, st_, sn, T, N, K,
+                          segs, lay, table, parts, S, lds, y, ldy, ring_bytes, status);
+    return launch_pdl(plora_fp8_fused_kernel<false>, grid, dim3(224), smem, stream, pdl, xmap, wmap, st_, sn, T, N, K, segs,
+                      lay, table, parts, S, lds, y, ldy, ring_bytes, status);
 }
