@@ -505,8 +505,31 @@ def run_tp(args, rank, world, local_rank):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
+    # one CUDA graph per copy (kernels and the NCCL all-reduces), replayed; eager launches if capture is refused
+    mode = "cuda graph per copy"
+    cap = torch.cuda.Stream(device=dev)
+    graphs = []
+    try:
+        with torch.cuda.stream(cap):
+            for c in range(copies):
+                block(c)
+            torch.cuda.synchronize()
+            real = stream
+            stream = cap
+            for c in range(copies):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=cap):
+                    block(c)
+                graphs.append(g)
+            torch.cuda.synchronize()
+        run = lambda i: graphs[i % copies].replay()
+    except Exception as e:  # noqa: BLE001
+        mode = f"eager launches (graph capture refused: {type(e).__name__})"
+        stream = torch.cuda.current_stream()
+        graphs = []
+        run = block
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    ms = _event_time(torch, stream, block, args.steps, args.warmup, barrier)
+    ms = _event_time(torch, stream, run, args.steps, args.warmup, barrier)
     # the collective alone: all-reduce of one [512, lds] plane
     s0 = sets[0]["lins"][1]._s[:sh.tokens]
     ar = _event_time(torch, stream, lambda i: torch.distributed.all_reduce(s0), 50, 5, barrier) / 50 if world > 1 else 0.0
@@ -527,7 +550,7 @@ def run_tp(args, rank, world, local_rank):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": wl.name, "tokens_per_step": sh.tokens, "adapters": sh.n_adapters,
                        "parallelism": f"tp{world}: column-parallel q, gate/up; row-parallel o, down",
-                       "collective": "NCCL all-reduce(sum) of the f32 shrink partials, 2 per step",
+                       "collective": "NCCL all-reduce(sum) of the f32 shrink partials, 2 per step", "launch": mode,
                        "l2": f"{copies} rotating copies"},
             "gpu_launches": (2 * ns + 2) * 2 * args.steps,
             "step_roofline": {"algorithmic_bytes_per_step_per_gpu": shw["bytes"], "achieved_gbs_per_gpu": shw["bytes"] / (us * 1e-6) / 1e9,
