@@ -242,6 +242,13 @@ int plora_join(plora_t* h, void* main_stream, void* side_stream);
  * tensor-core tile kernels (no counterpart in the engine, whose tiles are always 16 tokens). */
 int plora_set_run_min(plora_t* h, int tokens);
 
+/* The tile kernels cut a layer's inputs into a fixed number of ranges (a function of the layer's width and
+ * the adapter's rank alone), accumulate each on its own and add the results as a balanced tree, so that a
+ * token's result does not depend on what else is in the batch. `blocks` = 1, 2, 4 or 8 fixes how many thread
+ * blocks share the ranges of one 128-token tile; 0 (the default) lets the library choose from the step's row
+ * count. Every value gives bit-identical results. No counterpart in the engine. */
+int plora_set_tile_split(plora_t* h, int blocks);
+
 /* No counterpart in pocket-engine. One layer's adapter application (shrink, then expand, straight from the
  * engine's tile words and descriptor table) for callers that cannot allocate device memory: an engine whose
  * memory is fully claimed at start-up, code already inside a stream capture, a plugin host that forbids

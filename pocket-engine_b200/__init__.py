@@ -130,6 +130,7 @@ SYMBOLS = {
     "plora_fork": (_I, [_P, _P, _P]),
     "plora_join": (_I, [_P, _P, _P]),
     "plora_set_run_min": (_I, [_P, _I]),
+    "plora_set_tile_split": (_I, [_P, _I]),
     "plora_device_status": (_I, [_P]),
     "plora_site_apply_static": (_I, [_U64, _I, _I, _U64, _I, _U64, _I, _I, _I, _U64, _I, _I, _P]),
     "plora_static_scratch_bytes": (_U64, []),
@@ -408,6 +409,10 @@ class Loras:
 
     def set_run_min(self, tokens):
         self._check(lib.plora_set_run_min(self._h, tokens))
+
+    def set_tile_split(self, blocks):
+        """How many thread blocks share one 128-token tile's K ranges (0 = automatic); never changes a bit."""
+        self._check(lib.plora_set_tile_split(self._h, blocks))
 
     def device_status(self):
         self._check(lib.plora_device_status(self._h))

@@ -122,8 +122,41 @@ __global__ void __launch_bounds__(256) plora_fp8_quant_rows_kernel(const bf16* _
 // Adds the K-split partial planes of every gather token into plane 0, in split order. Grid (work items).
 __global__ void __launch_bounds__(128) plora_s_reduce_kernel(float* __restrict__ S, size_t s_stride, int lds, int nsplit,
                                                               const int* __restrict__ segs, SegLayout lay,
-                                                              const plora_desc* __restrict__ table) {
+                                                              const plora_desc* __restrict__ table, int work_cap,
+                                                              int tile_split, int K) {
     const int w = blockIdx.x;
+    if (w >= work_cap) {
+        // a tensor-core tile: the planes its shrink blocks wrote, added as a balanced tree
+        const int tile = w - work_cap;
+        if (tile >= segs[SEG_N_MMA]) return pdl_exit_idle();
+        const int* mt = segs + lay.mma() + 3 * tile;
+        const int start = mt[0], len = mt[1], rank = table[mt[2]].rank;
+        const int s_eff = rank ? min(tile_split, plora_tile_chunks(K, rank)) : 1;
+        if (s_eff <= 1) return pdl_exit_idle();
+        pdl_wait();
+        pdl_trigger();
+        const int q4 = rank >> 2;
+        for (int i = threadIdx.x; i < len * q4; i += 128) {
+            const int t = i / q4, j = i - t * q4;
+            float* sp = S + (size_t)(start + t) * lds + 4 * j;
+            float v[PLORA_TILE_SPLIT_MAX][4];
+#pragma unroll
+            for (int a = 0; a < PLORA_TILE_SPLIT_MAX; a++)
+                if (a < s_eff) {
+                    const float4 f = __ldcg(reinterpret_cast<const float4*>(sp + (size_t)a * s_stride));
+                    v[a][0] = f.x, v[a][1] = f.y, v[a][2] = f.z, v[a][3] = f.w;
+                }
+#pragma unroll
+            for (int stride = 1; stride < PLORA_TILE_SPLIT_MAX; stride <<= 1)
+#pragma unroll
+                for (int a = 0; a < PLORA_TILE_SPLIT_MAX; a += 2 * stride)
+                    if (a + stride < s_eff)
+#pragma unroll
+                        for (int q = 0; q < 4; q++) v[a][q] += v[a + stride][q];
+            *reinterpret_cast<float4*>(sp) = make_float4(v[0][0], v[0][1], v[0][2], v[0][3]);
+        }
+        return;
+    }
     const int n_work = segs[SEG_N_WORK];
     const int* work = segs + lay.work() + PLORA_WORK_WORDS * w;
     if (w >= n_work) return pdl_exit_idle();
@@ -539,10 +572,13 @@ cudaError_t plora_launch_fp8_quant(const void* x, int rows, int ldx, int K, void
 }
 
 cudaError_t plora_launch_s_reduce(float* S, size_t s_stride_elems, int lds, int nsplit, const int32_t* segs,
-                                  SegLayout lay, const plora_desc* table, int work_cap, bool pdl, cudaStream_t st) {
-    if (nsplit <= 1 || work_cap == 0) return cudaSuccess;
-    return launch_pdl(plora_s_reduce_kernel, dim3((unsigned)work_cap), dim3(128), 0, st, pdl, S, s_stride_elems, lds, nsplit,
-                      segs, lay, table);
+                                  SegLayout lay, const plora_desc* table, int work_cap, int tile_cap, int tile_split,
+                                  int K, bool pdl, cudaStream_t st) {
+    if (tile_split <= 1) tile_cap = 0;
+    if (nsplit <= 1 && tile_cap == 0) return cudaSuccess;
+    if (work_cap + tile_cap == 0) return cudaSuccess;
+    return launch_pdl(plora_s_reduce_kernel, dim3((unsigned)(work_cap + tile_cap)), dim3(128), 0, st, pdl, S, s_stride_elems,
+                      lds, nsplit, segs, lay, table, work_cap, tile_split, K);
 }
 
 cudaError_t plora_launch_fp8_fused(const void* xq, const float* st_, const void* wq, const float* sn, int T, int N, int K,

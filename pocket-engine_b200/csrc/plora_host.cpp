@@ -162,7 +162,7 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
     size_t entries = h->sites.size() * (size_t)(max_slots + 1);  // src/lora.rs:489
     h->table_bytes = entries * sizeof(plora_desc);
     h->s_stride = (size_t)max_tokens * (size_t)h->lds * 4;  // src/model.rs:1613
-    h->s_bytes = h->s_stride * (size_t)std::max(2, h->nsplit_max);
+    h->s_bytes = h->s_stride * (size_t)std::max(PLORA_TILE_SPLIT_MAX, h->nsplit_max);
     if (device < 0) {
         // Layout-only handle: adapters can be prepared and inspected, nothing can be uploaded or run.
         h->host_tables = (plora_desc*)calloc(entries, sizeof(plora_desc));
@@ -644,6 +644,16 @@ int plora_step_begin(plora_t* h, int max_tiles, int decode, void* stream, plora_
 
 // ------------------------------------------------------------------ bracket
 
+// How many blocks share the K chunks of one tensor-core tile: enough to fill the SMs when a step has few
+// tiles (prompt chunks inside a decode batch), one when there are plenty. Any value gives the same bits.
+static int tile_split(const plora_t* h, int rows) {
+    if (h->tile_split_force) return h->tile_split_force;
+    const int est = std::max(1, rows / PLORA_MMA_TOKENS);
+    int s = 1;
+    while (s < PLORA_TILE_SPLIT_MAX && 2 * s * est <= h->sm_count) s <<= 1;
+    return s;
+}
+
 static int shrink_impl(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, int rows, bool early,
                        void* stream);
 
@@ -673,13 +683,15 @@ static int shrink_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
     if (h->mma_ok && rows >= step->run_min)
         CU(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
-                                   h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s, step->lds,
-                                   hook->parts * h->max_rank, std::max(1, rows / 64), h->status, h->pdl, as_stream(stream)));
+                                   h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s,
+                                   (size_t)(step->s_stride / 4), step->lds, hook->parts * h->max_rank, std::max(1, rows / 64),
+                                   tile_split(h, rows), h->status, h->pdl, as_stream(stream)));
     return PLORA_OK;
 }
 
 static int expand_impl(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
                        int f32_out, bool reduced, bool early, void* stream);
+
 
 int plora_expand(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
                  int f32_out, void* stream) {
@@ -720,10 +732,12 @@ int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint
     if (h->mma_ok && rows >= step->run_min) {
         CU(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
-                                   h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s, step->lds,
-                                   hook->parts * h->max_rank, std::max(1, rows / 64), h->status, h->pdl, as_stream(stream)));
+                                   h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s,
+                                   (size_t)(step->s_stride / 4), step->lds, hook->parts * h->max_rank, std::max(1, rows / 64),
+                                   tile_split(h, rows), h->status, h->pdl, as_stream(stream)));
         CU(h, "expand (tile path)",
-           plora_launch_expand_mma((const float*)(uintptr_t)step->s, step->lds, (const int32_t*)(uintptr_t)step->segs, h->seg,
+           plora_launch_expand_mma((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.cols,
+                                   tile_split(h, rows), (const int32_t*)(uintptr_t)step->segs, h->seg,
                                    (const plora_desc*)(uintptr_t)hook->table, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
                                    hook->max_rows, std::max(1, rows / 64), h->status, h->pdl, as_stream(stream)));
     }
@@ -741,7 +755,9 @@ int plora_s_reduce(plora_t* h, const plora_hook* hook, const plora_step* step, i
     h->pdl_armed = true;
     CU(h, "S reduce", plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
                                             (const int32_t*)(uintptr_t)step->segs, h->seg,
-                                            (const plora_desc*)(uintptr_t)hook->table, work_cap, pdl, as_stream(stream)));
+                                            (const plora_desc*)(uintptr_t)hook->table, work_cap,
+                                            h->mma_ok && rows >= step->run_min ? std::max(1, rows / 64) : 0,
+                                            tile_split(h, rows), site.cols, pdl, as_stream(stream)));
     return PLORA_OK;
 }
 
@@ -766,7 +782,8 @@ static int expand_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
                            early, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min)
         CU(h, "expand (tile path)",
-           plora_launch_expand_mma((const float*)(uintptr_t)step->s, step->lds, (const int32_t*)(uintptr_t)step->segs, h->seg,
+           plora_launch_expand_mma((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.cols,
+                                   reduced ? 1 : tile_split(h, rows), (const int32_t*)(uintptr_t)step->segs, h->seg,
                                    (const plora_desc*)(uintptr_t)hook->table, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
                                    hook->max_rows, std::max(1, rows / 64), h->status, h->pdl, as_stream(stream)));
     return PLORA_OK;
@@ -806,7 +823,9 @@ int plora_linear_fp8_fused(plora_t* h, const plora_hook* hook, const plora_step*
     h->pdl_armed = true;
     CU(h, "S reduce", plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
                                             (const int32_t*)(uintptr_t)step->segs, h->seg,
-                                            (const plora_desc*)(uintptr_t)hook->table, work_cap, pdl, as_stream(stream)));
+                                            (const plora_desc*)(uintptr_t)hook->table, work_cap,
+                                            h->mma_ok && rows >= step->run_min ? std::max(1, rows / 64) : 0,
+                                            tile_split(h, rows), site.cols, pdl, as_stream(stream)));
     CU(h, "fused fp8 layer",
        plora_launch_fp8_fused((const void*)(uintptr_t)xq, (const float*)(uintptr_t)st, (const void*)(uintptr_t)wq,
                               (const float*)(uintptr_t)sn, rows, width, site.cols, (const int32_t*)(uintptr_t)step->segs,
@@ -845,6 +864,13 @@ int plora_set_run_min(plora_t* h, int tokens) {
     if (!h->mma_ok && tokens < (1 << 30))
         return fail(h, PLORA_ERR_CONFIG, "the tile path needs a device handle and max_rank <= 128");
     h->seg.run_min = tokens;
+    return PLORA_OK;
+}
+
+int plora_set_tile_split(plora_t* h, int blocks) {
+    if (!h || (blocks != 0 && blocks != 1 && blocks != 2 && blocks != 4 && blocks != 8))
+        return fail(h, PLORA_ERR_ARG, "tile split must be 0 (automatic), 1, 2, 4 or 8");
+    h->tile_split_force = blocks;
     return PLORA_OK;
 }
 

@@ -102,6 +102,7 @@ struct plora {
     mutable std::string err;
     int sm_count = 148;
     bool pdl = true;        // launch with programmatic stream serialization
+    int tile_split_force = 0;  // plora_set_tile_split: 0 = chosen per launch
     int apply_mode = 0;     // plora_apply: 0 = shrink/expand pair with early loads, 1 = one cluster kernel per layer
     bool site_ok = false;   // the cluster kernel's attributes were set
     bool fp8_ok = false;    // the fused FP8 layer can run
@@ -110,6 +111,21 @@ struct plora {
 };
 
 size_t plora_meta_group_smem(const SegLayout& lay);
+
+// The tensor-core tile path cuts a site's K inputs into `chunks` ranges that are accumulated separately (each in
+// its own tensor-memory accumulator, inputs in order) and then added as a balanced binary tree. The count is a
+// function of the site and of the slot's total rank only, so a token's result never depends on the batch; a
+// launch may hand the chunks to 1, 2, 4 or 8 blocks (each an aligned subtree, one plane of S per block, the
+// planes tree-summed by the reader) and every such choice gives the same bits. At most 256 accumulator
+// columns per block, so that two blocks share an SM's tensor memory, and at least 8 steps of 64 inputs per chunk.
+#define PLORA_TILE_SPLIT_MAX 8
+__host__ __device__ inline int plora_tile_cols(int R) { return R <= 32 ? 32 : R <= 64 ? 64 : R <= 128 ? 128 : R <= 256 ? 256 : 512; }
+__host__ __device__ inline int plora_tile_chunks(int K, int R) {
+    const int nk = (K + 63) / 64, rc = plora_tile_cols(R);
+    int c = PLORA_TILE_SPLIT_MAX;
+    while (c > 1 && (c * 8 > nk || c * rc > 256)) c >>= 1;
+    return c;
+}
 
 // ---- kernel launchers (plora_kernels.cu); each returns a cudaError_t from the launch ----
 cudaError_t plora_launch_meta_tiles(const int32_t* cu, const int32_t* seq_slot, int n_seqs, int32_t* tiles,
@@ -127,17 +143,20 @@ cudaError_t plora_mma_init();
 cudaError_t plora_fp8_init(int max_rank);
 cudaError_t plora_launch_fp8_quant(const void* x, int rows, int ldx, int K, void* xq, float* st, cudaStream_t stream);
 cudaError_t plora_launch_s_reduce(float* S, size_t s_stride_elems, int lds, int nsplit, const int32_t* segs,
-                                  SegLayout lay, const plora_desc* table, int work_cap, bool pdl, cudaStream_t st);
+                                  SegLayout lay, const plora_desc* table, int work_cap, int tile_cap, int tile_split,
+                                  int K, bool pdl, cudaStream_t st);
 cudaError_t plora_launch_fp8_fused(const void* xq, const float* st_, const void* wq, const float* sn, int T, int N, int K,
                                    const int32_t* segs, SegLayout lay, const plora_desc* table, int n_parts,
                                    const int* part_off, const int* part_rows, const float* S, int lds, void* y, int ldy,
                                    int f32_out, int max_rank, int* status, bool pdl, cudaStream_t stream);
 cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, const int32_t* segs, SegLayout lay,
-                                    const plora_desc* table, float* S, int lds, int max_rank_total, int tile_cap,
-                                    int* status, bool pdl, cudaStream_t st);
-cudaError_t plora_launch_expand_mma(const float* S, int lds, const int32_t* segs, SegLayout lay,
-                                    const plora_desc* table, void* y, int ldy, int f32_out, int parts, int max_rows,
-                                    int tile_cap, int* status, bool pdl, cudaStream_t st);
+                                    const plora_desc* table, float* S, size_t s_stride_elems, int lds,
+                                    int max_rank_total, int tile_cap, int tile_split, int* status, bool pdl,
+                                    cudaStream_t st);
+cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int lds, int K, int tile_split,
+                                    const int32_t* segs, SegLayout lay, const plora_desc* table, void* y, int ldy,
+                                    int f32_out, int parts, int max_rows, int tile_cap, int* status, bool pdl,
+                                    cudaStream_t st);
 cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay,
                                 const plora_desc* table, float* S, size_t s_stride_elems, int lds, int kchunk,
                                 int nsplit, int work_cap, int max_rank_total, int* status, bool pdl, bool early,

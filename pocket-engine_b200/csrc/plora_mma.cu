@@ -72,6 +72,29 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 8 consecutive columns, without the wait (several loads, then one tmem_ld_wait)
+__device__ __forceinline__ void tmem_ld8_nowait(uint32_t taddr, float* v) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// v[0] = balanced binary tree sum of v[0..n), n a power of two <= 8 (W values per item)
+template <int W>
+__device__ __forceinline__ void tree_sum(float (&v)[PLORA_TILE_SPLIT_MAX][W], int n) {
+#pragma unroll
+    for (int stride = 1; stride < PLORA_TILE_SPLIT_MAX; stride <<= 1)
+#pragma unroll
+        for (int a = 0; a < PLORA_TILE_SPLIT_MAX; a += 2 * stride)
+            if (a + stride < n)
+#pragma unroll
+                for (int q = 0; q < W; q++) v[a][q] += v[a + stride][q];
+}
+
 // Shared-memory matrix descriptor: start address, leading (K direction) and stride (8-row group) byte
 // offsets, descriptor version 1, swizzle mode in bits 61-63 (0 none, 2 = 128 bytes).
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo, uint32_t swizzle) {
@@ -109,7 +132,9 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 #define EXP_TPAD 66  // floats per row of the epilogue's transpose tile (64 columns + 2 of padding)
 
 // ------------------------------------------------------------------------------------------------------
-// Shrink of one 128-token tile. Grid (1, 1, tiles); 128 threads. K is walked in steps of 64 inputs through a
+// Shrink of one 128-token tile. Grid (split, 1, tiles); 128 threads. The slot's K chunks (plora_tile_chunks) are
+// shared evenly by min(split, chunks) blocks; each block accumulates its chunks in separate accumulators, adds
+// them as a tree and writes plane blockIdx.x of S. K is walked in steps of 64 inputs through a
 // ring of stages; thread 0 issues the x tile by TMA, all threads copy the slab's rows for the same 64
 // inputs into the 128-byte-swizzled layout the MMA reads; one elected thread issues the MMAs; the stage is
 // refilled one step later, after its MMAs have been committed. The f32 result leaves tensor memory one
@@ -120,8 +145,9 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_constant__ CUtensorMap xmap, int K,
                                                                 const int* __restrict__ segs, SegLayout lay,
                                                                 const plora_desc* __restrict__ table,
-                                                                float* __restrict__ S, int lds, int nstage,
-                                                                int stage_bytes, int* __restrict__ status) {
+                                                                float* __restrict__ S, size_t s_stride, int lds,
+                                                                int ksplit, int nstage, int stage_bytes,
+                                                                int* __restrict__ status) {
     extern __shared__ unsigned char dsm_raw[];
     __shared__ __align__(8) uint64_t full[4], done[4], acc_bar;
     __shared__ uint32_t tmem_slot;
@@ -134,11 +160,16 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
     const plora_desc& d = table[slot];
     const int R = d.rank;
     if (R == 0) return pdl_exit_idle();
+    const int n_chunks = plora_tile_chunks(K, R);
+    const int s_eff = min(ksplit, n_chunks);
+    if ((int)blockIdx.x >= s_eff) return pdl_exit_idle();
+    const int n_acc = n_chunks / s_eff;  // accumulators (chunks) of this block
     const bf16* A = reinterpret_cast<const bf16*>(d.a);
     const int tid = threadIdx.x, warp = tid >> 5;
     // 1024-byte aligned stage ring: [x tile 16 KB][slab rows R x 128 B]
     unsigned char* ring = dsm_raw + ((1024u - (smem_u32(dsm_raw) & 1023u)) & 1023u);
-    const uint32_t ncols = R <= 32 ? 32u : R <= 64 ? 64u : R <= 128 ? 128u : R <= 256 ? 256u : 512u;
+    const uint32_t acc_cols = (uint32_t)plora_tile_cols(R);
+    const uint32_t ncols = acc_cols * (uint32_t)n_acc;
     if (tid == 0) {
         for (int i = 0; i < nstage; i++) {
             mbar_init(&full[i], 1);
@@ -153,7 +184,10 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    const int nk = (K + SHR_KSTEP - 1) / SHR_KSTEP;
+    const int nk_all = (K + SHR_KSTEP - 1) / SHR_KSTEP;
+    const int spc = (nk_all + n_chunks - 1) / n_chunks;  // steps per chunk
+    const int k_first = (int)blockIdx.x * n_acc * spc;
+    const int nk = min(nk_all, k_first + n_acc * spc) - k_first;  // this block's steps
     const int chunks = R * 8;  // 16-byte chunks of the slab per step
     pdl_wait();  // x comes from the kernels before
     pdl_trigger();
@@ -162,7 +196,7 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
         const int st = ks % nstage;
         unsigned char* xs = ring + (size_t)st * stage_bytes;
         unsigned char* as = xs + SHR_X_BYTES;
-        const int k0 = ks * SHR_KSTEP;
+        const int k0 = (k_first + ks) * SHR_KSTEP;
         if (tid == 0) {
             mbar_expect_tx(&full[st], SHR_X_BYTES);
             tma_load_2d(xs, &xmap, k0, start, &full[st]);
@@ -195,14 +229,16 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
                     tc_fence_after();
                     const uint32_t xs = smem_u32(ring + (size_t)st * stage_bytes);
                     const uint32_t as = xs + SHR_X_BYTES;
+                    const int acc = it / spc, first = it - acc * spc;  // a chunk starts a fresh accumulator
+                    const uint32_t dacc = tmem + (uint32_t)acc * acc_cols;
 #pragma unroll
                     for (int kk = 0; kk < SHR_KSTEP / 16; kk++) {
                         const uint64_t da = umma_desc(xs + kk * 32, 16, 1024, 2);
                         const uint64_t db = umma_desc(as + kk * 32, 16, 1024, 2);
-                        umma_bf16(tmem, da, db, idesc_lo, (it | kk) != 0);
+                        umma_bf16(dacc, da, db, idesc_lo, (first | kk) != 0);
                         if (R > 256) {
                             const uint64_t db2 = umma_desc(as + 256 * 128 + kk * 32, 16, 1024, 2);
-                            umma_bf16(tmem + 256, da, db2, idesc_hi, (it | kk) != 0);
+                            umma_bf16(dacc + 256, da, db2, idesc_hi, (first | kk) != 0);
                         }
                     }
                     umma_commit(&done[st]);
@@ -227,8 +263,21 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
     if (ok && !s_fail) {
         tc_fence_after();
         const int row = tid;
-        float* out = S + (size_t)(start + row) * lds;
-        for (int c = 0; c < R; c += 32) {
+        float* out = S + (size_t)blockIdx.x * s_stride + (size_t)(start + row) * lds;
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        for (int c = 0; n_acc > 1 && c < R; c += 8) {
+            float v[PLORA_TILE_SPLIT_MAX][8];
+#pragma unroll
+            for (int a = 0; a < PLORA_TILE_SPLIT_MAX; a++)
+                if (a < n_acc) tmem_ld8_nowait(lane_base + (uint32_t)a * acc_cols + c, v[a]);
+            tmem_ld_wait();
+            tree_sum<8>(v, n_acc);
+            if (row < len) {
+                *reinterpret_cast<float4*>(out + c) = make_float4(v[0][0], v[0][1], v[0][2], v[0][3]);
+                *reinterpret_cast<float4*>(out + c + 4) = make_float4(v[0][4], v[0][5], v[0][6], v[0][7]);
+            }
+        }
+        for (int c = 0; n_acc == 1 && c < R; c += 32) {
             uint32_t v[32];
             tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
             if (row < len) {
@@ -264,7 +313,8 @@ __device__ __forceinline__ void load_rows_f32(float2 (&raw)[32], const float* y,
 }
 
 template <bool F32>
-__global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __restrict__ S, int lds,
+__global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __restrict__ S, size_t s_stride, int lds,
+                                                                int K, int ksplit,
                                                                 const int* __restrict__ segs, SegLayout lay,
                                                                 const plora_desc* __restrict__ table, void* Y,
                                                                 int ldy, int nb_per_cta, int op_bytes,
@@ -321,11 +371,26 @@ __global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __re
         const int row = tid;
         const bool valid = row < len;
         const float* sp = S + (size_t)(start + (valid ? row : 0)) * lds + d.r_off[p];
+        const int s_eff = min(ksplit, plora_tile_chunks(K, d.rank));  // planes the shrink wrote for this slot
         unsigned char* ahi = Ahi + (size_t)(row >> 3) * sbo + (row & 7) * 16;
         unsigned char* alo = Alo + (size_t)(row >> 3) * sbo + (row & 7) * 16;
         for (int j = 0; j < P; j++) {
             float f[8];
-            if (valid) {
+            if (valid && s_eff > 1) {
+                float v[PLORA_TILE_SPLIT_MAX][8];
+#pragma unroll
+                for (int s = 0; s < PLORA_TILE_SPLIT_MAX; s++)
+                    if (s < s_eff) {
+                        const float* q = sp + (size_t)s * s_stride + j * 8;
+                        const float4 a = __ldcg(reinterpret_cast<const float4*>(q));
+                        const float4 b = __ldcg(reinterpret_cast<const float4*>(q + 4));
+                        v[s][0] = a.x, v[s][1] = a.y, v[s][2] = a.z, v[s][3] = a.w;
+                        v[s][4] = b.x, v[s][5] = b.y, v[s][6] = b.z, v[s][7] = b.w;
+                    }
+                tree_sum<8>(v, s_eff);
+#pragma unroll
+                for (int e = 0; e < 8; e++) f[e] = v[0][e];
+            } else if (valid) {
                 const float4 a = __ldcg(reinterpret_cast<const float4*>(sp + j * 8));
                 const float4 b = __ldcg(reinterpret_cast<const float4*>(sp + j * 8 + 4));
                 f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
@@ -492,8 +557,9 @@ cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t 
 }  // namespace
 
 cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, const int32_t* segs, SegLayout lay,
-                                    const plora_desc* table, float* S, int lds, int max_rank_total, int tile_cap,
-                                    int* status, bool pdl, cudaStream_t st) {
+                                    const plora_desc* table, float* S, size_t s_stride_elems, int lds,
+                                    int max_rank_total, int tile_cap, int tile_split, int* status, bool pdl,
+                                    cudaStream_t st) {
     if (!g_encode) return cudaErrorNotSupported;
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -509,13 +575,14 @@ cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, con
     nstage = nstage > 4 ? 4 : nstage;
     if (nstage < 2) return cudaErrorInvalidValue;
     const size_t smem = (size_t)nstage * stage_bytes + 1024;
-    return launch_pdl(plora_shrink_mma_kernel, dim3(1, 1, (unsigned)tile_cap), dim3(128), smem, st, pdl, map, K, segs, lay,
-                      table, S, lds, nstage, stage_bytes, status);
+    return launch_pdl(plora_shrink_mma_kernel, dim3((unsigned)tile_split, 1, (unsigned)tile_cap), dim3(128), smem, st, pdl,
+                      map, K, segs, lay, table, S, s_stride_elems, lds, tile_split, nstage, stage_bytes, status);
 }
 
-cudaError_t plora_launch_expand_mma(const float* S, int lds, const int32_t* segs, SegLayout lay,
-                                    const plora_desc* table, void* y, int ldy, int f32_out, int parts, int max_rows,
-                                    int tile_cap, int* status, bool pdl, cudaStream_t st) {
+cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int lds, int K, int tile_split,
+                                    const int32_t* segs, SegLayout lay, const plora_desc* table, void* y, int ldy,
+                                    int f32_out, int parts, int max_rows, int tile_cap, int* status, bool pdl,
+                                    cudaStream_t st) {
     const int max_rank = lds / PLORA_MAX_PARTS;
     const int op_bytes = MMA_M * max_rank * 2;
     const int nblocks = (max_rows + 127) / 128;
@@ -527,8 +594,8 @@ cudaError_t plora_launch_expand_mma(const float* S, int lds, const int32_t* segs
     size_t smem = (size_t)4 * op_bytes + (size_t)4 * 32 * EXP_TPAD * sizeof(float);
     if (smem < 48 * 1024) smem = 48 * 1024;
     if (f32_out)
-        return launch_pdl(plora_expand_mma_kernel<true>, grid, dim3(128), smem, st, pdl, S, lds, segs, lay, table, y, ldy,
-                          nb_per_cta, op_bytes, status);
-    return launch_pdl(plora_expand_mma_kernel<false>, grid, dim3(128), smem, st, pdl, S, lds, segs, lay, table, y, ldy,
-                      nb_per_cta, op_bytes, status);
+        return launch_pdl(plora_expand_mma_kernel<true>, grid, dim3(128), smem, st, pdl, S, s_stride_elems, lds, K,
+                          tile_split, segs, lay, table, y, ldy, nb_per_cta, op_bytes, status);
+    return launch_pdl(plora_expand_mma_kernel<false>, grid, dim3(128), smem, st, pdl, S, s_stride_elems, lds, K,
+                      tile_split, segs, lay, table, y, ldy, nb_per_cta, op_bytes, status);
 }

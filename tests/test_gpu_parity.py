@@ -265,6 +265,40 @@ def test_tensor_core_tile_path(pe, wls, case):
         harness.run_and_check(pe, wl, f32_out=f32_out, meta="device", run_min=64, fused="cluster")
 
 
+def test_tile_split_never_changes_a_bit(pe, wls):
+    """However many thread blocks share a tile's K ranges, and whether the prompt runs alone or inside a larger
+    batch, the tile path gives the same bits: the K ranges and the order they are added in depend on the layer
+    and the adapter only."""
+    mods = [("gate", 640), ("up", 640)]
+    sites = [pe.Site.fused(0, 8192, mods), pe.Site.fused(0, 5120, [("q", 384)])]
+    ranks = [16, 32, 64]
+    mixed = wls.Workload("prompts-in-decode", sites, ranks, 1.0, [1] * 40 + [128, 200], [1, 2, 3, 0] * 10 + [1, 2], 31)
+    for f32_out in (True, False):
+        outs = []
+        for blocks in (0, 1, 2, 4, 8):
+            loras = harness.product_registry(pe, mixed)
+            loras.set_run_min(64)
+            loras.set_tile_split(blocks)
+            outs.append(harness.run_gpu(pe, loras, mixed, f32_out, meta="device"))
+            loras.close()
+        for o in outs[1:]:
+            for a, b in zip(outs[0], o):
+                assert np.array_equal(a, b)
+        # the 200-token prompt alone, in a step of its own (another automatic split): same bits for its rows
+        alone = wls.Workload("prompt-alone", sites, ranks, 1.0, [200], [2], 31)
+        first = mixed.tokens - 200
+        xs = [mixed.x_bits(si)[first:] for si in range(2)]
+        yb = [mixed.y_base(si)[first:] for si in range(2)]
+        loras = harness.product_registry(pe, alone)
+        loras.set_run_min(64)
+        loras.set_tile_split(1)
+        got = harness.run_gpu(pe, loras, alone, f32_out, meta="device", xs=xs, y_base=yb)
+        loras.close()
+        for si in range(2):
+            assert np.array_equal(got[si], outs[0][si][first:])
+    harness.run_and_check(pe, mixed, f32_out=True, meta="device", run_min=64)
+
+
 def test_heterogeneous_ranks_reduced(pe, wls):
     wl = wls.config4(tokens=96, adapters=20)
     harness.run_and_check(pe, wl, f32_out=True, meta="device")
