@@ -489,7 +489,9 @@ def run_tp(args, rank, world, local_rank):
              for si in range(ns)]
         L.meta_upload(pe.fill_tiles(sh.row_n, sh.row_slot, L.max_lora_tiles()))
         step = L.lora_step(L.max_lora_tiles())
-        lins = [tp.TPLinear(L, si, sh.modes[si]) for si in range(ns)]
+        if args.exchange == "fused":
+            tp.connect_exchange(L, rank, world)
+        lins = [tp.TPLinear(L, si, sh.modes[si], exchange=args.exchange) for si in range(ns)]
         sets.append({"L": L, "x": x, "y": y, "step": step, "lins": lins})
     torch.cuda.synchronize()
     stream = torch.cuda.current_stream()
@@ -532,7 +534,14 @@ def run_tp(args, rank, world, local_rank):
     ms = _event_time(torch, stream, run, args.steps, args.warmup, barrier)
     # the collective alone: all-reduce of one [512, lds] plane
     s0 = sets[0]["lins"][1]._s[:sh.tokens]
-    ar = _event_time(torch, stream, lambda i: torch.distributed.all_reduce(s0), 50, 5, barrier) / 50 if world > 1 else 0.0
+    if world == 1:
+        ar = 0.0
+    elif args.exchange == "fused":  # the exchange kernel alone (partials left over from the last step)
+        L0, lin0 = sets[0]["L"], sets[0]["lins"][1]
+        ar = _event_time(torch, stream, lambda i: L0.s_exchange(lin0.lora, sets[0]["step"], sh.tokens, stream.cuda_stream),
+                         50, 5, barrier) / 50
+    else:
+        ar = _event_time(torch, stream, lambda i: torch.distributed.all_reduce(s0), 50, 5, barrier) / 50
     clocks = sampler.stop() if sampler is not None else None
     for S in sets:
         S["L"].device_status()
@@ -550,7 +559,10 @@ def run_tp(args, rank, world, local_rank):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": wl.name, "tokens_per_step": sh.tokens, "adapters": sh.n_adapters,
                        "parallelism": f"tp{world}: column-parallel q, gate/up; row-parallel o, down",
-                       "collective": "NCCL all-reduce(sum) of the f32 shrink partials, 2 per step", "launch": mode,
+                       "collective": ("one exchange kernel per row-parallel layer: partials stored to every rank's staging "
+                                      "memory over NVLink, flags, sum in rank order" if args.exchange == "fused" else
+                                      "NCCL all-reduce(sum) of the f32 shrink partials") + ", 2 per step",
+                       "launch": mode,
                        "l2": f"{copies} rotating copies"},
             "gpu_launches": (2 * ns + 2) * 2 * args.steps,
             "step_roofline": {"algorithmic_bytes_per_step_per_gpu": shw["bytes"], "achieved_gbs_per_gpu": shw["bytes"] / (us * 1e-6) / 1e9,
@@ -723,6 +735,9 @@ def main():
                                                         "benchmark configuration; fewer for profiler captures)")
     ap.add_argument("--copies", type=int, default=0, help="override the number of rotating pool copies")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="tp workload only: how the row-parallel shrink partials are summed over the ranks: the "
+                         "library's one-kernel exchange over peer memory, or an NCCL all-reduce")
     ap.add_argument("--path", default="apply", choices=["apply", "cluster", "pair"],
                     help="apply: plora_apply after the layer's own matrix multiply (shrink and expand fetch x and y "
                          "ahead of their dependency waits); cluster: plora_apply as one cluster kernel per layer; "

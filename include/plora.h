@@ -234,6 +234,25 @@ int plora_s_reduce(plora_t* h, const plora_hook* hook, const plora_step* step, i
 int plora_expand_reduced(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, uint64_t y, int ldy,
                          int f32_out, void* stream);
 
+/* The same exchange in one kernel per GPU instead of a collective library call (no counterpart in the
+ * engine). Every rank stores its partial into a staging slot on every rank through peer mappings (NVLink),
+ * raises a flag there, waits (at most timeout_ms, then PLORA_ERR_TIMEOUT in the device status word) for the
+ * flags of all ranks in its own memory and adds the partials in rank order, so all ranks end with the same
+ * bits in plane 0. Set-up: plora_exchange_create on every rank (same world, max_tokens, max_rank, max_slots
+ * everywhere), then hand every other rank's 64-byte handle from plora_exchange_export to
+ * plora_exchange_import (another process; CUDA IPC) or its plora_t to plora_exchange_import_local (same
+ * process). All ranks must then make the same sequence of plora_s_exchange calls on steps with identical
+ * metadata; follow each with plora_expand_reduced. Graph-capturable: the call counter lives on the device. */
+int plora_exchange_create(plora_t* h, int world, int rank, int timeout_ms);
+int plora_exchange_export(plora_t* h, void* handle64);
+int plora_exchange_import(plora_t* h, int peer, const void* handle64);
+int plora_exchange_import_local(plora_t* h, int peer, plora_t* other);
+int plora_s_exchange(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, void* stream);
+/* All ranks of one process on ONE device in a single cooperative launch, for machines with fewer GPUs than
+ * ranks (kernels that wait on one another must not be separate launches on one GPU). hs[r] is rank r. */
+int plora_s_exchange_all_ranks(plora_t* const* hs, const plora_hook* const* hooks, const plora_step* const* steps,
+                               int world, int rows, void* stream);
+
 /* Gpu::fork / Gpu::join (src/gpu.rs:849-901): order `side` after `main`, and `main` after `side`. */
 int plora_fork(plora_t* h, void* main_stream, void* side_stream);
 int plora_join(plora_t* h, void* main_stream, void* side_stream);

@@ -127,6 +127,13 @@ SYMBOLS = {
     "plora_set_apply_mode": (_I, [_P, _I]),
     "plora_s_reduce": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _P]),
     "plora_expand_reduced": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _U64, _I, _I, _P]),
+    "plora_exchange_create": (_I, [_P, _I, _I, _I]),
+    "plora_exchange_export": (_I, [_P, _P]),
+    "plora_exchange_import": (_I, [_P, _I, _P]),
+    "plora_exchange_import_local": (_I, [_P, _I, _P]),
+    "plora_s_exchange": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _P]),
+    "plora_s_exchange_all_ranks": (_I, [C.POINTER(_P), C.POINTER(C.POINTER(Hook)), C.POINTER(C.POINTER(StepLora)), _I, _I,
+                                        _P]),
     "plora_fork": (_I, [_P, _P, _P]),
     "plora_join": (_I, [_P, _P, _P]),
     "plora_set_run_min": (_I, [_P, _I]),
@@ -452,6 +459,26 @@ class Loras:
         self._check(lib.plora_expand_reduced(self._h, C.byref(hook), C.byref(step), rows, y, ldy, int(f32_out),
                                              _P(stream)))
 
+    # ---- tensor-parallel exchange of the shrink partials in one kernel per GPU ----
+    def exchange_create(self, world, rank, timeout_ms=2000):
+        self._check(lib.plora_exchange_create(self._h, world, rank, timeout_ms))
+
+    def exchange_export(self):
+        """The 64-byte handle another process passes to exchange_import."""
+        buf = C.create_string_buffer(64)
+        self._check(lib.plora_exchange_export(self._h, buf))
+        return buf.raw
+
+    def exchange_import(self, peer, handle):
+        self._check(lib.plora_exchange_import(self._h, peer, C.c_char_p(bytes(handle))))
+
+    def exchange_import_local(self, peer, other):
+        self._check(lib.plora_exchange_import_local(self._h, peer, other._h))
+
+    def s_exchange(self, hook, step, rows, stream=0):
+        """Sums the shrink partials of all ranks into plane 0 of S (all ranks must call it in the same order)."""
+        self._check(lib.plora_s_exchange(self._h, C.byref(hook), C.byref(step), rows, _P(stream)))
+
     def fork(self, main=0, side=0):  # src/gpu.rs:849-858
         self._check(lib.plora_fork(self._h, _P(main), _P(side)))
 
@@ -490,6 +517,18 @@ class Linear:
             if side is not None and side != main:
                 L.join(main, side)
             L.expand(self.lora, lora, rows, y, ldy, f32_out, main)
+
+
+def s_exchange_all_ranks(ranks, hooks, steps, rows, stream=0):
+    """plora_s_exchange for every rank of one process on one device in a single cooperative launch; ranks[r] is
+    the Loras of rank r."""
+    n = len(ranks)
+    hs = (_P * n)(*[r._h for r in ranks])
+    hk = (C.POINTER(Hook) * n)(*[C.pointer(h) for h in hooks])
+    st = (C.POINTER(StepLora) * n)(*[C.pointer(s) for s in steps])
+    rc = lib.plora_s_exchange_all_ranks(hs, hk, st, n, rows, _P(stream))
+    if rc != 0:
+        ranks[0]._check(rc)
 
 
 def site_apply_static(x, rows, cols, tiles, max_tiles, hook, lds, y, ldy, f32_out=False, stream=0):

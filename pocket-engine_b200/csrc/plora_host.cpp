@@ -237,6 +237,9 @@ void plora_destroy(plora_t* h) {
         if (h->meta) cudaFree(h->meta);
         if (h->host_meta) cudaFreeHost(h->host_meta);
         if (h->status) cudaFree(h->status);
+        for (int p = 0; p < PLORA_XCHG_MAX_WORLD; p++)
+            if (h->xchg_ipc[p] && h->xchg_peer[p]) cudaIpcCloseMemHandle(h->xchg_peer[p]);
+        if (h->xchg) cudaFree(h->xchg);
         if (h->fork_ev) cudaEventDestroy(h->fork_ev);
         if (h->join_ev) cudaEventDestroy(h->join_ev);
     } else {
@@ -864,6 +867,146 @@ int plora_set_run_min(plora_t* h, int tokens) {
     if (!h->mma_ok && tokens < (1 << 30))
         return fail(h, PLORA_ERR_CONFIG, "the tile path needs a device handle and max_rank <= 128");
     h->seg.run_min = tokens;
+    return PLORA_OK;
+}
+
+// ------------------------------------------------------------------ tensor-parallel exchange
+
+int plora_exchange_create(plora_t* h, int world, int rank, int timeout_ms) {
+    if (!h) return PLORA_ERR_ARG;
+    if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
+    if (world < 1 || world > PLORA_XCHG_MAX_WORLD || rank < 0 || rank >= world || timeout_ms < 1)
+        return fail(h, PLORA_ERR_ARG, "exchange: world 1..8, rank inside it, timeout at least 1 ms");
+    if (h->xchg) return fail(h, PLORA_ERR_ARG, "exchange already created");
+    CU(h, "cudaSetDevice", cudaSetDevice(h->device));
+    const int work_cap = h->max_slots + h->max_tokens / PLORA_WORK_TOKENS + 1;
+    h->xchg_max_blocks = work_cap + std::max(1, h->max_tokens / 64);
+    const size_t staging = (size_t)2 * world * h->max_tokens * h->lds * 4;
+    h->xchg_flags_off = (staging + 255) / 256 * 256;
+    h->xchg_ctl_off = h->xchg_flags_off + ((size_t)2 * world * h->xchg_max_blocks * 4 + 255) / 256 * 256;
+    h->xchg_ctx_off = h->xchg_ctl_off + 256;
+    h->xchg_bytes = h->xchg_ctx_off + (size_t)PLORA_XCHG_MAX_WORLD * sizeof(PloraXchgCtx);
+    h->xchg_bytes = (h->xchg_bytes + ((size_t)2 << 20) - 1) / ((size_t)2 << 20) * ((size_t)2 << 20);
+    CU(h, "alloc exchange", cudaMalloc((void**)&h->xchg, h->xchg_bytes));
+    CU(h, "zero exchange", cudaMemset(h->xchg, 0, h->xchg_bytes));
+    CU(h, "sync", cudaDeviceSynchronize());
+    h->xchg_world = world;
+    h->xchg_rank = rank;
+    h->xchg_timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
+    h->xchg_peer[rank] = h->xchg;
+    return PLORA_OK;
+}
+
+int plora_exchange_export(plora_t* h, void* handle64) {
+    if (!h || !handle64) return PLORA_ERR_ARG;
+    if (!h->xchg) return fail(h, PLORA_ERR_ARG, "exchange not created");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t hd;
+    CU(h, "cudaSetDevice", cudaSetDevice(h->device));
+    CU(h, "export exchange memory", cudaIpcGetMemHandle(&hd, h->xchg));
+    memcpy(handle64, &hd, 64);
+    return PLORA_OK;
+}
+
+int plora_exchange_import(plora_t* h, int peer, const void* handle64) {
+    if (!h || !handle64) return PLORA_ERR_ARG;
+    if (!h->xchg) return fail(h, PLORA_ERR_ARG, "exchange not created");
+    if (peer < 0 || peer >= h->xchg_world || peer == h->xchg_rank || h->xchg_peer[peer])
+        return fail(h, PLORA_ERR_ARG, "exchange: peer out of range, self, or already imported");
+    cudaIpcMemHandle_t hd;
+    memcpy(&hd, handle64, 64);
+    void* p = nullptr;
+    CU(h, "cudaSetDevice", cudaSetDevice(h->device));
+    CU(h, "open peer exchange memory", cudaIpcOpenMemHandle(&p, hd, cudaIpcMemLazyEnablePeerAccess));
+    h->xchg_peer[peer] = (uint8_t*)p;
+    h->xchg_ipc[peer] = true;
+    return PLORA_OK;
+}
+
+int plora_exchange_import_local(plora_t* h, int peer, plora_t* other) {
+    if (!h || !other) return PLORA_ERR_ARG;
+    if (!h->xchg || !other->xchg) return fail(h, PLORA_ERR_ARG, "exchange not created");
+    if (peer < 0 || peer >= h->xchg_world || peer == h->xchg_rank || h->xchg_peer[peer] || other->xchg_rank != peer ||
+        other->xchg_world != h->xchg_world || other->xchg_bytes != h->xchg_bytes)
+        return fail(h, PLORA_ERR_ARG, "exchange: peer handle does not match (rank, world or sizes)");
+    if (other->device != h->device) {
+        CU(h, "cudaSetDevice", cudaSetDevice(h->device));
+        cudaError_t e = cudaDeviceEnablePeerAccess(other->device, 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+        else if (e != cudaSuccess) return cuda_fail(h, "enable peer access", e);
+    }
+    h->xchg_peer[peer] = other->xchg;
+    return PLORA_OK;
+}
+
+static int xchg_ctx(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, PloraXchgCtx* c, int* nblocks) {
+    if (!h || !hook || !step) return PLORA_ERR_ARG;
+    if (!h->xchg) return fail(h, PLORA_ERR_ARG, "exchange not created");
+    if (hook->site < 0 || hook->site >= (int)h->sites.size()) return fail(h, PLORA_ERR_ARG, "hook names no site");
+    if (rows < 0 || rows > h->max_tokens) return fail(h, PLORA_ERR_CAPACITY, "more rows than max_tokens");
+    for (int p = 0; p < h->xchg_world; p++)
+        if (!h->xchg_peer[p]) return fail(h, PLORA_ERR_ARG, "exchange: rank " + std::to_string(p) + " was not imported");
+    const SiteInfo& site = h->sites[(size_t)hook->site];
+    const int work_cap = std::min(std::min(step->max_tiles, rows), h->max_slots + rows / PLORA_WORK_TOKENS);
+    const int tile_cap = h->mma_ok && rows >= step->run_min ? std::max(1, rows / 64) : 0;
+    *nblocks = work_cap + tile_cap;
+    if (*nblocks > h->xchg_max_blocks) return fail(h, PLORA_ERR_CAPACITY, "exchange: more blocks than flags");
+    c->S = (float*)(uintptr_t)step->s;
+    c->s_stride = (size_t)(step->s_stride / 4);
+    c->lds = step->lds;
+    c->nsplit = site.nsplit;
+    c->segs = (const int32_t*)(uintptr_t)step->segs;
+    c->lay = h->seg;
+    c->table = (const plora_desc*)(uintptr_t)hook->table;
+    c->work_cap = work_cap;
+    c->tile_split = tile_split(h, rows);
+    c->K = site.cols;
+    c->world = h->xchg_world;
+    c->rank = h->xchg_rank;
+    c->max_tokens = h->max_tokens;
+    c->max_blocks = h->xchg_max_blocks;
+    for (int p = 0; p < PLORA_XCHG_MAX_WORLD; p++) {
+        c->staging[p] = p < h->xchg_world ? (float*)h->xchg_peer[p] : nullptr;
+        c->flags[p] = p < h->xchg_world ? (unsigned*)(h->xchg_peer[p] + h->xchg_flags_off) : nullptr;
+    }
+    c->ctl = (unsigned*)(h->xchg + h->xchg_ctl_off);
+    c->status = h->status;
+    c->timeout_ns = h->xchg_timeout_ns;
+    return PLORA_OK;
+}
+
+int plora_s_exchange(plora_t* h, const plora_hook* hook, const plora_step* step, int rows, void* stream) {
+    PloraXchgCtx c;
+    int nblocks = 0;
+    int rc = xchg_ctx(h, hook, step, rows, &c, &nblocks);
+    if (rc != PLORA_OK) return rc;
+    const bool pdl = h->pdl && h->pdl_armed;
+    h->pdl_armed = true;
+    CU(h, "S exchange", plora_launch_xchg(c, nblocks, pdl, as_stream(stream)));
+    return PLORA_OK;
+}
+
+int plora_s_exchange_all_ranks(plora_t* const* hs, const plora_hook* const* hooks, const plora_step* const* steps,
+                               int world, int rows, void* stream) {
+    if (!hs || !hooks || !steps || world < 1 || world > PLORA_XCHG_MAX_WORLD || !hs[0]) return PLORA_ERR_ARG;
+    plora_t* h0 = hs[0];
+    PloraXchgCtx cs[PLORA_XCHG_MAX_WORLD];
+    int nblocks = 0;
+    for (int r = 0; r < world; r++) {
+        if (!hs[r] || hs[r]->device != h0->device || hs[r]->xchg_world != world || hs[r]->xchg_rank != r)
+            return fail(h0, PLORA_ERR_ARG, "all-ranks exchange: handle r must be rank r of this world on one device");
+        int nb = 0;
+        int rc = xchg_ctx(hs[r], hooks[r], steps[r], rows, &cs[r], &nb);
+        if (rc != PLORA_OK) return rc;
+        if (r && nb != nblocks) return fail(h0, PLORA_ERR_ARG, "all-ranks exchange: ranks disagree on the step's shape");
+        nblocks = nb;
+        hs[r]->pdl_armed = false;  // a cooperative launch: the next kernel of each rank starts plain
+    }
+    CU(h0, "cudaSetDevice", cudaSetDevice(h0->device));
+    PloraXchgCtx* dev = (PloraXchgCtx*)(h0->xchg + h0->xchg_ctx_off);
+    CU(h0, "upload contexts",
+       cudaMemcpyAsync(dev, cs, sizeof(PloraXchgCtx) * (size_t)world, cudaMemcpyHostToDevice, as_stream(stream)));
+    CU(h0, "S exchange (all ranks)", plora_launch_xchg_all_ranks(dev, world, nblocks, as_stream(stream)));
     return PLORA_OK;
 }
 

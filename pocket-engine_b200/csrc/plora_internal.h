@@ -18,6 +18,7 @@
 #define PLORA_WORK_WORDS 32
 #define PLORA_MMA_TOKENS 128
 #define PLORA_RUN_MIN_DEFAULT 64
+#define PLORA_XCHG_MAX_WORLD 8  // ranks of a tensor-parallel exchange
 
 #define SEG_N_ACT 0    // slots that have gather tokens
 #define SEG_N_WORK 1   // gather work items
@@ -102,6 +103,14 @@ struct plora {
     mutable std::string err;
     int sm_count = 148;
     bool pdl = true;        // launch with programmatic stream serialization
+    // tensor-parallel exchange (plora_exchange_create): one device allocation holding the staging buffers, the
+    // flags, the call counters and room for the contexts of an all-ranks launch
+    uint8_t* xchg = nullptr;
+    size_t xchg_bytes = 0, xchg_flags_off = 0, xchg_ctl_off = 0, xchg_ctx_off = 0;
+    int xchg_world = 0, xchg_rank = 0, xchg_max_blocks = 0;
+    unsigned long long xchg_timeout_ns = 0;
+    uint8_t* xchg_peer[PLORA_XCHG_MAX_WORLD] = {};   // base of every rank's allocation as mapped in this process
+    bool xchg_ipc[PLORA_XCHG_MAX_WORLD] = {};        // opened from an IPC handle (closed on destroy)
     int tile_split_force = 0;  // plora_set_tile_split: 0 = chosen per launch
     int apply_mode = 0;     // plora_apply: 0 = shrink/expand pair with early loads, 1 = one cluster kernel per layer
     bool site_ok = false;   // the cluster kernel's attributes were set
@@ -111,6 +120,25 @@ struct plora {
 };
 
 size_t plora_meta_group_smem(const SegLayout& lay);
+
+// ---- tensor-parallel exchange of the shrink partials (plora_xchg.cu) ----
+struct PloraXchgCtx {
+    float* S;
+    size_t s_stride;  // floats between K-split planes
+    int lds, nsplit;
+    const int32_t* segs;
+    SegLayout lay;
+    const plora_desc* table;
+    int work_cap, tile_split, K;
+    int world, rank, max_tokens, max_blocks;
+    float* staging[PLORA_XCHG_MAX_WORLD];    // every rank's staging area [2][world][max_tokens][lds], as mapped here
+    unsigned* flags[PLORA_XCHG_MAX_WORLD];   // every rank's flags [2][world][max_blocks]
+    unsigned* ctl;                           // local: [0] calls completed, [1] blocks finished in this call
+    int* status;
+    unsigned long long timeout_ns;
+};
+cudaError_t plora_launch_xchg(const PloraXchgCtx& c, int nblocks, bool pdl, cudaStream_t st);
+cudaError_t plora_launch_xchg_all_ranks(const PloraXchgCtx* ctxs_dev, int world, int nblocks, cudaStream_t st);
 
 // The tensor-core tile path cuts a site's K inputs into `chunks` ranges that are accumulated separately (each in
 // its own tensor-memory accumulator, inputs in order) and then added as a balanced binary tree. The count is a

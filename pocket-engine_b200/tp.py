@@ -7,9 +7,11 @@ One process per GPU. A layer is sharded the way its base weights are:
   slice. No collective.
 * row-parallel (o, down): every rank holds the input-column slice ``A[:, rank * K/P : (rank + 1) * K/P]``
   and, of B, only the rows of the output slice it will write; x arrives sharded ``[T, K/P]``. Each rank's
-  shrink gives a partial S; the partials are all-reduced (sum) over NVLink with NCCL; then each rank expands
-  its own N/P slice of output columns into its partial y (whose reduction afterwards, the base layer's own,
-  therefore receives exactly one copy of the adapter term).
+  shrink gives a partial S; the partials are summed over the ranks (NVLink) either by an NCCL all-reduce or by
+  the library's own exchange kernel (``connect_exchange`` + ``TPLinear(exchange="fused")``: one launch that
+  pushes the partial to every rank, waits for theirs and adds them); then each rank expands its own N/P slice
+  of output columns into its partial y (whose reduction afterwards, the base layer's own, therefore receives
+  exactly one copy of the adapter term).
 
 Sharding is expressed with the registry's own vocabulary: a shard is just a ``Site`` with the local sizes, a
 row-parallel part carrying ``off = rank * N/P`` so the expand lands in the right columns of the full-width
@@ -123,13 +125,30 @@ class _DevView:
                                          "version": 2, "strides": None}
 
 
+def connect_exchange(loras, rank, world, group=None, timeout_ms=2000):
+    """Sets up the exchange kernel's peer mappings for one process per GPU: every rank creates its staging
+    memory, the 64-byte handles travel through the process group, every rank maps the others'. Ends with a
+    barrier so that no rank launches an exchange before all are mapped."""
+    import torch.distributed as dist
+    loras.exchange_create(world, rank, timeout_ms)
+    handles = [None] * world
+    dist.all_gather_object(handles, loras.exchange_export(), group=group)
+    for p in range(world):
+        if p != rank:
+            loras.exchange_import(p, handles[p])
+    dist.barrier(group=group)
+
+
 class TPLinear:
     """Linear::forward's adapter bracket for one shard. ``group`` is a torch.distributed process group (NCCL
-    on GPUs); for row-parallel layers the shrink's partial sums are all-reduced between shrink and expand."""
+    on GPUs); for row-parallel layers the shrink's partial sums are summed over the ranks between shrink and
+    expand: ``exchange="nccl"`` by an all-reduce on plane 0, ``"fused"`` by the library's one-kernel exchange
+    (after connect_exchange)."""
 
-    def __init__(self, loras, site, mode, group=None, base=None):
+    def __init__(self, loras, site, mode, group=None, base=None, exchange="nccl"):
         import torch
         self.loras, self.site, self.mode, self.group, self.base = loras, site, mode, group, base
+        self.exchange = exchange
         self.lora = loras.hook(site)
         # plane 0 of the f32 intermediate as a tensor, for the collective
         self._s = torch.as_tensor(_DevView(loras.s, (loras.max_tokens, loras.lds)), device=f"cuda:{loras.device}") \
@@ -145,7 +164,10 @@ class TPLinear:
             self.base(x, rows, y, ldy, f32_out)
         if lora is None:
             return
-        if self.mode == ROW:
+        if self.mode == ROW and self.exchange == "fused":
+            L.s_exchange(self.lora, lora, rows, main)  # K-split partials of every rank -> plane 0, one launch
+            L.expand_reduced(self.lora, lora, rows, y, ldy, f32_out, main)
+        elif self.mode == ROW:
             L.s_reduce(self.lora, lora, rows, main)  # K-split partials -> plane 0
             dist.all_reduce(self._s[:rows], op=dist.ReduceOp.SUM, group=self.group)
             L.expand_reduced(self.lora, lora, rows, y, ldy, f32_out, main)

@@ -33,11 +33,14 @@ def main():
     stream = torch.cuda.current_stream().cuda_stream
     loras.meta_upload(pe.fill_tiles(sh.row_n, sh.row_slot, loras.max_lora_tiles()), stream)
     step = loras.lora_step(loras.max_lora_tiles(), stream)
+    exchange = os.environ.get("PLORA_TP_EXCHANGE", "nccl")
+    if exchange == "fused":
+        tp.connect_exchange(loras, rank, world)
     worst = (0.0, 0.0)
     for si in range(len(sh.sites)):
         x = harness.to_dev_bf16(sh.x_bits(si), local)
         y = torch.from_numpy(sh.y_base(si).copy()).cuda()
-        lin = tp.TPLinear(loras, si, sh.modes[si])
+        lin = tp.TPLinear(loras, si, sh.modes[si], exchange=exchange)
         lin.forward(x.data_ptr(), sh.tokens, y.data_ptr(), y.shape[1], True, lora=step, main=stream)
         torch.cuda.synchronize()
         outs = [None] * world
@@ -53,7 +56,7 @@ def main():
     loras.device_status()
     if rank == 0:
         ok = worst[0] <= harness.MAX_TOL and worst[1] <= harness.MEAN_TOL
-        print(json.dumps({"tp_check": "ok" if ok else "FAILED", "world": world, "max_over_rms": worst[0],
+        print(json.dumps({"tp_check": "ok" if ok else "FAILED", "world": world, "exchange": exchange, "max_over_rms": worst[0],
                           "mean_over_rms": worst[1], "workload": wl.name}))
     loras.close()
     dist.barrier()
