@@ -141,6 +141,20 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 // token row per thread.
 #define SHR_KSTEP 64
 #define SHR_X_BYTES (MMA_M * SHR_KSTEP * 2)
+#define SHR_MAX_STAGES 8
+
+// waits until at most n of this thread's async-copy groups are still in flight
+__device__ __forceinline__ void cp_async_wait_upto(int n) {
+    switch (n) {
+        case 0: cp_async_wait<0>(); break;
+        case 1: cp_async_wait<1>(); break;
+        case 2: cp_async_wait<2>(); break;
+        case 3: cp_async_wait<3>(); break;
+        case 4: cp_async_wait<4>(); break;
+        case 5: cp_async_wait<5>(); break;
+        default: cp_async_wait<6>(); break;
+    }
+}
 
 __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_constant__ CUtensorMap xmap, int K,
                                                                 const int* __restrict__ segs, SegLayout lay,
@@ -149,7 +163,7 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
                                                                 int ksplit, int nstage, int stage_bytes,
                                                                 int* __restrict__ status) {
     extern __shared__ unsigned char dsm_raw[];
-    __shared__ __align__(8) uint64_t full[4], done[4], acc_bar;
+    __shared__ __align__(8) uint64_t full[SHR_MAX_STAGES], done[SHR_MAX_STAGES], acc_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int s_fail;
     const int tile = blockIdx.z;
@@ -218,9 +232,7 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
     for (int it = 0; it < nk; it++) {
         const int st = it % nstage;
         // the copies of this step's slab rows sit at most nstage - 2 groups back
-        if (nstage >= 4) cp_async_wait<2>();
-        else if (nstage == 3) cp_async_wait<1>();
-        else cp_async_wait<0>();
+        cp_async_wait_upto(nstage - 2);
         fence_async_smem();
         __syncthreads();
         if (warp == 0) {
@@ -572,7 +584,7 @@ cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, con
         return cudaErrorInvalidValue;
     const int stage_bytes = SHR_X_BYTES + ((max_rank_total * 128 + 1023) / 1024) * 1024;
     int nstage = (190 * 1024) / stage_bytes;
-    nstage = nstage > 4 ? 4 : nstage;
+    nstage = nstage > SHR_MAX_STAGES ? SHR_MAX_STAGES : nstage;
     if (nstage < 2) return cudaErrorInvalidValue;
     const size_t smem = (size_t)nstage * stage_bytes + 1024;
     return launch_pdl(plora_shrink_mma_kernel, dim3((unsigned)tile_split, 1, (unsigned)tile_cap), dim3(128), smem, st, pdl,
@@ -586,8 +598,12 @@ cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int l
     const int max_rank = lds / PLORA_MAX_PARTS;
     const int op_bytes = MMA_M * max_rank * 2;
     const int nblocks = (max_rows + 127) / 128;
-    // each block walks up to 8 column blocks with one staging of its S tile
-    const int nb_per_cta = nblocks < 8 ? nblocks : 8;
+    // each block walks up to 8 column blocks with one staging of its S tile; fewer when the step has so few
+    // tiles that the blocks would not fill the SMs twice over
+    const long long total = (long long)(tile_cap + 1) / 2 * nblocks * parts;  // tile_cap counts 64-token halves
+    int nb_per_cta = (int)(total / (2 * 148));
+    nb_per_cta = nb_per_cta < 1 ? 1 : nb_per_cta > 8 ? 8 : nb_per_cta;
+    if (nb_per_cta > nblocks) nb_per_cta = nblocks;
     dim3 grid((unsigned)((nblocks + nb_per_cta - 1) / nb_per_cta), (unsigned)parts, (unsigned)tile_cap);
     // at least 48 KB of shared memory per block: no more than four blocks, 128 tensor-memory columns each,
     // share an SM's 512 columns
