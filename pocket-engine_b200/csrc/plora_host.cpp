@@ -187,6 +187,13 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
             check("alloc pool", cudaMalloc((void**)&h->pool, h->slot_bytes * (size_t)max_slots));
             check("alloc tables", cudaMalloc((void**)&h->tables, h->table_bytes));
             check("pinned tables", cudaMallocHost((void**)&h->host_tables, h->table_bytes));
+            const size_t amap_bytes = sizeof(PloraTmap) * h->sites.size() * (size_t)(max_slots + 1);
+            check("alloc slab tensor maps", cudaMalloc((void**)&h->amaps, amap_bytes));
+            check("pinned slab tensor maps", cudaMallocHost((void**)&h->host_amaps, amap_bytes));
+            if (rc == PLORA_OK) {
+                memset(h->host_amaps, 0, amap_bytes);
+                check("zero slab tensor maps", cudaMemset(h->amaps, 0, amap_bytes));
+            }
             check("alloc S", cudaMalloc((void**)&h->s, h->s_bytes));
             check("alloc meta", cudaMalloc((void**)&h->meta, meta_words * 4));
             check("pinned meta", cudaMallocHost((void**)&h->host_meta, (size_t)(1 + 3 * h->cap_tiles) * 4));
@@ -233,6 +240,8 @@ void plora_destroy(plora_t* h) {
         if (h->pool) cudaFree(h->pool);
         if (h->tables) cudaFree(h->tables);
         if (h->host_tables) cudaFreeHost(h->host_tables);
+        if (h->amaps) cudaFree(h->amaps);
+        if (h->host_amaps) cudaFreeHost(h->host_amaps);
         if (h->s) cudaFree(h->s);
         if (h->meta) cudaFree(h->meta);
         if (h->host_meta) cudaFreeHost(h->host_meta);
@@ -478,6 +487,13 @@ int plora_upload(plora_t* h, int slot, uint32_t id, void* stream) {
         size_t at = si * (size_t)(h->max_slots + 1) + (size_t)slot;
         CU(h, "upload descriptor",
            cudaMemcpyAsync(h->tables + at, h->host_tables + at, sizeof(plora_desc), cudaMemcpyHostToDevice, st));
+        const plora_desc& d = h->host_tables[at];
+        if (h->mma_ok && d.rank > 0) {  // the tile path's view of the stacked A
+            CU(h, "encode slab tensor map",
+               plora_mma_encode_slab(&h->host_amaps[at], (const void*)(uintptr_t)d.a, h->sites[si].cols, d.rank));
+            CU(h, "upload slab tensor map",
+               cudaMemcpyAsync(h->amaps + at, h->host_amaps + at, sizeof(PloraTmap), cudaMemcpyHostToDevice, st));
+        }
     }
     return PLORA_OK;
 }
@@ -686,7 +702,8 @@ static int shrink_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
     if (h->mma_ok && rows >= step->run_min)
         CU(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
-                                   h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s,
+                                   h->seg, (const plora_desc*)(uintptr_t)hook->table,
+                                   h->amaps + (size_t)hook->site * (size_t)(h->max_slots + 1), (float*)(uintptr_t)step->s,
                                    (size_t)(step->s_stride / 4), step->lds, hook->parts * h->max_rank, std::max(1, rows / 64),
                                    tile_split(h, rows), h->status, h->pdl, as_stream(stream)));
     return PLORA_OK;
@@ -735,7 +752,8 @@ int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint
     if (h->mma_ok && rows >= step->run_min) {
         CU(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
-                                   h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s,
+                                   h->seg, (const plora_desc*)(uintptr_t)hook->table,
+                                   h->amaps + (size_t)hook->site * (size_t)(h->max_slots + 1), (float*)(uintptr_t)step->s,
                                    (size_t)(step->s_stride / 4), step->lds, hook->parts * h->max_rank, std::max(1, rows / 64),
                                    tile_split(h, rows), h->status, h->pdl, as_stream(stream)));
         CU(h, "expand (tile path)",

@@ -43,6 +43,10 @@ struct SegLayout {
     __host__ __device__ int words() const { return tslot() + max_tokens; }
 };
 
+struct alignas(64) PloraTmap {  // a CUtensorMap, opaque to the host registry
+    unsigned char b[128];
+};
+
 struct SiteInfo {
     int layer = 0, cols = 0;
     int col_heads_start = -1, col_heads_block = 0;
@@ -88,6 +92,8 @@ struct plora {
     plora_desc* tables = nullptr;       // device
     plora_desc* host_tables = nullptr;  // pinned mirror
     size_t table_bytes = 0;
+    PloraTmap* amaps = nullptr;       // device: per (layer, slot) tensor map of the stacked A (tile path)
+    PloraTmap* host_amaps = nullptr;  // pinned mirror
     std::unordered_map<uint32_t, plora_adapter*> adapters;
     std::map<std::string, uint32_t> names;
     uint32_t next_id = 1;
@@ -177,8 +183,9 @@ cudaError_t plora_launch_fp8_fused(const void* xq, const float* st_, const void*
                                    const int32_t* segs, SegLayout lay, const plora_desc* table, int n_parts,
                                    const int* part_off, const int* part_rows, const float* S, int lds, void* y, int ldy,
                                    int f32_out, int max_rank, int* status, bool pdl, cudaStream_t stream);
+cudaError_t plora_mma_encode_slab(void* out128, const void* a, int K, int R);
 cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, const int32_t* segs, SegLayout lay,
-                                    const plora_desc* table, float* S, size_t s_stride_elems, int lds,
+                                    const plora_desc* table, const PloraTmap* amaps, float* S, size_t s_stride_elems, int lds,
                                     int max_rank_total, int tile_cap, int tile_split, int* status, bool pdl,
                                     cudaStream_t st);
 cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int lds, int K, int tile_split,

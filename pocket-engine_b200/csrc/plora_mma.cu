@@ -1,8 +1,8 @@
 // Tensor-core tile path for long runs of contiguous tokens of one slot (prefill segments): tcgen05.mma with
 // the accumulator in tensor memory, 128 tokens per tile.
 //
-//   plora_shrink_mma_kernel  S[128, R] = X[128, K] . A_slot[R, K]^T   x tiles by TMA (128-byte swizzle), slab tiles
-//                            by 16-byte async copies into the same swizzle, a ring of stages, f32 in TMEM
+//   plora_shrink_mma_kernel  S[128, R] = X[128, K] . A_slot[R, K]^T   x tiles and slab tiles by TMA (128-byte
+//                            swizzle) from a producer thread, MMAs from another, a ring of stages, f32 in TMEM
 //   plora_expand_mma_kernel  y[128, 128-column block] += S[128, r] . B_p[block, r]^T   S split into a bf16 high
 //                            and low part (two accumulating MMAs, so S keeps ~16 bits of mantissa), operands in
 //                            the unswizzled core-matrix layout, y read-modify-written from registers
@@ -128,42 +128,48 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 
+// Makes a tensor map that sits in global memory (written by a copy earlier in the stream) visible to this
+// thread's tensor copies.
+__device__ __forceinline__ void tmap_acquire(const CUtensorMap* map) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(map) : "memory");
+}
+
+// A wait that may span a block's whole main loop: the same bounded try-wait, with a pause between tries
+// (about a second in all before it gives up).
+__device__ __forceinline__ bool mbar_wait_long(uint64_t* bar, uint32_t parity, int* status) {
+    for (int i = 0; i < (1 << 22); i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 64) __nanosleep(200);
+    }
+    atomicMax(status, PLORA_ERR_TIMEOUT);
+    return false;
+}
+
 #define MMA_M 128
 #define EXP_TPAD 66  // floats per row of the epilogue's transpose tile (64 columns + 2 of padding)
 
 // ------------------------------------------------------------------------------------------------------
 // Shrink of one 128-token tile. Grid (split, 1, tiles); 128 threads. The slot's K chunks (plora_tile_chunks) are
 // shared evenly by min(split, chunks) blocks; each block accumulates its chunks in separate accumulators, adds
-// them as a tree and writes plane blockIdx.x of S. K is walked in steps of 64 inputs through a
-// ring of stages; thread 0 issues the x tile by TMA, all threads copy the slab's rows for the same 64
-// inputs into the 128-byte-swizzled layout the MMA reads; one elected thread issues the MMAs; the stage is
-// refilled one step later, after its MMAs have been committed. The f32 result leaves tensor memory one
-// token row per thread.
+// them as a tree and writes plane blockIdx.x of S. K is walked in steps of 64 inputs through a ring of stages
+// with two roles and no block-wide synchronisation in the loop: one thread of warp 0 issues, per step, the x
+// tile and the slab's rows for the same 64 inputs as tensor copies (both in the 128-byte swizzle; the slab
+// through the tensor map plora_upload encoded for the slot), waiting for a stage's MMAs before it refills it;
+// one thread of warp 1 waits for a stage to land, issues its MMAs and commits them to the stage's "empty"
+// barrier. Once the last MMAs are complete the f32 result leaves tensor memory one token row per thread.
 #define SHR_KSTEP 64
 #define SHR_X_BYTES (MMA_M * SHR_KSTEP * 2)
 #define SHR_MAX_STAGES 8
 
-// waits until at most n of this thread's async-copy groups are still in flight
-__device__ __forceinline__ void cp_async_wait_upto(int n) {
-    switch (n) {
-        case 0: cp_async_wait<0>(); break;
-        case 1: cp_async_wait<1>(); break;
-        case 2: cp_async_wait<2>(); break;
-        case 3: cp_async_wait<3>(); break;
-        case 4: cp_async_wait<4>(); break;
-        case 5: cp_async_wait<5>(); break;
-        default: cp_async_wait<6>(); break;
-    }
-}
-
-__global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_constant__ CUtensorMap xmap, int K,
+__global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_constant__ CUtensorMap xmap,
+                                                                const CUtensorMap* __restrict__ amaps, int K,
                                                                 const int* __restrict__ segs, SegLayout lay,
                                                                 const plora_desc* __restrict__ table,
                                                                 float* __restrict__ S, size_t s_stride, int lds,
                                                                 int ksplit, int nstage, int stage_bytes,
                                                                 int* __restrict__ status) {
     extern __shared__ unsigned char dsm_raw[];
-    __shared__ __align__(8) uint64_t full[SHR_MAX_STAGES], done[SHR_MAX_STAGES], acc_bar;
+    __shared__ __align__(8) uint64_t full[SHR_MAX_STAGES], empty[SHR_MAX_STAGES], acc_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int s_fail;
     const int tile = blockIdx.z;
@@ -178,7 +184,7 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
     const int s_eff = min(ksplit, n_chunks);
     if ((int)blockIdx.x >= s_eff) return pdl_exit_idle();
     const int n_acc = n_chunks / s_eff;  // accumulators (chunks) of this block
-    const bf16* A = reinterpret_cast<const bf16*>(d.a);
+    const CUtensorMap* amap = amaps + slot;
     const int tid = threadIdx.x, warp = tid >> 5;
     // 1024-byte aligned stage ring: [x tile 16 KB][slab rows R x 128 B]
     unsigned char* ring = dsm_raw + ((1024u - (smem_u32(dsm_raw) & 1023u)) & 1023u);
@@ -187,7 +193,7 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
     if (tid == 0) {
         for (int i = 0; i < nstage; i++) {
             mbar_init(&full[i], 1);
-            mbar_init(&done[i], 1);
+            mbar_init(&empty[i], 1);
         }
         mbar_init(&acc_bar, 1);
         mbar_fence_init();
@@ -202,75 +208,64 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
     const int spc = (nk_all + n_chunks - 1) / n_chunks;  // steps per chunk
     const int k_first = (int)blockIdx.x * n_acc * spc;
     const int nk = min(nk_all, k_first + n_acc * spc) - k_first;  // this block's steps
-    const int chunks = R * 8;  // 16-byte chunks of the slab per step
+    // the slab's rows arrive as one box of R rows, or two of R / 2 when R is over the 256-row limit of a box
+    const int nbox = R > 256 ? 2 : 1, box_rows = R / nbox;
     pdl_wait();  // x comes from the kernels before
     pdl_trigger();
 
-    auto issue = [&](int ks) {
-        const int st = ks % nstage;
-        unsigned char* xs = ring + (size_t)st * stage_bytes;
-        unsigned char* as = xs + SHR_X_BYTES;
-        const int k0 = (k_first + ks) * SHR_KSTEP;
-        if (tid == 0) {
-            mbar_expect_tx(&full[st], SHR_X_BYTES);
-            tma_load_2d(xs, &xmap, k0, start, &full[st]);
-        }
-        for (int c = tid; c < chunks; c += 128) {
-            const int n = c >> 3, q = c & 7;
-            const int k = k0 + q * 8;
-            cp_async16(as + n * 128 + ((q ^ (n & 7)) << 4), A + (size_t)n * K + (k < K ? k : 0), k < K);
-        }
-    };
-
-    for (int ks = 0; ks < nstage; ks++) {
-        if (ks < nk) issue(ks);
-        cp_async_commit();
-    }
-    const uint32_t idesc_lo = umma_idesc_bf16(MMA_M, R > 256 ? 256 : R);
-    const uint32_t idesc_hi = umma_idesc_bf16(MMA_M, R > 256 ? R - 256 : 16);
-    bool ok = true;
-    for (int it = 0; it < nk; it++) {
-        const int st = it % nstage;
-        // the copies of this step's slab rows sit at most nstage - 2 groups back
-        cp_async_wait_upto(nstage - 2);
-        fence_async_smem();
-        __syncthreads();
-        if (warp == 0) {
-            if (elect_one()) {
-                if (mbar_wait(&full[st], (it / nstage) & 1, status)) {
-                    tc_fence_after();
-                    const uint32_t xs = smem_u32(ring + (size_t)st * stage_bytes);
-                    const uint32_t as = xs + SHR_X_BYTES;
-                    const int acc = it / spc, first = it - acc * spc;  // a chunk starts a fresh accumulator
-                    const uint32_t dacc = tmem + (uint32_t)acc * acc_cols;
-#pragma unroll
-                    for (int kk = 0; kk < SHR_KSTEP / 16; kk++) {
-                        const uint64_t da = umma_desc(xs + kk * 32, 16, 1024, 2);
-                        const uint64_t db = umma_desc(as + kk * 32, 16, 1024, 2);
-                        umma_bf16(dacc, da, db, idesc_lo, (first | kk) != 0);
-                        if (R > 256) {
-                            const uint64_t db2 = umma_desc(as + 256 * 128 + kk * 32, 16, 1024, 2);
-                            umma_bf16(dacc + 256, da, db2, idesc_hi, (first | kk) != 0);
-                        }
-                    }
-                    umma_commit(&done[st]);
-                    if (it == nk - 1) umma_commit(&acc_bar);
-                } else {
+    if (warp == 0) {
+        // producer: one thread feeds the ring, waiting for a stage's MMAs before refilling it
+        if (elect_one()) {
+            tmap_acquire(amap);
+            for (int ks = 0; ks < nk; ks++) {
+                const int st = ks % nstage;
+                if (ks >= nstage && !mbar_wait(&empty[st], ((ks / nstage) - 1) & 1, status)) {
                     s_fail = 1;
+                    break;
                 }
+                unsigned char* xs = ring + (size_t)st * stage_bytes;
+                unsigned char* as = xs + SHR_X_BYTES;
+                const int k0 = (k_first + ks) * SHR_KSTEP;
+                mbar_expect_tx(&full[st], SHR_X_BYTES + (uint32_t)R * 128u);
+                tma_load_2d(xs, &xmap, k0, start, &full[st]);
+                for (int b = 0; b < nbox; b++) tma_load_2d(as + (size_t)b * box_rows * 128, amap, k0, b * box_rows, &full[st]);
             }
-            __syncwarp();
         }
-        // refill the stage used one step ago, now that its MMAs had a whole step to finish
-        if (it >= 1 && it - 1 + nstage < nk) {
-            const int pst = (it - 1) % nstage;
-            ok = mbar_wait(&done[pst], ((it - 1) / nstage) & 1, status);
-            if (ok) issue(it - 1 + nstage);
+        __syncwarp();
+    } else if (warp == 1) {
+        // MMA issuer: a chunk of K starts a fresh accumulator
+        if (elect_one()) {
+            const uint32_t idesc_lo = umma_idesc_bf16(MMA_M, R > 256 ? 256 : R);
+            const uint32_t idesc_hi = umma_idesc_bf16(MMA_M, R > 256 ? R - 256 : 16);
+            for (int it = 0; it < nk; it++) {
+                const int st = it % nstage;
+                if (!mbar_wait(&full[st], (it / nstage) & 1, status)) {
+                    s_fail = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t xs = smem_u32(ring + (size_t)st * stage_bytes);
+                const uint32_t as = xs + SHR_X_BYTES;
+                const int acc = it / spc, first = it - acc * spc;
+                const uint32_t dacc = tmem + (uint32_t)acc * acc_cols;
+#pragma unroll
+                for (int kk = 0; kk < SHR_KSTEP / 16; kk++) {
+                    const uint64_t da = umma_desc(xs + kk * 32, 16, 1024, 2);
+                    const uint64_t db = umma_desc(as + kk * 32, 16, 1024, 2);
+                    umma_bf16(dacc, da, db, idesc_lo, (first | kk) != 0);
+                    if (R > 256) {
+                        const uint64_t db2 = umma_desc(as + 256 * 128 + kk * 32, 16, 1024, 2);
+                        umma_bf16(dacc + 256, da, db2, idesc_hi, (first | kk) != 0);
+                    }
+                }
+                umma_commit(&empty[st]);
+                if (it == nk - 1) umma_commit(&acc_bar);
+            }
         }
-        cp_async_commit();
-        if (!ok) break;
+        __syncwarp();
     }
-    if (ok) ok = mbar_wait(&acc_bar, 0, status);
+    // everyone: the accumulators are complete once the last commit has arrived
+    bool ok = mbar_wait_long(&acc_bar, 0, status);
     __syncthreads();
     if (ok && !s_fail) {
         tc_fence_after();
@@ -291,7 +286,7 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
         }
         for (int c = 0; n_acc == 1 && c < R; c += 32) {
             uint32_t v[32];
-            tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
+            tmem_ld32(lane_base + c, v);
             if (row < len) {
 #pragma unroll
                 for (int q = 0; q < 32; q += 4)
@@ -302,7 +297,6 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
             }
         }
     }
-    cp_async_wait<0>();
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, ncols);
@@ -568,8 +562,24 @@ cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t 
 }
 }  // namespace
 
+// The tensor map of one slot's stacked A for one layer: [R, K] bf16 row-major, boxes of 64 inputs by R rows
+// (R / 2 rows when R is over 256, the limit of a box), 128-byte swizzle.
+cudaError_t plora_mma_encode_slab(void* out128, const void* a, int K, int R) {
+    static_assert(sizeof(CUtensorMap) == sizeof(PloraTmap), "tensor map size");
+    if (!g_encode) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)R};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {SHR_KSTEP, (cuuint32_t)(R > 256 ? R / 2 : R)};
+    const cuuint32_t es[2] = {1, 1};
+    if (g_encode(reinterpret_cast<CUtensorMap*>(out128), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a), dims,
+                 strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    return cudaSuccess;
+}
+
 cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, const int32_t* segs, SegLayout lay,
-                                    const plora_desc* table, float* S, size_t s_stride_elems, int lds,
+                                    const plora_desc* table, const PloraTmap* amaps, float* S, size_t s_stride_elems, int lds,
                                     int max_rank_total, int tile_cap, int tile_split, int* status, bool pdl,
                                     cudaStream_t st) {
     if (!g_encode) return cudaErrorNotSupported;
@@ -588,7 +598,8 @@ cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, con
     if (nstage < 2) return cudaErrorInvalidValue;
     const size_t smem = (size_t)nstage * stage_bytes + 1024;
     return launch_pdl(plora_shrink_mma_kernel, dim3((unsigned)tile_split, 1, (unsigned)tile_cap), dim3(128), smem, st, pdl,
-                      map, K, segs, lay, table, S, s_stride_elems, lds, tile_split, nstage, stage_bytes, status);
+                      map, reinterpret_cast<const CUtensorMap*>(amaps), K, segs, lay, table, S, s_stride_elems, lds, tile_split,
+                      nstage, stage_bytes, status);
 }
 
 cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int lds, int K, int tile_split,
