@@ -141,6 +141,10 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
         si.kchunk = next_mult((si.cols + want - 1) / want, 256);
         si.nsplit = (si.cols + si.kchunk - 1) / si.kchunk;
         h->nsplit_max = std::max(h->nsplit_max, si.nsplit);
+        for (size_t p = 0; p < si.parts.size() && p < PLORA_MAX_PARTS; p++) {
+            si.part_off[p] = si.parts[p].off;
+            si.part_rows[p] = si.parts[p].rows;
+        }
         h->sites.push_back(si);
     }
     // src/lora.rs:482-488
@@ -760,7 +764,8 @@ int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint
            plora_launch_expand_mma((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.cols,
                                    tile_split(h, rows), (const int32_t*)(uintptr_t)step->segs, h->seg,
                                    (const plora_desc*)(uintptr_t)hook->table, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
-                                   hook->max_rows, std::max(1, rows / 64), h->status, h->pdl, as_stream(stream)));
+                                   site.part_off, site.part_rows, rows, hook->max_rows, std::max(1, rows / 64), h->status,
+                                   h->pdl, as_stream(stream)));
     }
     return PLORA_OK;
 }
@@ -806,7 +811,8 @@ static int expand_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
            plora_launch_expand_mma((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.cols,
                                    reduced ? 1 : tile_split(h, rows), (const int32_t*)(uintptr_t)step->segs, h->seg,
                                    (const plora_desc*)(uintptr_t)hook->table, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
-                                   hook->max_rows, std::max(1, rows / 64), h->status, h->pdl, as_stream(stream)));
+                                   site.part_off, site.part_rows, rows, hook->max_rows, std::max(1, rows / 64), h->status,
+                                   h->pdl, as_stream(stream)));
     return PLORA_OK;
 }
 

@@ -60,6 +60,7 @@ struct SiteInfo {
         for (auto& p : parts) m = p.rows > m ? p.rows : m;
         return m;
     }
+    int part_off[PLORA_MAX_PARTS] = {0, 0, 0, 0}, part_rows[PLORA_MAX_PARTS] = {0, 0, 0, 0};  // copies of parts[]
     // K-split of the shrink: fixed per site so results do not depend on the batch
     int kchunk = 0, nsplit = 1;
     bool cluster_ok = false;  // the one-kernel-per-layer cluster path fits this layer's shapes
@@ -190,8 +191,8 @@ cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, con
                                     cudaStream_t st);
 cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int lds, int K, int tile_split,
                                     const int32_t* segs, SegLayout lay, const plora_desc* table, void* y, int ldy,
-                                    int f32_out, int parts, int max_rows, int tile_cap, int* status, bool pdl,
-                                    cudaStream_t st);
+                                    int f32_out, int parts, const int* part_off, const int* part_rows, int rows_total,
+                                    int max_rows, int tile_cap, int* status, bool pdl, cudaStream_t st);
 cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay,
                                 const plora_desc* table, float* S, size_t s_stride_elems, int lds, int kchunk,
                                 int nsplit, int work_cap, int max_rank_total, int* status, bool pdl, bool early,

@@ -520,6 +520,305 @@ __global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __re
     TRACE(7);
 }
 
+// ------------------------------------------------------------------------------------------------------
+// The same expand with y moved by tensor copies, for outputs whose base, row pitch and part offsets are
+// 16-byte aligned (every model width in practice; the kernel above stays for the rest). 256 threads. Each warp
+// owns the 32 token rows tensor memory gives it (two warps per 32 rows, taking alternate slots of columns) and
+// a private ring of 4 KB slots; a slot holds 32 rows x 128 bytes of y
+// (64 bf16 or 32 f32 columns, 128-byte swizzle). Lane 0 keeps the ring full of loads; a landed slot gets the
+// accumulator columns added in shared memory (thread = row: with the swizzle, eight rows cover all banks) and
+// goes back with a tensor store, whose completion frees the slot for the next load. So the read-modify-write
+// of y, which is most of the bytes of a prefill step, is asynchronous on both sides and many slots deep. The
+// accumulator is double-buffered in tensor memory: the MMAs of the next column block run during this block's
+// additions. Tensor maps are per part and end at the part's last column, so a box at the edge is clipped
+// instead of touching the next part's columns. A warp whose 32 rows are not all inside the tile (the tail of
+// a run) loads the same way but writes its live rows with plain stores: the other rows belong to other tokens.
+struct ExpandYMaps {
+    CUtensorMap m[PLORA_MAX_PARTS];
+};
+#define EXP_RING_MAX 8
+#define EXP_SLOT_BYTES 4096
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, const void* src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0), "r"(c1),
+                 "r"(smem_u32(src))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+template <bool F32>
+__global__ void __launch_bounds__(256) plora_expand_tma_kernel(const float* __restrict__ S, size_t s_stride, int lds, int K,
+                                                                int ksplit, const int* __restrict__ segs, SegLayout lay,
+                                                                const plora_desc* __restrict__ table,
+                                                                const __grid_constant__ ExpandYMaps ymaps, void* Y, int ldy,
+                                                                int nb_per_cta, int op_bytes, int nst,
+                                                                int* __restrict__ status) {
+    extern __shared__ unsigned char dsm_raw[];
+    __shared__ __align__(8) uint64_t done[2], ybar[8][EXP_RING_MAX];
+    __shared__ uint32_t tmem_slot;
+    constexpr int CW = F32 ? 32 : 64;  // y columns per slot
+    constexpr int CH = 128 / CW;       // slots per block of 128 columns
+    const int tile = blockIdx.z;
+    const int n_mma = segs[SEG_N_MMA];
+    const int* mt = segs + lay.mma() + 3 * tile;
+    const int start = mt[0], len = mt[1], slot = mt[2];
+    if (tile >= n_mma) return pdl_exit_idle();
+    const plora_desc& d = table[slot];
+    const int p = blockIdx.y, r = d.r[p];
+    if (r == 0) return pdl_exit_idle();
+    const int rows = d.rows[p];
+    const int cb0 = blockIdx.x * nb_per_cta;
+    if (cb0 * 128 >= rows) return pdl_exit_idle();
+    const int nblk = min(nb_per_cta, (rows - cb0 * 128 + 127) / 128);
+    const int nchunks = min(nblk * CH, (rows - cb0 * 128 + CW - 1) / CW);  // slots this block fills, in column order
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    unsigned char* dsm = dsm_raw + ((1024u - (smem_u32(dsm_raw) & 1023u)) & 1023u);
+    unsigned char* ring = dsm + (size_t)warp * nst * EXP_SLOT_BYTES;  // this warp's slots
+    unsigned char* ops = dsm + (size_t)8 * nst * EXP_SLOT_BYTES;
+    // Eight warps: warps w and w + 4 read the same 32 lanes of tensor memory (rows 32 (w % 4) ...) and take
+    // the even and the odd slots of every column block.
+    const int wq = warp & 3, wh = warp >> 2;
+    constexpr int CPW = CH / 2;  // slots per column block and warp
+    unsigned char* Ahi = ops;
+    unsigned char* Alo = ops + op_bytes;
+    unsigned char* Bs[2] = {ops + 2 * (size_t)op_bytes, ops + 3 * (size_t)op_bytes};
+    const bf16* B = reinterpret_cast<const bf16*>(d.b[p]);
+    const uint32_t sbo = (uint32_t)r * 16u;  // 8-row group stride
+    const int P = r >> 3;
+    const CUtensorMap* ymap = &ymaps.m[p];
+
+    auto load_b = [&](int cb, unsigned char* dst) {
+        const int n = tid & 127;  // row of B = output column of the block; the two halves of the block share its chunks
+        const bool valid = cb * 128 + n < rows;
+        const bf16* src = B + (size_t)(valid ? cb * 128 + n : 0) * r;
+        unsigned char* drow = dst + (size_t)(n >> 3) * sbo + (n & 7) * 16;
+        for (int j = tid >> 7; j < P; j += 2) cp_async16(drow + j * 128, src + j * 8, valid);
+    };
+
+    if (tid == 0) {
+        mbar_init(&done[0], 1);
+        mbar_init(&done[1], 1);
+        for (int w = 0; w < 8; w++)
+            for (int i = 0; i < nst; i++) mbar_init(&ybar[w][i], 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 256);
+    load_b(cb0, Bs[0]);  // B is a slab: it may be fetched before the kernels ahead have finished
+    cp_async_commit();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    pdl_wait();
+    pdl_trigger();
+
+    const int wrow0 = wq * 32;
+    const bool live = wrow0 < len;            // the warp has rows of the tile
+    const bool whole = wrow0 + 32 <= len;     // all its 32 rows are: results go back by tensor store
+    const int ycol0 = d.off[p] + cb0 * 128;   // first y column of this block's range
+    // the warp's i-th slot is slot q of the block's column range
+    auto slot_of = [&](int i) { return (i / CPW) * CH + wh + 2 * (i % CPW); };
+    int my_n = 0;  // slots this warp handles
+    while (slot_of(my_n) < nchunks) my_n++;
+    auto load_y = [&](int i) {                // lane 0 only
+        uint64_t* bar = &ybar[warp][i % nst];
+        mbar_expect_tx(bar, EXP_SLOT_BYTES);
+        tma_load_2d(ring + (size_t)(i % nst) * EXP_SLOT_BYTES, ymap, ycol0 + slot_of(i) * CW, start + wrow0, bar);
+    };
+    if (live && lane == 0)
+        for (int i = 0; i < nst && i < my_n; i++) load_y(i);
+
+    // this thread's token row of S, split into a bf16 high part and the bf16 of what is left
+    {
+        const int row = tid & 127;
+        const bool valid = row < len;
+        const float* sp = S + (size_t)(start + (valid ? row : 0)) * lds + d.r_off[p];
+        const int s_eff = min(ksplit, plora_tile_chunks(K, d.rank));  // planes the shrink wrote for this slot
+        unsigned char* ahi = Ahi + (size_t)(row >> 3) * sbo + (row & 7) * 16;
+        unsigned char* alo = Alo + (size_t)(row >> 3) * sbo + (row & 7) * 16;
+        for (int j = tid >> 7; j < P; j += 2) {
+            float f[8];
+            if (valid && s_eff > 1) {
+                float v[PLORA_TILE_SPLIT_MAX][8];
+#pragma unroll
+                for (int s = 0; s < PLORA_TILE_SPLIT_MAX; s++)
+                    if (s < s_eff) {
+                        const float* q = sp + (size_t)s * s_stride + j * 8;
+                        const float4 a = __ldcg(reinterpret_cast<const float4*>(q));
+                        const float4 b = __ldcg(reinterpret_cast<const float4*>(q + 4));
+                        v[s][0] = a.x, v[s][1] = a.y, v[s][2] = a.z, v[s][3] = a.w;
+                        v[s][4] = b.x, v[s][5] = b.y, v[s][6] = b.z, v[s][7] = b.w;
+                    }
+                tree_sum<8>(v, s_eff);
+#pragma unroll
+                for (int e = 0; e < 8; e++) f[e] = v[0][e];
+            } else if (valid) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(sp + j * 8));
+                const float4 b = __ldcg(reinterpret_cast<const float4*>(sp + j * 8 + 4));
+                f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; e++) f[e] = 0.f;
+            }
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+                const float2 hf = __bfloat1622float2(h);
+                const __nv_bfloat162 l = __floats2bfloat162_rn(f[2 * e] - hf.x, f[2 * e + 1] - hf.y);
+                hi[e] = *reinterpret_cast<const uint32_t*>(&h);
+                lo[e] = *reinterpret_cast<const uint32_t*>(&l);
+            }
+            *reinterpret_cast<uint4*>(ahi + j * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4*>(alo + j * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+    }
+    const uint32_t idesc = umma_idesc_bf16(MMA_M, 128);
+    auto issue_mma = [&](int nb) {  // one elected thread of warp 0
+        const uint32_t a_hi = smem_u32(Ahi), a_lo = smem_u32(Alo), b = smem_u32(Bs[nb & 1]);
+        const uint32_t acc = tmem + (uint32_t)(nb & 1) * 128u;
+        for (int kk = 0; kk < r / 16; kk++)
+            umma_bf16(acc, umma_desc(a_hi + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, kk != 0);
+        for (int kk = 0; kk < r / 16; kk++)
+            umma_bf16(acc, umma_desc(a_lo + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, 1);
+        umma_commit(&done[nb & 1]);
+    };
+    // block 0's MMAs, then the copy of block 1's rows of B behind them
+    cp_async_wait<0>();
+    fence_async_smem();
+    __syncthreads();
+    if (warp == 0) {
+        if (elect_one()) {
+            tc_fence_after();
+            issue_mma(0);
+        }
+        __syncwarp();
+    }
+    if (nblk > 1) load_b(cb0 + 1, Bs[1]);
+    cp_async_commit();
+
+    bool ok = true;
+    for (int nb = 0; nb < nblk; nb++) {
+        // everyone is done with the block before last: its accumulator is free, and block nb + 1's B has landed
+        cp_async_wait<0>();
+        fence_async_smem();
+        tc_fence_before();
+        if (__syncthreads_or(!ok)) {
+            ok = false;
+            break;
+        }
+        if (nb + 1 < nblk && warp == 0) {
+            if (elect_one()) {
+                tc_fence_after();
+                issue_mma(nb + 1);
+            }
+            __syncwarp();
+        }
+        ok = mbar_wait(&done[nb & 1], (nb >> 1) & 1, status);
+        if (!ok) continue;  // meets the others at the barrier above, and all leave
+        tc_fence_after();
+        if (nb + 2 < nblk) load_b(cb0 + nb + 2, Bs[nb & 1]);  // block nb's MMAs are complete: its B buffer is free
+        cp_async_commit();
+        if (!live) continue;
+        const uint32_t acc = tmem + ((uint32_t)wrow0 << 16) + (uint32_t)(nb & 1) * 128u;
+#pragma unroll 1
+        for (int ci = 0; ci < CPW; ci++) {
+            const int i = nb * CPW + ci;  // the warp's slot counter
+            if (i >= my_n) break;
+            const int ch = wh + 2 * ci, q = nb * CH + ch;
+            unsigned char* sl = ring + (size_t)(i % nst) * EXP_SLOT_BYTES;
+            if (!mbar_wait(&ybar[warp][i % nst], (i / nst) & 1, status)) {
+                ok = false;
+                break;
+            }
+            unsigned char* myrow = sl + lane * 128;
+            const int col0 = (cb0 + nb) * 128 + ch * CW;  // first column of the slot within the part
+            const bool mine = wrow0 + lane < len;
+            if (F32) {
+                uint32_t v[32];
+                tmem_ld32(acc + ch * 32, v);
+                float* yrow = reinterpret_cast<float*>(Y) + (size_t)(start + wrow0 + lane) * ldy + d.off[p] + col0;
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    float4* at = reinterpret_cast<float4*>(myrow + ((c ^ (lane & 7)) << 4));
+                    float4 y = *at;
+                    y.x += __uint_as_float(v[4 * c]), y.y += __uint_as_float(v[4 * c + 1]);
+                    y.z += __uint_as_float(v[4 * c + 2]), y.w += __uint_as_float(v[4 * c + 3]);
+                    if (whole) {
+                        *at = y;
+                    } else if (mine) {
+                        if (col0 + 4 * c + 4 <= rows) {
+                            *reinterpret_cast<float4*>(yrow + 4 * c) = y;
+                        } else {
+                            const float e[4] = {y.x, y.y, y.z, y.w};
+                            for (int i = 0; i < 4; i++)
+                                if (col0 + 4 * c + i < rows) yrow[4 * c + i] = e[i];
+                        }
+                    }
+                }
+            } else {
+                bf16* yrow = reinterpret_cast<bf16*>(Y) + (size_t)(start + wrow0 + lane) * ldy + d.off[p] + col0;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    uint32_t v[32];
+                    tmem_ld32(acc + ch * 64 + h * 32, v);
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; c4++) {
+                        const int c = h * 4 + c4;
+                        uint4* at = reinterpret_cast<uint4*>(myrow + ((c ^ (lane & 7)) << 4));
+                        const uint4 raw = *at;
+                        float f[8];
+                        unpack8(raw, f);
+                        uint32_t o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(f[2 * e] + __uint_as_float(v[8 * c4 + 2 * e]),
+                                                                            f[2 * e + 1] + __uint_as_float(v[8 * c4 + 2 * e + 1]));
+                            o[e] = *reinterpret_cast<const uint32_t*>(&b2);
+                        }
+                        if (whole) {
+                            *at = make_uint4(o[0], o[1], o[2], o[3]);
+                        } else if (mine) {
+                            if (col0 + 8 * c + 8 <= rows) {
+                                *reinterpret_cast<uint4*>(yrow + 8 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+                            } else {
+                                const bf16* e = reinterpret_cast<const bf16*>(o);
+                                for (int i = 0; i < 8; i++)
+                                    if (col0 + 8 * c + i < rows) yrow[8 * c + i] = e[i];
+                            }
+                        }
+                    }
+                }
+            }
+            if (whole) fence_async_smem();  // the additions above, before the tensor store reads them
+            __syncwarp();
+            if (lane == 0) {
+                if (whole) {
+                    tma_store_2d(ymap, ycol0 + q * CW, start + wrow0, sl);
+                    bulk_commit();
+                    if (nst == 1) {  // one slot: wait for this store to have read it, then refill it
+                        bulk_wait_read_0();
+                        if (i + 1 < my_n) load_y(i + 1);
+                    } else {  // the store before this one has read its slot: refill that slot
+                        bulk_wait_read_1();
+                        if (i >= 1 && i - 1 + nst < my_n) load_y(i - 1 + nst);
+                    }
+                } else if (i + nst < my_n) {
+                    load_y(i + nst);  // plain stores: the slot is free at once
+                }
+            }
+        }
+    }
+    if (lane == 0) bulk_wait_all();
+    cp_async_wait<0>();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
 // cuTensorMapEncodeTiled, fetched from the driver once (no link-time dependency on libcuda)
 typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -541,7 +840,11 @@ cudaError_t plora_mma_init() {
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(plora_expand_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 172 * 1024);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(plora_expand_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 172 * 1024);
+    e = cudaFuncSetAttribute(plora_expand_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 172 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(plora_expand_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(plora_expand_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
 }
 
 namespace {
@@ -604,8 +907,8 @@ cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, con
 
 cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int lds, int K, int tile_split,
                                     const int32_t* segs, SegLayout lay, const plora_desc* table, void* y, int ldy,
-                                    int f32_out, int parts, int max_rows, int tile_cap, int* status, bool pdl,
-                                    cudaStream_t st) {
+                                    int f32_out, int parts, const int* part_off, const int* part_rows, int rows_total,
+                                    int max_rows, int tile_cap, int* status, bool pdl, cudaStream_t st) {
     const int max_rank = lds / PLORA_MAX_PARTS;
     const int op_bytes = MMA_M * max_rank * 2;
     const int nblocks = (max_rows + 127) / 128;
@@ -616,6 +919,36 @@ cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int l
     nb_per_cta = nb_per_cta < 1 ? 1 : nb_per_cta > 8 ? 8 : nb_per_cta;
     if (nb_per_cta > nblocks) nb_per_cta = nblocks;
     dim3 grid((unsigned)((nblocks + nb_per_cta - 1) / nb_per_cta), (unsigned)parts, (unsigned)tile_cap);
+    // y by tensor copies where its base, pitch and part offsets are 16-byte aligned
+    const int elt = f32_out ? 4 : 2;
+    bool aligned = g_encode && ((uintptr_t)y & 15) == 0 && ((size_t)ldy * elt) % 16 == 0 && rows_total > 0;
+    for (int p = 0; p < parts; p++) aligned = aligned && ((size_t)part_off[p] * elt) % 16 == 0;
+    // ring slots per warp: what two blocks per SM leave room for, else what one block per SM does
+    int nst = (111 * 1024 - 1024 - 4 * op_bytes) / (8 * EXP_SLOT_BYTES);
+    if (nst < 1) nst = (216 * 1024 - 1024 - 4 * op_bytes) / (8 * EXP_SLOT_BYTES);
+    nst = nst > 4 ? 4 : nst;
+    if (aligned && nst >= 1) {
+        ExpandYMaps maps;
+        memset(&maps, 0, sizeof(maps));
+        const cuuint32_t es[2] = {1, 1};
+        const cuuint32_t box[2] = {(cuuint32_t)(128 / elt), 32};
+        const cuuint64_t strides[1] = {(cuuint64_t)ldy * elt};
+        for (int p = 0; p < parts && aligned; p++) {
+            // the map ends at the part's last column: a box over the edge is clipped
+            const cuuint64_t dims[2] = {(cuuint64_t)(part_off[p] + part_rows[p]), (cuuint64_t)rows_total};
+            aligned = g_encode(&maps.m[p], f32_out ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y,
+                               dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+        }
+        if (aligned) {
+            const size_t smem_tma = 1024 + (size_t)8 * nst * EXP_SLOT_BYTES + (size_t)4 * op_bytes;
+            if (f32_out)
+                return launch_pdl(plora_expand_tma_kernel<true>, grid, dim3(256), smem_tma, st, pdl, S, s_stride_elems, lds, K,
+                                  tile_split, segs, lay, table, maps, y, ldy, nb_per_cta, op_bytes, nst, status);
+            return launch_pdl(plora_expand_tma_kernel<false>, grid, dim3(256), smem_tma, st, pdl, S, s_stride_elems, lds, K,
+                              tile_split, segs, lay, table, maps, y, ldy, nb_per_cta, op_bytes, nst, status);
+        }
+    }
     // at least 48 KB of shared memory per block: no more than four blocks, 128 tensor-memory columns each,
     // share an SM's 512 columns
     size_t smem = (size_t)4 * op_bytes + (size_t)4 * 32 * EXP_TPAD * sizeof(float);
