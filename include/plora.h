@@ -214,6 +214,18 @@ int plora_expand(plora_t* h, const plora_hook* hook, const plora_step* step, int
 int plora_fp8_quant_rows(plora_t* h, uint64_t x, int rows, int cols, uint64_t xq, uint64_t st, void* stream);
 int plora_linear_fp8_fused(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t xq, uint64_t st,
                            uint64_t wq, uint64_t sn, int rows, uint64_t y, int ldy, int f32_out, void* stream);
+/* The same for a bf16 layer: y = x w^T + adapter term, x [rows, cols] and w [width, cols] bf16 row-major, y
+ * written once. The engine runs its bf16 matrix multiply and then lora_expand as a read-modify-write pass over y
+ * (src/linear.rs:844-847, 889-921). One kernel does the base product and the adapter term of every long run of
+ * tokens on the tensor cores; tokens outside long runs get their term from the gather kernel afterwards.
+ * Needs x, w, y 16-byte aligned, pitches that are multiples of 16 bytes, and every part starting at a multiple
+ * of 256 columns (PLORA_ERR_ARG otherwise). Call plora_shrink first. */
+int plora_linear_bf16_fused(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, uint64_t w, int rows,
+                            uint64_t y, int ldy, int f32_out, void* stream);
+/* plora_linear_fp8_fused uses that same one-kernel form (with the FP8 scales) for steps of at least this many
+ * rows, where the layer's shapes meet the conditions above; smaller steps keep the decode-shaped kernel, which
+ * builds the adapter term of mixed tokens on the CUDA cores. Default 1024. */
+int plora_set_fused_tile_rows(plora_t* h, int rows);
 
 /* Shrink and expand of one layer in one call, for callers whose x and y are both ready (that is, after the
  * layer's own matrix multiply, where Linear::forward issues lora_expand: src/linear.rs:844-847). Same results

@@ -123,6 +123,8 @@ SYMBOLS = {
     "plora_fp8_quant_rows": (_I, [_P, _U64, _I, _I, _U64, _U64, _P]),
     "plora_linear_fp8_fused": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _U64, _U64, _U64, _U64, _I, _U64, _I, _I,
                                     _P]),
+    "plora_linear_bf16_fused": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _U64, _U64, _I, _U64, _I, _I, _P]),
+    "plora_set_fused_tile_rows": (_I, [_P, _I]),
     "plora_apply": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _U64, _I, _U64, _I, _I, _P]),
     "plora_set_apply_mode": (_I, [_P, _I]),
     "plora_s_reduce": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _P]),
@@ -449,6 +451,14 @@ class Loras:
     def set_apply_mode(self, mode):
         """0: apply() = shrink / expand pair with early activation loads; 1: one cluster kernel per layer."""
         self._check(lib.plora_set_apply_mode(self._h, mode))
+
+    def linear_bf16_fused(self, hook, step, x, w, rows, y, ldy, f32_out=False, stream=0):
+        """y = x w^T + adapter term in one tensor-core kernel (bf16 x [rows, cols] and w [width, cols]); shrink first."""
+        self._check(lib.plora_linear_bf16_fused(self._h, C.byref(hook), C.byref(step), x, w, rows, y, ldy, int(f32_out),
+                                                _P(stream)))
+
+    def set_fused_tile_rows(self, rows):
+        self._check(lib.plora_set_fused_tile_rows(self._h, rows))
 
     def s_reduce(self, hook, step, rows, stream=0):
         """Adds the shrink's K-split partials into plane 0 of S (before a tensor-parallel all-reduce)."""

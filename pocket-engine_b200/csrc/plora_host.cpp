@@ -211,6 +211,7 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
                 s.cluster_ok = h->site_ok && plora_site_plan(s.cols, (int)s.parts.size(), h->max_rank, total, &a, &b, &c, &d2, &e) > 0;
             }
             if (rc == PLORA_OK && h->max_rank <= 128) h->fp8_ok = plora_fp8_init(h->max_rank) == cudaSuccess;
+            if (rc == PLORA_OK && h->mma_ok) h->gemm_ok = plora_gemm_init() == cudaSuccess;
             // runs of 64 or more contiguous tokens of one slot take the tensor-core tile kernels
             if (h->mma_ok) h->seg.run_min = PLORA_RUN_MIN_DEFAULT;
             if (const char* e = getenv("PLORA_PDL")) h->pdl = e[0] != '0';
@@ -827,6 +828,60 @@ int plora_fp8_quant_rows(plora_t* h, uint64_t x, int rows, int cols, uint64_t xq
     return PLORA_OK;
 }
 
+// The one-kernel layer (plora_gemm.cu) followed by the gather expand from plane 0 for the tokens outside long
+// runs. The caller has already reduced S to plane 0.
+static int gemm_layer(plora_t* h, const plora_hook* hook, const plora_step* step, int kind, uint64_t x, uint64_t st,
+                      uint64_t w, uint64_t sn, int rows, int width, uint64_t y, int ldy, int f32_out, int work_cap,
+                      void* stream) {
+    const SiteInfo& site = h->sites[(size_t)hook->site];
+    CU(h, "fused layer (tensor-core adapter term)",
+       plora_launch_gemm_fused(kind, (const void*)(uintptr_t)x, (const float*)(uintptr_t)st, (const void*)(uintptr_t)w,
+                               (const float*)(uintptr_t)sn, rows, width, site.cols, (const int32_t*)(uintptr_t)step->segs,
+                               h->seg, (const plora_desc*)(uintptr_t)hook->table, (int)site.parts.size(), site.part_off,
+                               site.part_rows, (const float*)(uintptr_t)step->s, step->lds, (void*)(uintptr_t)y, ldy, f32_out,
+                               h->status, h->pdl, as_stream(stream)));
+    if (work_cap > 0)
+        CU(h, "expand (tokens outside long runs)",
+           plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, 1,
+                               (const int32_t*)(uintptr_t)step->segs, h->seg, (const plora_desc*)(uintptr_t)hook->table,
+                               (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap, h->status, h->pdl,
+                               false, as_stream(stream)));
+    return PLORA_OK;
+}
+
+int plora_linear_bf16_fused(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, uint64_t w, int rows,
+                            uint64_t y, int ldy, int f32_out, void* stream) {
+    if (!h || !hook || !step) return PLORA_ERR_ARG;
+    if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
+    if (!h->gemm_ok) return fail(h, PLORA_ERR_CONFIG, "the fused layer needs max_rank <= 128");
+    if (hook->site < 0 || hook->site >= (int)h->sites.size()) return fail(h, PLORA_ERR_ARG, "hook names no site");
+    if (rows < 0 || rows > h->max_tokens) return fail(h, PLORA_ERR_CAPACITY, "more rows than max_tokens");
+    const SiteInfo& site = h->sites[(size_t)hook->site];
+    if (rows == 0) return PLORA_OK;
+    int width = 0;
+    for (auto& p : site.parts) width = std::max(width, p.off + p.rows);
+    if (!x || !w || !y ||
+        !plora_gemm_fits(1, (const void*)(uintptr_t)x, (const void*)(uintptr_t)w, (const void*)(uintptr_t)y, ldy, f32_out,
+                         site.cols, (int)site.parts.size(), site.part_off))
+        return fail(h, PLORA_ERR_ARG,
+                    "x, w and y must be 16-byte aligned with 16-byte multiple pitches, and parts must start at multiples of 256 columns");
+    int work_cap = std::min(std::min(step->max_tiles, rows), h->max_slots + rows / PLORA_WORK_TOKENS);
+    const bool pdl = h->pdl && h->pdl_armed;
+    h->pdl_armed = true;
+    CU(h, "S reduce", plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
+                                            (const int32_t*)(uintptr_t)step->segs, h->seg,
+                                            (const plora_desc*)(uintptr_t)hook->table, work_cap,
+                                            h->mma_ok && rows >= step->run_min ? std::max(1, rows / 64) : 0,
+                                            tile_split(h, rows), site.cols, pdl, as_stream(stream)));
+    return gemm_layer(h, hook, step, 1, x, 0, w, 0, rows, width, y, ldy, f32_out, work_cap, stream);
+}
+
+int plora_set_fused_tile_rows(plora_t* h, int rows) {
+    if (!h || rows < 1) return PLORA_ERR_ARG;
+    h->fused_tile_rows = rows;
+    return PLORA_OK;
+}
+
 int plora_linear_fp8_fused(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t xq, uint64_t st,
                            uint64_t wq, uint64_t sn, int rows, uint64_t y, int ldy, int f32_out, void* stream) {
     if (!h || !hook || !step) return PLORA_ERR_ARG;
@@ -853,6 +908,12 @@ int plora_linear_fp8_fused(plora_t* h, const plora_hook* hook, const plora_step*
                                             (const plora_desc*)(uintptr_t)hook->table, work_cap,
                                             h->mma_ok && rows >= step->run_min ? std::max(1, rows / 64) : 0,
                                             tile_split(h, rows), site.cols, pdl, as_stream(stream)));
+    // prefill-sized steps: base product and the long runs' adapter term on the tensor cores in one kernel, then
+    // the gather kernel for the tokens outside long runs
+    if (h->gemm_ok && rows >= h->fused_tile_rows && rows >= step->run_min &&
+        plora_gemm_fits(0, (const void*)(uintptr_t)xq, (const void*)(uintptr_t)wq, (const void*)(uintptr_t)y, ldy, f32_out,
+                        site.cols, (int)site.parts.size(), off))
+        return gemm_layer(h, hook, step, 0, xq, st, wq, sn, rows, width, y, ldy, f32_out, work_cap, stream);
     CU(h, "fused fp8 layer",
        plora_launch_fp8_fused((const void*)(uintptr_t)xq, (const float*)(uintptr_t)st, (const void*)(uintptr_t)wq,
                               (const float*)(uintptr_t)sn, rows, width, site.cols, (const int32_t*)(uintptr_t)step->segs,

@@ -122,6 +122,8 @@ struct plora {
     int apply_mode = 0;     // plora_apply: 0 = shrink/expand pair with early loads, 1 = one cluster kernel per layer
     bool site_ok = false;   // the cluster kernel's attributes were set
     bool fp8_ok = false;    // the fused FP8 layer can run
+    bool gemm_ok = false;   // the one-kernel layer for prefill-sized steps can run
+    int fused_tile_rows = 1024;  // steps with at least this many rows take it (plora_set_fused_tile_rows)
     bool mma_ok = false;    // the tensor-core tile kernels can run (max_rank <= 128 and the driver entry point exists)
     bool pdl_armed = false;  // false right after the step's grouping kernel: the next launch is a plain one
 };
@@ -184,6 +186,13 @@ cudaError_t plora_launch_fp8_fused(const void* xq, const float* st_, const void*
                                    const int32_t* segs, SegLayout lay, const plora_desc* table, int n_parts,
                                    const int* part_off, const int* part_rows, const float* S, int lds, void* y, int ldy,
                                    int f32_out, int max_rank, int* status, bool pdl, cudaStream_t stream);
+cudaError_t plora_gemm_init();
+bool plora_gemm_fits(int kind, const void* x, const void* w, const void* y, int ldy, int f32_out, int K, int n_parts,
+                     const int* part_off);
+cudaError_t plora_launch_gemm_fused(int kind, const void* x, const float* st_, const void* w, const float* sn, int T, int N,
+                                    int K, const int32_t* segs, SegLayout lay, const plora_desc* table, int n_parts,
+                                    const int* part_off, const int* part_rows, const float* S, int lds, void* y, int ldy,
+                                    int f32_out, int* status, bool pdl, cudaStream_t stream);
 cudaError_t plora_mma_encode_slab(void* out128, const void* a, int K, int R);
 cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, const int32_t* segs, SegLayout lay,
                                     const plora_desc* table, const PloraTmap* amaps, float* S, size_t s_stride_elems, int lds,

@@ -45,16 +45,34 @@ CASES = [
     ("all-base", [5, 9], [0, 0], [16], 256, [("gate", 64)]),
 ]
 
+# shapes the one-kernel prefill form takes (parts starting at multiples of 256 columns, aligned pitches): runs of
+# all lengths against the 128-row blocks, decode tokens in between, a rank over 64 (two passes), a ragged edge
+TILE_CASES = [
+    ("prompts-and-decode-two-parts", [1] * 30 + [128, 200, 70, 64] + [1] * 5, None, [64, 128, 16], 640,
+     [("gate", 512), ("up", 296)]),
+    ("one-long-prompt", [700], [1], [32], 1024, [("gate", 256)]),
+    ("short-prompts-only", [40, 63, 17], [1, 2, 1], [16, 48], 256, [("gate", 520)]),
+]
 
-@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
-def test_fused_fp8_layer_matches_the_oracle(pe, oracle, case):
+
+def _slots(case):
+    name, rows, slots, ranks, K, mods = case
+    if slots is None:
+        rng = np.random.default_rng(len(rows))
+        slots = rng.integers(0, len(ranks) + 1, len(rows))
+    return slots
+
+
+ALL_CASES = [(c, False) for c in CASES] + [(c, True) for c in TILE_CASES]
+
+
+@pytest.mark.parametrize("case,tile_form", ALL_CASES, ids=[c[0] + ("-one-kernel" if t else "") for c, t in ALL_CASES])
+def test_fused_fp8_layer_matches_the_oracle(pe, oracle, case, tile_form):
     from pocket_engine_b200 import workloads as wls
     import torch
     name, rows, slots, ranks, K, mods = case
     sites = [pe.Site.fused(0, K, mods)]
-    if slots is None:
-        rng = np.random.default_rng(len(rows))
-        slots = rng.integers(0, len(ranks) + 1, len(rows))
+    slots = _slots(case)
     wl = wls.Workload(name, sites, ranks, 1.0, rows, slots, 13, max_rank=128)
     N = sites[0].width()
     wq, sn = _weights(N, K, 5)
@@ -63,10 +81,13 @@ def test_fused_fp8_layer_matches_the_oracle(pe, oracle, case):
     table, _ = harness.oracle_registry(wl)
     tiles = harness.tiles_of(pe, wl)
     y64 = oracle.fp8_base_f64(xq, st, wq, sn)
+    base_abs = np.abs(y64)
     oracle.site_f64(xb, K, tiles, table.tables[0], y64)
     rms = float(np.sqrt(np.mean(y64 ** 2)))
 
     loras = harness.product_registry(pe, wl)
+    if tile_form:
+        loras.set_fused_tile_rows(1)  # the prefill-sized form (tensor-core adapter term) whatever the step's size
     stream = torch.cuda.current_stream().cuda_stream
     x = harness.to_dev_bf16(xb, 0)
     xq_d = torch.zeros(wl.tokens, K, dtype=torch.uint8, device="cuda")
@@ -90,7 +111,68 @@ def test_fused_fp8_layer_matches_the_oracle(pe, oracle, case):
             assert d.max() <= harness.MAX_TOL * rms and d.mean() <= harness.MEAN_TOL * rms, (name, d.max() / rms, d.mean() / rms)
             assert d.max() <= 2e-4 * rms, (name, d.max() / rms)  # f32 accumulation: far inside the stated bound
         else:
-            # one bf16 rounding of the result: within half a bf16 step (2^-9 relative) plus the f32 error
-            assert np.all(d <= np.abs(y64) * 2.0 ** -8 + 2e-4 * rms), (name, float((d / rms).max()))
+            # one bf16 rounding of the result: within half a bf16 step (2^-9 relative) plus the f32 error. In the
+            # one-kernel form the tokens outside long runs get their adapter term from the gather kernel afterwards,
+            # as in the engine (lora_expand after the layer's GEMM): the base is rounded to bf16 first, then the sum.
+            slack = base_abs * 2.0 ** -8 if tile_form else 0.0
+            assert np.all(d <= np.abs(y64) * 2.0 ** -8 + slack + 2e-4 * rms), (name, float((d / rms).max()))
     assert np.array_equal(xq_d.cpu().numpy(), xq)
+    loras.close()
+
+
+@pytest.mark.parametrize("case", TILE_CASES, ids=[c[0] for c in TILE_CASES])
+def test_fused_bf16_layer_matches_the_oracle(pe, oracle, case):
+    """y = x W^T + adapter term written once by the one-kernel layer, against the fp64 product of the same bf16
+    operands plus the oracle's adapter term."""
+    from pocket_engine_b200 import workloads as wls
+    import torch
+    name, rows, slots, ranks, K, mods = case
+    sites = [pe.Site.fused(0, K, mods)]
+    wl = wls.Workload(name, sites, ranks, 1.0, rows, _slots(case), 17, max_rank=128)
+    N = sites[0].width()
+    rng = np.random.default_rng(23)
+    wb = pe.bf16_bits(rng.standard_normal((N, K), dtype=np.float32) / np.float32(np.sqrt(K)))
+    xb = wl.x_bits(0)
+    xf = pe.bf16_to_f32(xb).reshape(wl.tokens, K).astype(np.float64)
+    wf = pe.bf16_to_f32(wb).reshape(N, K).astype(np.float64)
+    table, _ = harness.oracle_registry(wl)
+    tiles = harness.tiles_of(pe, wl)
+    y64 = xf @ wf.T
+    base_abs = np.abs(y64)
+    oracle.site_f64(xb, K, tiles, table.tables[0], y64)
+    rms = float(np.sqrt(np.mean(y64 ** 2)))
+    loras = harness.product_registry(pe, wl)
+    stream = torch.cuda.current_stream().cuda_stream
+    x = harness.to_dev_bf16(xb, 0)
+    w = harness.to_dev_bf16(wb, 0)
+    for f32_out in (True, False):
+        y = torch.full((wl.tokens, N), 7.0, dtype=torch.float32 if f32_out else torch.bfloat16, device="cuda")
+        loras.meta_upload(tiles, stream)
+        step = loras.lora_step(loras.max_lora_tiles(), stream)
+        hook = loras.hook(0)
+        loras.shrink(hook, step, x.data_ptr(), wl.tokens, stream)
+        loras.linear_bf16_fused(hook, step, x.data_ptr(), w.data_ptr(), wl.tokens, y.data_ptr(), N, f32_out, stream)
+        torch.cuda.synchronize()
+        loras.device_status()
+        d = np.abs(y.float().cpu().numpy().astype(np.float64) - y64)
+        if f32_out:
+            assert d.max() <= 2e-4 * rms and d.mean() <= harness.MEAN_TOL * rms, (name, d.max() / rms, d.mean() / rms)
+        else:
+            # tokens outside long runs: base rounded to bf16, then the sum rounded again (as in the engine)
+            assert np.all(d <= (np.abs(y64) + base_abs) * 2.0 ** -8 + 2e-4 * rms), (name, float((d / rms).max()))
+    loras.close()
+
+
+def test_fused_bf16_layer_rejects_unaligned_shapes(pe):
+    import torch
+    sites = [pe.Site.fused(0, 256, [("gate", 130), ("up", 64)])]  # the second part starts at column 130
+    loras = pe.Loras(sites, 2, 16, 64, 4, device=0)
+    x = torch.zeros(8, 256, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(194, 256, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(8, 200, dtype=torch.bfloat16, device="cuda")
+    loras.meta_upload(pe.fill_tiles([8], [0], loras.max_lora_tiles()))
+    step = loras.lora_step(loras.max_lora_tiles())
+    with pytest.raises(pe.PloraError) as err:
+        loras.linear_bf16_fused(loras.hook(0), step, x.data_ptr(), w.data_ptr(), 8, y.data_ptr(), 200)
+    assert err.value.code == pe.ERR_ARG
     loras.close()
