@@ -465,6 +465,84 @@ def run_fp8(args, rank, world, local_rank):
             "clocks": clocks}
 
 
+def run_fused_bf16(args, rank, world, local_rank):
+    """The prefill block with its bf16 base layers: a step = the four layers of one transformer block over 8 x 2048
+    tokens, each as y = x W^T + adapter term. Two ways, timed the same way: (a) the engine's order, a library bf16
+    matrix multiply (cuBLAS through torch.matmul) followed by shrink and the read-modify-write expand; (b) shrink,
+    then the library's one-kernel layer (base product and adapter term on the tensor cores, y written once)."""
+    import torch
+    pe = entry.load_package()
+    from pocket_engine_b200 import workloads
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    wl = workloads.config3(seed=1000 * rank, seqs=args.seqs)
+    ns, T = len(wl.sites), wl.tokens
+    main = torch.cuda.Stream(device=dev)
+    L = pe.Loras(wl.sites, wl.n_adapters, wl.max_rank, T, wl.n_seqs, device=local_rank)
+    prep = L.prep()
+    for i in range(wl.n_adapters):
+        L.upload(i + 1, L.insert(prep.prepare(f"a{i}", wl.factors(i))), main.cuda_stream)
+    g = torch.Generator(device=dev).manual_seed(5 + rank)
+    xs = [torch.from_numpy(wl.x_bits(si).view(np.int16)).to(dev).view(torch.bfloat16) for si in range(ns)]
+    ws = [(torch.randn(s.width(), s.cols, device=dev, generator=g) / s.cols ** 0.5).to(torch.bfloat16) for s in wl.sites]
+    ys = [torch.zeros(T, s.width(), dtype=torch.bfloat16, device=dev) for s in wl.sites]
+    cu, ss = torch.from_numpy(wl.cu()).to(dev), torch.from_numpy(wl.row_slot.copy()).to(dev)
+    L.meta_build(cu.data_ptr(), ss.data_ptr(), wl.n_seqs, main.cuda_stream)
+    step = L.lora_step(L.max_lora_tiles(), main.cuda_stream)
+    hooks = [L.hook(si) for si in range(ns)]
+    torch.cuda.synchronize()
+
+    def separate(i):
+        for si in range(ns):
+            torch.matmul(xs[si], ws[si].t(), out=ys[si])
+            L.apply(hooks[si], step, xs[si].data_ptr(), T, ys[si].data_ptr(), ys[si].shape[1], False, main.cuda_stream)
+
+    def fused(i):
+        for si in range(ns):
+            L.shrink(hooks[si], step, xs[si].data_ptr(), T, main.cuda_stream)
+            L.linear_bf16_fused(hooks[si], step, xs[si].data_ptr(), ws[si].data_ptr(), T, ys[si].data_ptr(),
+                                ys[si].shape[1], False, main.cuda_stream)
+
+    def base_only(i):
+        for si in range(ns):
+            torch.matmul(xs[si], ws[si].t(), out=ys[si])
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    t_fused = _event_time(torch, main, fused, args.steps, args.warmup, barrier)
+    clocks = sampler.stop() if sampler is not None else None
+    t_sep = _event_time(torch, main, separate, args.steps, args.warmup, barrier)
+    t_base = _event_time(torch, main, base_only, args.steps, args.warmup, barrier)
+    L.device_status()
+    if world > 1:
+        t = torch.tensor([t_fused, t_sep, t_base], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        t_fused, t_sep, t_base = (float(v) for v in t)
+    if rank != 0:
+        return None
+    flops = sum(2.0 * T * s.cols * s.width() for s in wl.sites) + wl.work()["flops"]
+    _, _, pk = peaks()
+    tf_peak = pk.get("bf16_tflops_sustained") or 1400.0
+    us = 1e3 * t_fused / args.steps
+    return {"metric": METRIC, "value": world * T * args.steps / (t_fused * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_fused / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl.name + "+bf16-base-layers", "tokens_per_step": T, "adapters": wl.n_adapters,
+                       "step": "per layer: shrink, then base product + adapter term in one kernel (y written once)",
+                       "l2": "inputs larger than L2 (x, W, y of the four layers)"},
+            "gpu_launches": 4 * ns * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "plora_gemm_fused_kernel (bf16)", "achieved": flops / (us * 1e-6) / 1e12,
+                         "peak": tf_peak, "unit": "TFLOP/s", "frac": flops / (us * 1e-6) / 1e12 / tf_peak if tf_peak else None,
+                         "peak_kind": "measured, sustained bf16", "traffic": None},
+            "compare": {"library_gemm_then_shrink_expand_ms": t_sep / args.steps, "library_gemm_alone_ms": t_base / args.steps,
+                        "one_kernel_layers_ms": t_fused / args.steps},
+            "clocks": clocks}
+
+
 def run_tp(args, rank, world, local_rank):
     """Tensor-parallel 27B-shaped layer set (q, o, gate/up, down; hidden 5120, intermediate 17408), 512 tokens,
     32 rank-32 adapters: column-parallel q and gate/up, row-parallel o and down with an NCCL all-reduce of the
@@ -729,7 +807,7 @@ def main():
     ap.add_argument("--steps", type=int, default=0, help="default: 200 (decode), 10 (prefill)")
     ap.add_argument("--warmup", type=int, default=0, help="default: 20 (decode), 3 (prefill)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "plumbing", "fp8", "tp"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "plumbing", "fp8", "tp", "fused-bf16"])
     ap.add_argument("--tokens", type=int, default=0, help="fp8 workload only: run the layer at this prefill-sized M")
     ap.add_argument("--seqs", type=int, default=8, help="prefill workload only: sequences of 2048 tokens (8 = the "
                                                         "benchmark configuration; fewer for profiler captures)")
@@ -748,8 +826,8 @@ def main():
     args = ap.parse_args()
     global PREFILL_SEQS
     PREFILL_SEQS = args.seqs
-    args.steps = args.steps or (10 if args.workload == "prefill" else 200)
-    args.warmup = max(args.warmup or (3 if args.workload == "prefill" else 20), 3)
+    args.steps = args.steps or (10 if args.workload in ("prefill", "fused-bf16") else 200)
+    args.warmup = max(args.warmup or (3 if args.workload in ("prefill", "fused-bf16") else 20), 3)
     if args.workload == "fp8" and args.tokens:
         args.steps, args.warmup = min(args.steps, 10), 3
     rank = int(os.environ.get("RANK", "0"))
@@ -768,8 +846,8 @@ def main():
         os.environ.setdefault("MASTER_PORT", "29533")
         torch.distributed.init_process_group("nccl", rank=rank, world_size=world,
                                              device_id=torch.device(f"cuda:{local_rank}"))
-    if args.workload in ("fp8", "tp"):
-        out = (run_fp8 if args.workload == "fp8" else run_tp)(args, rank, world, local_rank)
+    if args.workload in ("fp8", "tp", "fused-bf16"):
+        out = {"fp8": run_fp8, "tp": run_tp, "fused-bf16": run_fused_bf16}[args.workload](args, rank, world, local_rank)
         if rank == 0:
             print(json.dumps(out))
         if torch.distributed.is_initialized():
