@@ -98,6 +98,16 @@ class ClockSampler:
 
 # ------------------------------------------------------------------------------------- ours
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels that dominate the two
+# block workloads, from the ncu captures summarised under profiles/ (decode_block_gather_kernels_bulk_async.md:
+# the gate/up expand of the decode block, captured at full size; prefill_block_tile_kernels_tma_pipelines.md: the
+# gate/up expand captured on 2 of the 8 sequences, traffic scaled by 4 since it grows with the token count).
+NCU_TRAFFIC = {
+    ("decode-4096x12288-64tok-16xr16", "expand[2]"): 15.02e6,
+    ("prefill-4096x12288-8x2048-r64", "expand[2]"): 4 * (214.6e6 + 148.2e6),
+}
+
+
 def kernel_bytes(wl, si, which, f32_out=False):
     """Algorithmic bytes of one launch of the shrink or the expand of site si (true ranks)."""
     site = wl.sites[si]
@@ -310,7 +320,7 @@ def run_ours(args, rank, world, local_rank):
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": (8 if decode else 16) * args.steps,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                     "peak_kind": peak_kind, "traffic": None, "us_per_launch": kern[dom]["us"],
+                     "peak_kind": peak_kind, "traffic": NCU_TRAFFIC.get((wl.name, dom)), "us_per_launch": kern[dom]["us"],
                      "algorithmic_bytes_per_launch": kern[dom]["bytes"]},
         "step_roofline": {"algorithmic_bytes_per_step": work["bytes"], "achieved_gbs": work["bytes"] / (step_us * 1e-6) / 1e9,
                           "frac": work["bytes"] / (step_us * 1e-6) / 1e9 / peak, "us_per_step": step_us},
