@@ -48,6 +48,7 @@ enum {
 typedef struct plora plora_t;                 /* src/lora.rs:416-442  Loras */
 typedef struct plora_adapter plora_adapter_t; /* src/lora.rs:82-88    Adapter */
 typedef struct plora_slots plora_slots_t;     /* src/sched.rs:410-420 LoraSlots */
+typedef struct plora_manager plora_manager_t; /* the adapter lifecycle of src/engine.rs:490-655 */
 
 /* src/lora.rs:33-41 SitePart. heads_start < 0 is Heads::None (src/lora.rs:23-31). */
 typedef struct {
@@ -161,6 +162,34 @@ int plora_upload(plora_t* h, int slot, uint32_t id, void* stream);
 int plora_hook_of(const plora_t* h, int site, plora_hook* out);
 /* the pinned mirror of one descriptor (src/lora.rs:596-615), for inspection */
 int plora_desc_of(const plora_t* h, int site, int slot, plora_desc* out);
+
+/* Prep::read (src/lora.rs:298-306): reads an adapter from a PEFT directory (adapter_config.json + *.safetensors,
+ * src/lora.rs:148-233) or a llama.cpp GGUF adapter file (src/lora.rs:237-281) and lays it out as its GPU slot will
+ * hold it. Same rejections as the engine (DoRA, modules_to_save, trained biases, alpha_pattern, vision modules;
+ * `.mtp.` modules skipped), scale = alpha / r (alpha / sqrt(r) with use_rslora; alpha defaults to 8) folded into B
+ * in f32. Callable from any thread; errors in plora_adapter_error(). */
+int plora_adapter_read(const plora_t* h, const char* name, const char* path, plora_adapter_t** out);
+
+/* ---- adapter lifecycle: Engine::{start_load, finish_loads, evict, unload_adapter, submit} (src/engine.rs:490-655).
+ * plora_manager_load starts a worker thread that reads the adapter (plora_adapter_read) and returns a ticket;
+ * plora_manager_finish_loads, called from the engine thread between steps, registers what the workers finished,
+ * answers the tickets (plora_manager_poll), drops the least recently used idle on-demand adapters beyond
+ * max_cpu_loras (0 = no limit), and frees unloaded adapters once no request uses them. `slots` may be NULL; when
+ * given, a freed adapter also leaves its GPU slot (Scheduler::forget_adapter, src/sched.rs:569-585). Requests
+ * are counted with plora_manager_submit / plora_manager_release. All calls except the worker's read belong to the
+ * thread that owns the handle. */
+plora_manager_t* plora_manager_new(plora_t* h, plora_slots_t* slots, int max_cpu_loras);
+void plora_manager_free(plora_manager_t* m); /* joins the worker threads */
+const char* plora_manager_error(const plora_manager_t* m);
+int plora_manager_load(plora_manager_t* m, const char* name, const char* path, int on_demand, uint64_t* ticket);
+int plora_manager_finish_loads(plora_manager_t* m); /* returns how many adapters it registered */
+int plora_manager_wait(plora_manager_t* m, int timeout_ms); /* 1 = a worker has finished something */
+int plora_manager_poll(plora_manager_t* m, uint64_t ticket, int* done, int* status, char* text, int text_cap);
+int plora_manager_loading(const plora_manager_t* m);
+int plora_manager_unload(plora_manager_t* m, const char* name);
+int plora_manager_submit(plora_manager_t* m, uint32_t adapter);
+void plora_manager_release(plora_manager_t* m, uint32_t adapter);
+int plora_manager_resident_on_demand(const plora_manager_t* m);
 
 /* ---- scheduler side: src/sched.rs ---- */
 

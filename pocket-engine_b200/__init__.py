@@ -96,6 +96,19 @@ SYMBOLS = {
     "plora_adapter_data": (C.POINTER(C.c_uint8), [_P]),
     "plora_adapter_error": (C.c_char_p, []),
     "plora_adapter_desc": (_I, [_P, _P, _I, _U64, C.POINTER(Desc)]),
+    "plora_adapter_read": (_I, [_P, C.c_char_p, C.c_char_p, C.POINTER(_P)]),
+    "plora_manager_new": (_P, [_P, _P, _I]),
+    "plora_manager_free": (None, [_P]),
+    "plora_manager_error": (C.c_char_p, [_P]),
+    "plora_manager_load": (_I, [_P, C.c_char_p, C.c_char_p, _I, C.POINTER(C.c_uint64)]),
+    "plora_manager_finish_loads": (_I, [_P]),
+    "plora_manager_wait": (_I, [_P, _I]),
+    "plora_manager_poll": (_I, [_P, C.c_uint64, C.POINTER(_I), C.POINTER(_I), C.c_char_p, _I]),
+    "plora_manager_loading": (_I, [_P]),
+    "plora_manager_unload": (_I, [_P, C.c_char_p]),
+    "plora_manager_submit": (_I, [_P, C.c_uint32]),
+    "plora_manager_release": (None, [_P, C.c_uint32]),
+    "plora_manager_resident_on_demand": (_I, [_P]),
     "plora_insert": (_I, [_P, _P, _U32P]),
     "plora_retire": (_I, [_P, C.c_char_p, _U32P]),
     "plora_free": (_I, [_P, C.c_uint32]),
@@ -290,6 +303,91 @@ class Prep:
         if rc != OK:
             raise PloraError(rc, lib.plora_adapter_error().decode())
         return Adapter(out.value, name)
+
+    def read(self, name, path):
+        """Prep::read (src/lora.rs:298-306): a PEFT directory or a llama.cpp GGUF adapter file."""
+        out = _P()
+        rc = lib.plora_adapter_read(self._loras._h, name.encode(), str(path).encode(), C.byref(out))
+        if rc != OK:
+            raise PloraError(rc, lib.plora_adapter_error().decode())
+        return Adapter(out.value, name)
+
+
+class AdapterManager:
+    """The adapter lifecycle of src/engine.rs:490-655 around a registry: loads on worker threads, tickets for
+    the answers, least-recently-used drop of on-demand adapters, unload that drains."""
+
+    def __init__(self, loras, slots=None, max_cpu_loras=0):
+        self._loras = loras
+        self._m = lib.plora_manager_new(loras._h, slots._s if slots is not None else None, max_cpu_loras)
+        if not self._m:
+            raise PloraError(ERR_ARG, "could not create the adapter manager")
+
+    def close(self):
+        if self._m:
+            lib.plora_manager_free(self._m)
+            self._m = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def load(self, name, path, on_demand=False):
+        """Engine::start_load: returns a ticket; poll() it after finish_loads()."""
+        t = C.c_uint64()
+        rc = lib.plora_manager_load(self._m, name.encode(), str(path).encode(), int(on_demand), C.byref(t))
+        if rc != OK:
+            raise PloraError(rc, "plora_manager_load")
+        return t.value
+
+    def finish_loads(self):
+        return lib.plora_manager_finish_loads(self._m)
+
+    def wait(self, timeout_ms=1000):
+        return lib.plora_manager_wait(self._m, timeout_ms)
+
+    def poll(self, ticket):
+        """(done, status, text) of a load."""
+        done, status = _I(), _I()
+        buf = C.create_string_buffer(512)
+        rc = lib.plora_manager_poll(self._m, ticket, C.byref(done), C.byref(status), buf, 512)
+        if rc != OK:
+            raise PloraError(rc, "unknown ticket")
+        return bool(done.value), status.value, buf.value.decode()
+
+    def settle(self, ticket, timeout_s=30.0):
+        """Runs finish_loads until the ticket is answered; returns (status, text)."""
+        import time
+        end = time.time() + timeout_s
+        while True:
+            self.finish_loads()
+            done, status, text = self.poll(ticket)
+            if done:
+                return status, text
+            if time.time() > end:
+                raise TimeoutError("adapter load did not finish")
+            self.wait(100)
+
+    def loading(self):
+        return bool(lib.plora_manager_loading(self._m))
+
+    def unload(self, name):
+        rc = lib.plora_manager_unload(self._m, name.encode())
+        if rc != OK:
+            raise PloraError(rc, lib.plora_manager_error(self._m).decode())
+
+    def submit(self, adapter_id):
+        rc = lib.plora_manager_submit(self._m, adapter_id)
+        if rc != OK:
+            raise PloraError(rc, lib.plora_manager_error(self._m).decode())
+
+    def release(self, adapter_id):
+        lib.plora_manager_release(self._m, adapter_id)
+
+    def resident_on_demand(self):
+        return lib.plora_manager_resident_on_demand(self._m)
 
 
 class Loras:

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libplora.so")
-SOURCES = ["plora_host.cpp", "plora_kernels.cu", "plora_mma.cu", "plora_fp8.cu", "plora_site.cu", "plora_static.cu", "plora_xchg.cu", "plora_gemm.cu"]
+SOURCES = ["plora_host.cpp", "plora_read.cpp", "plora_manager.cpp", "plora_kernels.cu", "plora_mma.cu", "plora_fp8.cu", "plora_site.cu", "plora_static.cu", "plora_xchg.cu", "plora_gemm.cu"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-Wall,-Wextra", "-shared", "-cudart", "static",

@@ -90,6 +90,9 @@ cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 static_assert(sizeof(plora_desc) == 112, "Desc is 112 bytes (src/lora.rs:59-70)");
 
+// for the readers in plora_read.cpp: the text plora_adapter_error returns on this thread
+void plora_set_adapter_error(const std::string& text) { g_adapter_err = text; }
+
 extern "C" {
 
 // ------------------------------------------------------------------ registry
