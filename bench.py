@@ -258,31 +258,40 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
 
-    # ---- per-kernel durations (CUDA events on the launching stream, rotating copies)
+    # ---- per-kernel durations: for every (layer, shrink | expand) one graph holding that launch once per
+    # rotating copy (so each launch finds its slabs, x and y in HBM), CUDA events around replays on the launching
+    # stream, divided by the number of launches. Single eager launches between two events would add several
+    # microseconds of launch and event overhead to kernels that last about as long.
     kern = {}
-    reps = max(copies, min(args.steps, 4 * copies))
+    reps = 5 if decode else 2
     with torch.cuda.stream(main):
         m = main.cuda_stream
         for si in range(ns):
             for which in ("shrink", "expand"):
-                evs = []
-                for i in range(reps + 3):
-                    S = sets[i % copies]
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    hook = S["lins"][si].lora
-                    a.record(main)
-                    if which == "shrink":
-                        S["L"].shrink(hook, S["step"], S["x"][si].data_ptr(), wl.tokens, m)
-                    else:
-                        S["L"].expand(hook, S["step"], wl.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1], False, m)
-                    b.record(main)
-                    evs.append((a, b))
-                torch.cuda.synchronize()
-                ts = [a.elapsed_time(b) for a, b in evs[3:]]
-                kern[f"{which}[{si}]"] = {"us": 1e3 * float(np.mean(ts)), "bytes": kernel_bytes(wl, si, which)}
+                def launches():
+                    for S in sets:
+                        hook = S["lins"][si].lora
+                        if which == "shrink":
+                            S["L"].shrink(hook, S["step"], S["x"][si].data_ptr(), wl.tokens, m)
+                        else:
+                            S["L"].expand(hook, S["step"], wl.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1], False, m)
+                launches()
+                main.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=main):
+                    launches()
+                g.replay()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(main)
+                for _ in range(reps):
+                    g.replay()
+                b.record(main)
+                main.synchronize()
+                kern[f"{which}[{si}]"] = {"us": 1e3 * a.elapsed_time(b) / (reps * copies), "bytes": kernel_bytes(wl, si, which)}
+                del g
         # the step's metadata kernels, for the record
         evs = []
-        for i in range(reps):
+        for i in range(max(copies, 8)):
             S = sets[i % copies]
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(main)
