@@ -168,7 +168,15 @@ __global__ void __launch_bounds__(128) plora_s_reduce_kernel(float* __restrict__
         const int t = i / rank, j = i - t * rank;
         float* sp = S + (size_t)work[4 + t] * lds + j;
         float acc = sp[0];
-        for (int s = 1; s < nsplit; s++) acc += __ldcg(sp + (size_t)s * s_stride);
+        int s = 1;
+        for (; s + 4 <= nsplit; s += 4) {  // in split order, four loads in flight
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = __ldcg(sp + (size_t)(s + u) * s_stride);
+#pragma unroll
+            for (int u = 0; u < 4; u++) acc += v[u];
+        }
+        for (; s < nsplit; s++) acc += __ldcg(sp + (size_t)s * s_stride);
         sp[0] = acc;
     }
 }

@@ -218,6 +218,7 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
             // runs of 64 or more contiguous tokens of one slot take the tensor-core tile kernels
             if (h->mma_ok) h->seg.run_min = PLORA_RUN_MIN_DEFAULT;
             if (const char* e = getenv("PLORA_PDL")) h->pdl = e[0] != '0';
+            if (const char* e = getenv("PLORA_FUSED_TILE_ROWS")) h->fused_tile_rows = std::max(1, atoi(e));
             if (rc == PLORA_OK) {
                 memset(h->host_tables, 0, h->table_bytes);
                 check("zero tables", cudaMemset(h->tables, 0, h->table_bytes));  // src/lora.rs:494
@@ -837,6 +838,15 @@ static int gemm_layer(plora_t* h, const plora_hook* hook, const plora_step* step
                       uint64_t w, uint64_t sn, int rows, int width, uint64_t y, int ldy, int f32_out, int work_cap,
                       void* stream) {
     const SiteInfo& site = h->sites[(size_t)hook->site];
+    const bool pdl = h->pdl && h->pdl_armed;
+    h->pdl_armed = true;
+    // the kernel reads the long runs' S from plane 0: fold the tile path's planes (the gather tokens' K-split
+    // planes are added by the gather expand itself)
+    CU(h, "S reduce (tiles)",
+       plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, 1,
+                             (const int32_t*)(uintptr_t)step->segs, h->seg, (const plora_desc*)(uintptr_t)hook->table, 0,
+                             h->mma_ok && rows >= step->run_min ? std::max(1, rows / 64) : 0, tile_split(h, rows),
+                             site.cols, pdl, as_stream(stream)));
     CU(h, "fused layer (tensor-core adapter term)",
        plora_launch_gemm_fused(kind, (const void*)(uintptr_t)x, (const float*)(uintptr_t)st, (const void*)(uintptr_t)w,
                                (const float*)(uintptr_t)sn, rows, width, site.cols, (const int32_t*)(uintptr_t)step->segs,
@@ -845,7 +855,7 @@ static int gemm_layer(plora_t* h, const plora_hook* hook, const plora_step* step
                                h->status, h->pdl, as_stream(stream)));
     if (work_cap > 0)
         CU(h, "expand (tokens outside long runs)",
-           plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, 1,
+           plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
                                (const int32_t*)(uintptr_t)step->segs, h->seg, (const plora_desc*)(uintptr_t)hook->table,
                                (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap, h->status, h->pdl,
                                false, as_stream(stream)));
@@ -869,13 +879,6 @@ int plora_linear_bf16_fused(plora_t* h, const plora_hook* hook, const plora_step
         return fail(h, PLORA_ERR_ARG,
                     "x, w and y must be 16-byte aligned with 16-byte multiple pitches, and parts must start at multiples of 256 columns");
     int work_cap = std::min(std::min(step->max_tiles, rows), h->max_slots + rows / PLORA_WORK_TOKENS);
-    const bool pdl = h->pdl && h->pdl_armed;
-    h->pdl_armed = true;
-    CU(h, "S reduce", plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
-                                            (const int32_t*)(uintptr_t)step->segs, h->seg,
-                                            (const plora_desc*)(uintptr_t)hook->table, work_cap,
-                                            h->mma_ok && rows >= step->run_min ? std::max(1, rows / 64) : 0,
-                                            tile_split(h, rows), site.cols, pdl, as_stream(stream)));
     return gemm_layer(h, hook, step, 1, x, 0, w, 0, rows, width, y, ldy, f32_out, work_cap, stream);
 }
 
@@ -904,6 +907,12 @@ int plora_linear_fp8_fused(plora_t* h, const plora_hook* hook, const plora_step*
         width = std::max(width, off[p] + prow[p]);
     }
     int work_cap = std::min(std::min(step->max_tiles, rows), h->max_slots + rows / PLORA_WORK_TOKENS);
+    // base product and the long runs' adapter term on the tensor cores in one kernel, then the gather kernel for
+    // the tokens outside long runs
+    if (h->gemm_ok && rows >= h->fused_tile_rows &&
+        plora_gemm_fits(0, (const void*)(uintptr_t)xq, (const void*)(uintptr_t)wq, (const void*)(uintptr_t)y, ldy, f32_out,
+                        site.cols, (int)site.parts.size(), off))
+        return gemm_layer(h, hook, step, 0, xq, st, wq, sn, rows, width, y, ldy, f32_out, work_cap, stream);
     const bool pdl = h->pdl && h->pdl_armed;
     h->pdl_armed = true;
     CU(h, "S reduce", plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
@@ -911,12 +920,6 @@ int plora_linear_fp8_fused(plora_t* h, const plora_hook* hook, const plora_step*
                                             (const plora_desc*)(uintptr_t)hook->table, work_cap,
                                             h->mma_ok && rows >= step->run_min ? std::max(1, rows / 64) : 0,
                                             tile_split(h, rows), site.cols, pdl, as_stream(stream)));
-    // prefill-sized steps: base product and the long runs' adapter term on the tensor cores in one kernel, then
-    // the gather kernel for the tokens outside long runs
-    if (h->gemm_ok && rows >= h->fused_tile_rows && rows >= step->run_min &&
-        plora_gemm_fits(0, (const void*)(uintptr_t)xq, (const void*)(uintptr_t)wq, (const void*)(uintptr_t)y, ldy, f32_out,
-                        site.cols, (int)site.parts.size(), off))
-        return gemm_layer(h, hook, step, 0, xq, st, wq, sn, rows, width, y, ldy, f32_out, work_cap, stream);
     CU(h, "fused fp8 layer",
        plora_launch_fp8_fused((const void*)(uintptr_t)xq, (const float*)(uintptr_t)st, (const void*)(uintptr_t)wq,
                               (const float*)(uintptr_t)sn, rows, width, site.cols, (const int32_t*)(uintptr_t)step->segs,

@@ -123,7 +123,7 @@ struct plora {
     bool site_ok = false;   // the cluster kernel's attributes were set
     bool fp8_ok = false;    // the fused FP8 layer can run
     bool gemm_ok = false;   // the one-kernel layer for prefill-sized steps can run
-    int fused_tile_rows = 1024;  // steps with at least this many rows take it (plora_set_fused_tile_rows)
+    int fused_tile_rows = 1;  // steps with at least this many rows take it (plora_set_fused_tile_rows)
     bool mma_ok = false;    // the tensor-core tile kernels can run (max_rank <= 128 and the driver entry point exists)
     bool pdl_armed = false;  // false right after the step's grouping kernel: the next launch is a plain one
 };

@@ -86,8 +86,9 @@ def test_fused_fp8_layer_matches_the_oracle(pe, oracle, case, tile_form):
     rms = float(np.sqrt(np.mean(y64 ** 2)))
 
     loras = harness.product_registry(pe, wl)
-    if tile_form:
-        loras.set_fused_tile_rows(1)  # the prefill-sized form (tensor-core adapter term) whatever the step's size
+    # the tensor-core form (base product + long runs in one kernel, gather kernel for the rest), or the
+    # decode-shaped kernel that builds every token's adapter term inside its tiles
+    loras.set_fused_tile_rows(1 if tile_form else 1 << 30)
     stream = torch.cuda.current_stream().cuda_stream
     x = harness.to_dev_bf16(xb, 0)
     xq_d = torch.zeros(wl.tokens, K, dtype=torch.uint8, device="cuda")
