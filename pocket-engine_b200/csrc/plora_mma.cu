@@ -9,7 +9,6 @@
 //
 // Every wait is bounded (mbar_wait); on a timeout the block records PLORA_ERR_TIMEOUT, frees its tensor
 // memory and leaves. Replaces the reference's mma.sync tiles of 16 tokens (src/kernels/lora.cuh:23-126).
-#include <cstdlib>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -926,7 +925,6 @@ cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int l
     for (int p = 0; p < parts; p++) aligned = aligned && ((size_t)part_off[p] * elt) % 16 == 0;
     // ring slots per warp: what two blocks per SM leave room for, else what one block per SM does
     int nst = (111 * 1024 - 1024 - 4 * op_bytes) / (8 * EXP_SLOT_BYTES);
-    if (getenv("PLORA_EXP_ONE")) nst = 0;
     if (nst < 1) nst = (216 * 1024 - 1024 - 4 * op_bytes) / (8 * EXP_SLOT_BYTES);
     nst = nst > 4 ? 4 : nst;
     if (aligned && nst >= 1) {
