@@ -43,17 +43,16 @@ __device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(
 // rows add the tile path's planes as a balanced tree (the same sums plora_expand would form)
 __device__ __forceinline__ float4 local_sum(const float* sp, size_t s_stride, int nplanes, bool tree) {
     if (!tree) {
-        // in plane order, four loads in flight at a time
-        float4 acc = __ldcg(reinterpret_cast<const float4*>(sp));
-        int s = 1;
-        for (; s + 4 <= nplanes; s += 4) {
-            float4 v[4];
+        // all planes requested together (a layer has at most 16), then added in plane order
+        float4 v[16];
 #pragma unroll
-            for (int u = 0; u < 4; u++) v[u] = __ldcg(reinterpret_cast<const float4*>(sp + (size_t)(s + u) * s_stride));
+        for (int s = 0; s < 16; s++)
+            if (s < nplanes) v[s] = __ldcg(reinterpret_cast<const float4*>(sp + (size_t)s * s_stride));
+        float4 acc = v[0];
 #pragma unroll
-            for (int u = 0; u < 4; u++) acc = add4(acc, v[u]);
-        }
-        for (; s < nplanes; s++) acc = add4(acc, __ldcg(reinterpret_cast<const float4*>(sp + (size_t)s * s_stride)));
+        for (int s = 1; s < 16; s++)
+            if (s < nplanes) acc = add4(acc, v[s]);
+        for (int s = 16; s < nplanes; s++) acc = add4(acc, __ldcg(reinterpret_cast<const float4*>(sp + (size_t)s * s_stride)));
         return acc;
     }
     float4 v[PLORA_TILE_SPLIT_MAX];
