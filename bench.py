@@ -154,24 +154,32 @@ def run_ours(args, rank, world, local_rank):
     side_h = side.cuda_stream if args.streams == 2 else None
     facs = [wl.factors(i) for i in range(wl.n_adapters)]
     sets = []
-    xs_host = [torch.from_numpy(wl.x_bits(si).view(np.int16)).pin_memory() for si in range(ns)]
-    yb_host = [torch.from_numpy(pe.bf16_bits(wl.y_base(si)).reshape(wl.tokens, -1).view(np.int16)).pin_memory()
-               for si in range(ns)]
-    cu_host = torch.from_numpy(wl.cu()).pin_memory()
-    ss_host = torch.from_numpy(wl.row_slot.copy()).pin_memory()
+    # One pinned host buffer holds the step's activations, x of every layer and then y_base of every layer, and one
+    # device buffer per copy mirrors it (x[si], y[si] are views), so a step's inputs travel in one copy and its
+    # results (the y region) in one. The step's sequence table (cu, then the slot of every sequence) likewise.
+    x_np = [wl.x_bits(si).view(np.int16).reshape(-1) for si in range(ns)]
+    y_np = [pe.bf16_bits(wl.y_base(si)).view(np.int16).reshape(-1) for si in range(ns)]
+    in_host = torch.from_numpy(np.concatenate(x_np + y_np)).pin_memory()
+    x_off = np.concatenate([[0], np.cumsum([a.size for a in x_np])])
+    y_off = x_off[-1] + np.concatenate([[0], np.cumsum([a.size for a in y_np])])
+    assert all(int(o) % 8 == 0 for o in list(x_off) + list(y_off))  # 16-byte aligned views
+    meta_host = torch.from_numpy(np.concatenate([wl.cu(), wl.row_slot]).astype(np.int32)).pin_memory()
+    n_cu = len(wl.cu())
     for c in range(copies):
         L = pe.Loras(wl.sites, wl.n_adapters, wl.max_rank, wl.tokens, wl.n_seqs, device=local_rank)
         prep = L.prep()
         for i in range(wl.n_adapters):
             L.upload(i + 1, L.insert(prep.prepare(f"a{i}", facs[i])), main.cuda_stream)
-        x = [h.to(dev, non_blocking=True).view(torch.bfloat16) for h in xs_host]
-        y = [h.to(dev, non_blocking=True).view(torch.bfloat16) for h in yb_host]
-        cu = cu_host.to(dev)
-        ss = ss_host.to(dev)
+        pack = in_host.to(dev, non_blocking=True)
+        x = [pack[int(x_off[si]):int(x_off[si + 1])].view(torch.bfloat16).view(wl.tokens, -1) for si in range(ns)]
+        y = [pack[int(y_off[si]):int(y_off[si + 1])].view(torch.bfloat16).view(wl.tokens, -1) for si in range(ns)]
+        meta_dev = meta_host.to(dev)
+        cu, ss = meta_dev[:n_cu], meta_dev[n_cu:]
         L.meta_build(cu.data_ptr(), ss.data_ptr(), wl.n_seqs, main.cuda_stream)
         step = L.lora_step(L.max_lora_tiles(), main.cuda_stream, decode=decode)
         lins = [pe.Linear(L, si) for si in range(ns)]
-        sets.append({"L": L, "x": x, "y": y, "cu": cu, "ss": ss, "step": step, "lins": lins})
+        sets.append({"L": L, "x": x, "y": y, "cu": cu, "ss": ss, "step": step, "lins": lins, "pack": pack,
+                     "meta": meta_dev, "yreg": pack[int(y_off[0]):]})
     torch.cuda.synchronize()
 
     fused = args.path != "pair"
@@ -226,35 +234,42 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- end to end through the C ABI with host buffers: H2D of x, y_base and the step's sequence table,
     # device metadata build + grouping, the block, D2H of y
-    y_out = [torch.empty_like(h) for h in yb_host]
-    y_out = [t.pin_memory() for t in y_out]
-    h2d = sum(h.numel() * 2 for h in xs_host) + sum(h.numel() * 2 for h in yb_host) + cu_host.numel() * 4 + \
-        ss_host.numel() * 4
-    d2h = sum(h.numel() * 2 for h in y_out)
+    # Two steps are in flight at a time (two streams, two result buffers; consecutive steps use different copies),
+    # so the copy of one step's inputs overlaps the other's kernels and result copy; the host waits for step i - 1
+    # after issuing step i. With a single copy (prefill) the steps run one after the other.
+    depth = 2 if copies >= 2 else 1
+    lanes = [main, torch.cuda.Stream(device=dev)][:depth]
+    y_out = [torch.empty(sets[0]["yreg"].numel(), dtype=torch.int16).pin_memory() for _ in range(depth)]
+    h2d = in_host.numel() * 2 + meta_host.numel() * 4
+    d2h = y_out[0].numel() * 2
 
-    def e2e_step(S):
-        m = main.cuda_stream
-        with torch.cuda.stream(main):
-            for si in range(ns):
-                S["x"][si].view(torch.int16).copy_(xs_host[si], non_blocking=True)
-                S["y"][si].view(torch.int16).copy_(yb_host[si], non_blocking=True)
-            S["cu"].copy_(cu_host, non_blocking=True)
-            S["ss"].copy_(ss_host, non_blocking=True)
+    def e2e_issue(S, lane):
+        stream = lanes[lane]
+        m = stream.cuda_stream
+        with torch.cuda.stream(stream):
+            S["pack"].copy_(in_host, non_blocking=True)
+            S["meta"].copy_(meta_host, non_blocking=True)
             S["L"].meta_build(S["cu"].data_ptr(), S["ss"].data_ptr(), wl.n_seqs, m)
             st = S["L"].lora_step(S["L"].max_lora_tiles(), m, decode=decode)
             for si in range(ns):
                 S["lins"][si].forward(S["x"][si].data_ptr(), wl.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1],
-                                      False, lora=st, main=m, side=side_h, fused=fused)
-            for si in range(ns):
-                y_out[si].copy_(S["y"][si].view(torch.int16), non_blocking=True)
-        main.synchronize()
+                                      False, lora=st, main=m, side=side_h if depth == 1 else None, fused=fused)
+            y_out[lane].copy_(S["yreg"], non_blocking=True)
 
-    for i in range(args.warmup):
-        e2e_step(sets[i % copies])
+    def e2e_run(first, count):
+        for i in range(count):
+            e2e_issue(sets[(first + i) % copies], i % depth)
+            if depth == 2 and i >= 1:
+                lanes[(i - 1) % depth].synchronize()
+            elif depth == 1:
+                lanes[0].synchronize()
+        for s in lanes:
+            s.synchronize()
+
+    e2e_run(0, args.warmup)
     barrier()
     t0 = time.perf_counter()
-    for i in range(args.steps):
-        e2e_step(sets[(args.warmup + i) % copies])
+    e2e_run(args.warmup, args.steps)
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
 
@@ -326,7 +341,7 @@ def run_ours(args, rank, world, local_rank):
                    "partitioning": "adapter-affine, one batch per GPU, no collective",
                    "graph": f"one CUDA graph per copy, {args.streams} stream(s)", "path": args.path},
         "e2e": {"value": world * wl.tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps, "steps_in_flight": depth},
         "gpu_launches": (8 if decode else 16) * args.steps,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                      "peak_kind": peak_kind, "traffic": NCU_TRAFFIC.get((wl.name, dom)), "us_per_launch": kern[dom]["us"],
