@@ -255,7 +255,7 @@ int plora_linear_bf16_fused(plora_t* h, const plora_hook* hook, const plora_step
  * layer's shapes meet the conditions above; smaller steps, and layers that do not meet them, take the
  * decode-shaped kernel, which builds the adapter term of all tokens on the CUDA cores inside 128 x 64 tiles and
  * writes y once. Default 1: on B200 the tensor-core form followed by the gather kernel is faster at every size
- * measured (256 mixed decode tokens over 4096 -> 12288: 83 us against 204 us). */
+ * measured (256 mixed decode tokens over 4096 -> 12288: 65 us against 204 us). */
 int plora_set_fused_tile_rows(plora_t* h, int rows);
 
 /* Shrink and expand of one layer in one call, for callers whose x and y are both ready (that is, after the

@@ -487,7 +487,12 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
     TRACE_K(2, 2);
     const int rows = d.rows[p], c0 = blockIdx.x * nc;
     if (c0 >= rows) continue;
-    const int ncols = min(nc, rows - c0);
+    const int ncols_all = min(nc, rows - c0);
+    // The tile buffer holds bs_bytes of B: all the block's columns for ranks up to bs_bytes / (2 nc), fewer
+    // columns per pass (a multiple of 32) for higher ranks, so that a high maximum rank does not cost every
+    // block, whatever its slot's rank, the shared memory that limits how many blocks share an SM.
+    const int sub = min(nc, max(32, (bs_bytes / (2 * r)) & ~31));
+    int ncols = min(sub, ncols_all);
     unsigned char* Bs = dsm;
     float* ss = reinterpret_cast<float*>(dsm + bs_bytes);
     if (threadIdx.x == 0) {
@@ -498,8 +503,8 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
     if (threadIdx.x < PLORA_WORK_TOKENS) stok[threadIdx.x] = mytok;
     const int r_off = d.r_off[p];
     const int c = 2 * threadIdx.x;
-    const bool mine = c < ncols;
-    const size_t ycol = (size_t)d.off[p] + c0 + c;
+    bool mine = c < ncols;
+    size_t ycol = (size_t)d.off[p] + c0 + c;
     TRACE_K(2, 3);
     __syncthreads();
     if (!early && !waited) {
@@ -542,6 +547,29 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
     }
     __syncthreads();
     TRACE_K(2, 5);
+    for (int cs = 0; cs < ncols_all; cs += sub) {
+    if (cs > 0) {
+        // the next columns of the block: the tile buffer is free once every thread is through the pass before
+        __syncthreads();
+        ncols = min(sub, ncols_all - cs);
+        if (threadIdx.x == 0) {
+            const uint32_t bytes = (uint32_t)ncols * (uint32_t)r * 2u;
+            mbar_expect_tx(&bar, bytes);
+            bulk_g2s(Bs, reinterpret_cast<const bf16*>(d.b[p]) + (size_t)(c0 + cs) * r, bytes, &bar);
+        }
+        mine = c < ncols;
+        ycol = (size_t)d.off[p] + c0 + cs + c;
+        if (mine) {
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                if (t < cnt) {
+                    const size_t at = (size_t)stok[t] * ldy + ycol;
+                    if (f32_out) yv[t] = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(Y) + at);
+                    else yv[t] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(Y) + at));
+                }
+            }
+        }
+    }
     if (!mbar_wait(&bar, phase, status)) return;
     phase ^= 1;
     TRACE_K(2, 6);
@@ -597,6 +625,7 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
                         __floats2bfloat162_rn(yv[t].x + acc[t][0], yv[t].y + acc[t][1]);
             }
         }
+    }
     }
     }
     TRACE_K(2, 7);
@@ -689,7 +718,9 @@ cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, 
                                 int max_rows, int work_cap, int* status, bool pdl, bool early, cudaStream_t st) {
     const int max_rank = lds / PLORA_MAX_PARTS;
     const int nc = plora_expand_nc(max_rank, max_rows);
-    const int bs_bytes = nc * max_rank * 2;
+    // tile buffer: all of a block's columns at the maximum rank, up to 32 KB; blocks of higher-rank slots take
+    // their columns in passes
+    const int bs_bytes = nc * max_rank * 2 < 32 * 1024 ? nc * max_rank * 2 : 32 * 1024;
     dim3 grid((unsigned)((max_rows + nc - 1) / nc), (unsigned)parts,
               (unsigned)(work_cap < PLORA_GRID_Z_CAP ? work_cap : PLORA_GRID_Z_CAP));
     const size_t smem = (size_t)bs_bytes + (size_t)PLORA_WORK_TOKENS * (size_t)(max_rank / 8) * EXP_SPAD * sizeof(float);
