@@ -165,7 +165,7 @@ def run_ours(args, rank, world, local_rank):
     assert all(int(o) % 8 == 0 for o in list(x_off) + list(y_off))  # 16-byte aligned views
     meta_host = torch.from_numpy(np.concatenate([wl.cu(), wl.row_slot]).astype(np.int32)).pin_memory()
     n_cu = len(wl.cu())
-    for c in range(copies):
+    def make_set():
         L = pe.Loras(wl.sites, wl.n_adapters, wl.max_rank, wl.tokens, wl.n_seqs, device=local_rank)
         prep = L.prep()
         for i in range(wl.n_adapters):
@@ -178,13 +178,15 @@ def run_ours(args, rank, world, local_rank):
         L.meta_build(cu.data_ptr(), ss.data_ptr(), wl.n_seqs, main.cuda_stream)
         step = L.lora_step(L.max_lora_tiles(), main.cuda_stream, decode=decode)
         lins = [pe.Linear(L, si) for si in range(ns)]
-        sets.append({"L": L, "x": x, "y": y, "cu": cu, "ss": ss, "step": step, "lins": lins, "pack": pack,
-                     "meta": meta_dev, "yreg": pack[int(y_off[0]):]})
+        L.set_apply_mode(1 if args.path == "cluster" else 0)
+        return {"L": L, "x": x, "y": y, "cu": cu, "ss": ss, "step": step, "lins": lins, "pack": pack,
+                "meta": meta_dev, "yreg": pack[int(y_off[0]):]}
+
+    for c in range(copies):
+        sets.append(make_set())
     torch.cuda.synchronize()
 
     fused = args.path != "pair"
-    for S in sets:
-        S["L"].set_apply_mode(1 if args.path == "cluster" else 0)
 
     def block(S, m, s):
         for si in range(ns):
@@ -236,9 +238,11 @@ def run_ours(args, rank, world, local_rank):
     # device metadata build + grouping, the block, D2H of y
     # Two steps are in flight at a time (two streams, two result buffers; consecutive steps use different copies),
     # so the copy of one step's inputs overlaps the other's kernels and result copy; the host waits for step i - 1
-    # after issuing step i. With a single copy (prefill) the steps run one after the other.
-    depth = 2 if copies >= 2 else 1
-    lanes = [main, torch.cuda.Stream(device=dev)][:depth]
+    # after issuing step i.
+    e2e_sets = sets if copies >= 2 else sets + [make_set()]  # two steps in flight need two sets of buffers
+    torch.cuda.synchronize()
+    depth = 2
+    lanes = [main, torch.cuda.Stream(device=dev)]
     y_out = [torch.empty(sets[0]["yreg"].numel(), dtype=torch.int16).pin_memory() for _ in range(depth)]
     h2d = in_host.numel() * 2 + meta_host.numel() * 4
     d2h = y_out[0].numel() * 2
@@ -258,7 +262,7 @@ def run_ours(args, rank, world, local_rank):
 
     def e2e_run(first, count):
         for i in range(count):
-            e2e_issue(sets[(first + i) % copies], i % depth)
+            e2e_issue(e2e_sets[(first + i) % len(e2e_sets)], i % depth)
             if depth == 2 and i >= 1:
                 lanes[(i - 1) % depth].synchronize()
             elif depth == 1:
@@ -316,7 +320,7 @@ def run_ours(args, rank, world, local_rank):
             evs.append((a, b))
         torch.cuda.synchronize()
         meta_us = 1e3 * float(np.mean([a.elapsed_time(b) for a, b in evs]))
-    for S in sets:
+    for S in e2e_sets:
         S["L"].device_status()
 
     # max over ranks

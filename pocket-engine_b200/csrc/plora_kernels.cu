@@ -720,7 +720,7 @@ cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, 
     const int nc = plora_expand_nc(max_rank, max_rows);
     // tile buffer: all of a block's columns at the maximum rank, up to 32 KB; blocks of higher-rank slots take
     // their columns in passes
-    const int bs_bytes = nc * max_rank * 2 < 16 * 1024 ? nc * max_rank * 2 : 16 * 1024;
+    const int bs_bytes = nc * max_rank * 2 < 32 * 1024 ? nc * max_rank * 2 : 32 * 1024;
     dim3 grid((unsigned)((max_rows + nc - 1) / nc), (unsigned)parts,
               (unsigned)(work_cap < PLORA_GRID_Z_CAP ? work_cap : PLORA_GRID_Z_CAP));
     const size_t smem = (size_t)bs_bytes + (size_t)PLORA_WORK_TOKENS * (size_t)(max_rank / 8) * EXP_SPAD * sizeof(float);
