@@ -336,3 +336,24 @@ def test_capacity_errors_are_reported_not_faulted(pe):
         loras.device_status()
     assert e.value.code == pe.ERR_ARG
     loras.close()
+
+
+def test_random_steps_match_the_oracle(pe, wls):
+    """Seeded random steps: run lengths on both sides of the tile threshold and of the 128-token tile size, base-only
+    sequences, ranks from 8 to 64, one to three parts, input widths that are and are not multiples of
+    64, output widths that do and do not meet the alignment of tensor copies; both output types, both paths."""
+    rng = np.random.default_rng(2024)
+    for trial in range(8):
+        K = int(rng.choice([256, 520, 1024, 2048 + 64, 4096]))
+        nparts = int(rng.integers(1, 4))
+        widths = [int(rng.choice([64, 130, 256, 384, 1000, 1024])) for _ in range(nparts)]
+        sites = [pe.Site.fused(0, K, [(f"m{p}", w) for p, w in enumerate(widths)])]
+        n_ad = int(rng.integers(2, 6))
+        ranks = [int(rng.choice([8, 16, 32, 48, 64])) for _ in range(n_ad)]
+        n_seq = int(rng.integers(3, 14))
+        rows = [int(rng.choice([1, 1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 200, 300])) for _ in range(n_seq)]
+        slots = [int(rng.integers(0, n_ad + 1)) for _ in range(n_seq)]
+        wl = wls.Workload(f"random-{trial}", sites, ranks, 1.0, rows, slots, 100 + trial, max_rank=64)
+        for f32_out in (True, False):
+            harness.run_and_check(pe, wl, f32_out=f32_out, meta="device", run_min=64)
+            harness.run_and_check(pe, wl, f32_out=f32_out, meta="device", run_min=64, fused="early")
