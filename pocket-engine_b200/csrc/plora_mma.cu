@@ -145,6 +145,10 @@ __device__ __forceinline__ bool mbar_wait_long(uint64_t* bar, uint32_t parity, i
     return false;
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 #define MMA_M 128
 #define EXP_TPAD 66  // floats per row of the epilogue's transpose tile (64 columns + 2 of padding)
 
@@ -522,9 +526,11 @@ __global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __re
 
 // ------------------------------------------------------------------------------------------------------
 // The same expand with y moved by tensor copies, for outputs whose base, row pitch and part offsets are
-// 16-byte aligned (every model width in practice; the kernel above stays for the rest). 256 threads. Each warp
-// owns the 32 token rows tensor memory gives it (two warps per 32 rows, taking alternate slots of columns) and
-// a private ring of 4 KB slots; a slot holds 32 rows x 128 bytes of y
+// 16-byte aligned (every model width in practice; the kernel above stays for the rest). 288 threads: warp 8
+// copies the blocks' rows of B and issues the MMAs, up to two column blocks ahead (mbarriers tell it when S is
+// staged and when an accumulator has been read); the other eight never meet at a block-wide barrier inside the
+// loop. Each of them owns the 32 token rows tensor memory gives it (two warps per 32 rows, taking alternate
+// slots of columns) and a private ring of 4 KB slots; a slot holds 32 rows x 128 bytes of y
 // (64 bf16 or 32 f32 columns, 128-byte swizzle). Lane 0 keeps the ring full of loads; a landed slot gets the
 // accumulator columns added in shared memory (thread = row: with the swizzle, eight rows cover all banks) and
 // goes back with a tensor store, whose completion frees the slot for the next load. So the read-modify-write
@@ -550,14 +556,14 @@ __device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 template <bool F32>
-__global__ void __launch_bounds__(256) plora_expand_tma_kernel(const float* __restrict__ S, size_t s_stride, int lds, int K,
+__global__ void __launch_bounds__(288) plora_expand_tma_kernel(const float* __restrict__ S, size_t s_stride, int lds, int K,
                                                                 int ksplit, const int* __restrict__ segs, SegLayout lay,
                                                                 const plora_desc* __restrict__ table,
                                                                 const __grid_constant__ ExpandYMaps ymaps, void* Y, int ldy,
                                                                 int nb_per_cta, int op_bytes, int nst,
                                                                 int* __restrict__ status) {
     extern __shared__ unsigned char dsm_raw[];
-    __shared__ __align__(8) uint64_t done[2], ybar[8][EXP_RING_MAX];
+    __shared__ __align__(8) uint64_t done[2], acc_free[2], a_full, ybar[8][EXP_RING_MAX];
     __shared__ uint32_t tmem_slot;
     constexpr int CW = F32 ? 32 : 64;  // y columns per slot
     constexpr int CH = 128 / CW;       // slots per block of 128 columns
@@ -590,30 +596,77 @@ __global__ void __launch_bounds__(256) plora_expand_tma_kernel(const float* __re
     const int P = r >> 3;
     const CUtensorMap* ymap = &ymaps.m[p];
 
+    // warp 8 alone copies the blocks' rows of B (four rows of the block per lane) and issues the MMAs
     auto load_b = [&](int cb, unsigned char* dst) {
-        const int n = tid & 127;  // row of B = output column of the block; the two halves of the block share its chunks
-        const bool valid = cb * 128 + n < rows;
-        const bf16* src = B + (size_t)(valid ? cb * 128 + n : 0) * r;
-        unsigned char* drow = dst + (size_t)(n >> 3) * sbo + (n & 7) * 16;
-        for (int j = tid >> 7; j < P; j += 2) cp_async16(drow + j * 128, src + j * 8, valid);
+        for (int n = lane; n < 128; n += 32) {  // row of B = output column of the block
+            const bool valid = cb * 128 + n < rows;
+            const bf16* src = B + (size_t)(valid ? cb * 128 + n : 0) * r;
+            unsigned char* drow = dst + (size_t)(n >> 3) * sbo + (n & 7) * 16;
+            for (int j = 0; j < P; j++) cp_async16(drow + j * 128, src + j * 8, valid);
+        }
     };
+    const int live_warps = 2 * min(4, (len + 31) / 32);  // warps that have rows of the tile
 
     if (tid == 0) {
         mbar_init(&done[0], 1);
         mbar_init(&done[1], 1);
+        mbar_init(&acc_free[0], live_warps);
+        mbar_init(&acc_free[1], live_warps);
+        mbar_init(&a_full, 256);
         for (int w = 0; w < 8; w++)
             for (int i = 0; i < nst; i++) mbar_init(&ybar[w][i], 1);
         mbar_fence_init();
     }
-    if (warp == 0) tmem_alloc(&tmem_slot, 256);
-    load_b(cb0, Bs[0]);  // B is a slab: it may be fetched before the kernels ahead have finished
-    cp_async_commit();
+    if (warp == 8) {
+        tmem_alloc(&tmem_slot, 256);
+        load_b(cb0, Bs[0]);  // B is a slab: it may be fetched before the kernels ahead have finished
+        cp_async_commit();
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
     pdl_wait();
     pdl_trigger();
+
+    if (warp == 8) {
+        // ---- B copies and MMAs, running up to two column blocks ahead of the additions
+        const uint32_t idesc = umma_idesc_bf16(MMA_M, 128);
+        bool ok = mbar_wait_long(&a_full, 0, status);  // S staged by the other warps
+        for (int nb = 0; ok && nb < nblk; nb++) {
+            cp_async_wait<0>();  // this warp's copies of block nb's rows of B
+            fence_async_smem();
+            __syncwarp();
+            // the accumulator this block goes to was last read for block nb - 2
+            if (nb >= 2) ok = mbar_wait_long(&acc_free[nb & 1], ((nb >> 1) - 1) & 1, status);
+            if (!ok) break;
+            if (elect_one()) {
+                tc_fence_after();
+                const uint32_t a_hi = smem_u32(Ahi), a_lo = smem_u32(Alo), b = smem_u32(Bs[nb & 1]);
+                const uint32_t acc = tmem + (uint32_t)(nb & 1) * 128u;
+                for (int kk = 0; kk < r / 16; kk++)
+                    umma_bf16(acc, umma_desc(a_hi + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, kk != 0);
+                for (int kk = 0; kk < r / 16; kk++)
+                    umma_bf16(acc, umma_desc(a_lo + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, 1);
+                umma_commit(&done[nb & 1]);
+            }
+            __syncwarp();
+            if (nb + 1 < nblk) {
+                // the other B buffer was read by block nb - 1's MMAs
+                if (nb >= 1) ok = mbar_wait_long(&done[(nb - 1) & 1], ((nb - 1) >> 1) & 1, status);
+                if (ok) load_b(cb0 + nb + 1, Bs[(nb + 1) & 1]);
+            }
+            cp_async_commit();
+        }
+        // every MMA has completed before the tensor memory goes back
+        if (ok && nblk >= 1) mbar_wait_long(&done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, status);
+        if (ok && nblk >= 2) mbar_wait_long(&done[(nblk - 2) & 1], ((nblk - 2) >> 1) & 1, status);
+        cp_async_wait<0>();
+        tc_fence_before();
+        __syncthreads();
+        tmem_dealloc(tmem, 256);
+        return;
+    }
 
     const int wrow0 = wq * 32;
     const bool live = wrow0 < len;            // the warp has rows of the tile
@@ -676,53 +729,15 @@ __global__ void __launch_bounds__(256) plora_expand_tma_kernel(const float* __re
             *reinterpret_cast<uint4*>(alo + j * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
         }
     }
-    const uint32_t idesc = umma_idesc_bf16(MMA_M, 128);
-    auto issue_mma = [&](int nb) {  // one elected thread of warp 0
-        const uint32_t a_hi = smem_u32(Ahi), a_lo = smem_u32(Alo), b = smem_u32(Bs[nb & 1]);
-        const uint32_t acc = tmem + (uint32_t)(nb & 1) * 128u;
-        for (int kk = 0; kk < r / 16; kk++)
-            umma_bf16(acc, umma_desc(a_hi + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, kk != 0);
-        for (int kk = 0; kk < r / 16; kk++)
-            umma_bf16(acc, umma_desc(a_lo + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, 1);
-        umma_commit(&done[nb & 1]);
-    };
-    // block 0's MMAs, then the copy of block 1's rows of B behind them
-    cp_async_wait<0>();
+    // S is staged: tell the MMA warp (the writes above, made visible to the tensor cores first)
     fence_async_smem();
-    __syncthreads();
-    if (warp == 0) {
-        if (elect_one()) {
-            tc_fence_after();
-            issue_mma(0);
-        }
-        __syncwarp();
-    }
-    if (nblk > 1) load_b(cb0 + 1, Bs[1]);
-    cp_async_commit();
+    mbar_arrive(&a_full);
 
     bool ok = true;
-    for (int nb = 0; nb < nblk; nb++) {
-        // everyone is done with the block before last: its accumulator is free, and block nb + 1's B has landed
-        cp_async_wait<0>();
-        fence_async_smem();
-        tc_fence_before();
-        if (__syncthreads_or(!ok)) {
-            ok = false;
-            break;
-        }
-        if (nb + 1 < nblk && warp == 0) {
-            if (elect_one()) {
-                tc_fence_after();
-                issue_mma(nb + 1);
-            }
-            __syncwarp();
-        }
-        ok = mbar_wait(&done[nb & 1], (nb >> 1) & 1, status);
-        if (!ok) continue;  // meets the others at the barrier above, and all leave
+    for (int nb = 0; ok && live && nb < nblk; nb++) {
+        ok = mbar_wait_long(&done[nb & 1], (nb >> 1) & 1, status);  // block nb's MMAs are complete
+        if (!ok) break;
         tc_fence_after();
-        if (nb + 2 < nblk) load_b(cb0 + nb + 2, Bs[nb & 1]);  // block nb's MMAs are complete: its B buffer is free
-        cp_async_commit();
-        if (!live) continue;
         const uint32_t acc = tmem + ((uint32_t)wrow0 << 16) + (uint32_t)(nb & 1) * 128u;
 #pragma unroll 1
         for (int ci = 0; ci < CPW; ci++) {
@@ -811,12 +826,14 @@ __global__ void __launch_bounds__(256) plora_expand_tma_kernel(const float* __re
                 }
             }
         }
+        // this warp is done with block nb's accumulator
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_free[nb & 1]);
     }
     if (lane == 0) bulk_wait_all();
-    cp_async_wait<0>();
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
 // cuTensorMapEncodeTiled, fetched from the driver once (no link-time dependency on libcuda)
@@ -943,9 +960,9 @@ cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int l
         if (aligned) {
             const size_t smem_tma = 1024 + (size_t)8 * nst * EXP_SLOT_BYTES + (size_t)4 * op_bytes;
             if (f32_out)
-                return launch_pdl(plora_expand_tma_kernel<true>, grid, dim3(256), smem_tma, st, pdl, S, s_stride_elems, lds, K,
+                return launch_pdl(plora_expand_tma_kernel<true>, grid, dim3(288), smem_tma, st, pdl, S, s_stride_elems, lds, K,
                                   tile_split, segs, lay, table, maps, y, ldy, nb_per_cta, op_bytes, nst, status);
-            return launch_pdl(plora_expand_tma_kernel<false>, grid, dim3(256), smem_tma, st, pdl, S, s_stride_elems, lds, K,
+            return launch_pdl(plora_expand_tma_kernel<false>, grid, dim3(288), smem_tma, st, pdl, S, s_stride_elems, lds, K,
                               tile_split, segs, lay, table, maps, y, ldy, nb_per_cta, op_bytes, nst, status);
         }
     }
