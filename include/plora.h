@@ -256,7 +256,7 @@ int plora_linear_bf16_fused(plora_t* h, const plora_hook* hook, const plora_step
  * decode-shaped kernel, which builds the adapter term of all tokens on the CUDA cores inside 128 x 64 tiles and
  * writes y once. Default 1: on B200 the tensor-core form followed by the gather kernel is faster at every size
  * measured (256 mixed decode tokens over 4096 -> 12288: 65 us against 204 us). */
-int plora_set_fused_tile_rows(plora_t* h, int rows);
+int plora_set_fused_tile_rows(plora_t* h, int rows); /* PLORA_FUSED_TILE_ROWS in the environment sets it at plora_create */
 
 /* Shrink and expand of one layer in one call, for callers whose x and y are both ready (that is, after the
  * layer's own matrix multiply, where Linear::forward issues lora_expand: src/linear.rs:844-847). Same results
