@@ -684,7 +684,7 @@ cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t 
 }
 }  // namespace
 
-#define PLORA_GRID_Z_CAP 256  // blocks along the work-item axis; more work items are walked in a loop
+#define PLORA_GRID_Z_CAP 64  // blocks along the work-item axis; more work items are walked in a loop
 
 // rows of A per block: 16 (one 4-row group per warp), so that a slot's rows spread over many blocks and
 // each block's copies are issued and consumed quickly
