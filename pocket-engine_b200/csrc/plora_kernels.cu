@@ -454,6 +454,7 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
 // its two rows of B once per group of 4 tokens and writes y back.
 #define EXP_SPAD 12  // floats per 8-wide piece of an S row in shared memory (conflict-free for rotated reads)
 
+template <bool PASSES>  // whether the tile buffer is smaller than a block's columns at the maximum rank
 __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float* __restrict__ S, size_t s_stride,
                                                                       int lds, int nsplit,
                                                                       const int* __restrict__ segs, SegLayout lay,
@@ -491,7 +492,7 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
     // The tile buffer holds bs_bytes of B: all the block's columns for ranks up to bs_bytes / (2 nc), fewer
     // columns per pass (a multiple of 32) for higher ranks, so that a high maximum rank does not cost every
     // block, whatever its slot's rank, the shared memory that limits how many blocks share an SM.
-    const int sub = min(nc, max(32, (bs_bytes / (2 * r)) & ~31));
+    const int sub = PASSES ? min(nc, max(32, (bs_bytes / (2 * r)) & ~31)) : nc;
     int ncols = min(sub, ncols_all);
     unsigned char* Bs = dsm;
     float* ss = reinterpret_cast<float*>(dsm + bs_bytes);
@@ -657,7 +658,9 @@ cudaError_t plora_kernels_init(const SegLayout& lay) {
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(plora_shrink_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 136 * 1024);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(plora_expand_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    e = cudaFuncSetAttribute(plora_expand_gather_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(plora_expand_gather_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
 }
 
 cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status,
@@ -724,6 +727,9 @@ cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, 
     dim3 grid((unsigned)((max_rows + nc - 1) / nc), (unsigned)parts,
               (unsigned)(work_cap < PLORA_GRID_Z_CAP ? work_cap : PLORA_GRID_Z_CAP));
     const size_t smem = (size_t)bs_bytes + (size_t)PLORA_WORK_TOKENS * (size_t)(max_rank / 8) * EXP_SPAD * sizeof(float);
-    return launch_pdl(plora_expand_gather_kernel, grid, dim3((unsigned)(nc / 2)), smem, st, pdl, S, s_stride_elems, lds, nsplit, segs,
-                      lay, table, y, ldy, f32_out, nc, bs_bytes, early ? 1 : 0, status);
+    if (bs_bytes < nc * max_rank * 2)
+        return launch_pdl(plora_expand_gather_kernel<true>, grid, dim3((unsigned)(nc / 2)), smem, st, pdl, S, s_stride_elems, lds,
+                          nsplit, segs, lay, table, y, ldy, f32_out, nc, bs_bytes, early ? 1 : 0, status);
+    return launch_pdl(plora_expand_gather_kernel<false>, grid, dim3((unsigned)(nc / 2)), smem, st, pdl, S, s_stride_elems, lds,
+                      nsplit, segs, lay, table, y, ldy, f32_out, nc, bs_bytes, early ? 1 : 0, status);
 }
