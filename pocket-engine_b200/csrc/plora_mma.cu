@@ -526,8 +526,10 @@ __global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __re
 
 // ------------------------------------------------------------------------------------------------------
 // The same expand with y moved by tensor copies, for outputs whose base, row pitch and part offsets are
-// 16-byte aligned (every model width in practice; the kernel above stays for the rest). 288 threads: warp 8
-// copies the blocks' rows of B and issues the MMAs, up to two column blocks ahead (mbarriers tell it when S is
+// 16-byte aligned (every model width in practice; the kernel above stays for the rest). Eight adding warps and
+// one more (two blocks per SM; sixteen and one, one block per SM, where the operands of a high maximum rank leave
+// no room for two: measured slower at equal shared memory, 509 against 399 us on the widest prefill layer). The
+// last warp copies the blocks' rows of B and issues the MMAs, up to two column blocks ahead (mbarriers tell it when S is
 // staged and when an accumulator has been read); the other eight never meet at a block-wide barrier inside the
 // loop. Each of them owns the 32 token rows tensor memory gives it (two warps per 32 rows, taking alternate
 // slots of columns) and a private ring of 4 KB slots; a slot holds 32 rows x 128 bytes of y
@@ -555,15 +557,15 @@ __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-template <bool F32>
-__global__ void __launch_bounds__(288) plora_expand_tma_kernel(const float* __restrict__ S, size_t s_stride, int lds, int K,
+template <bool F32, int WPQ>  // WPQ: warps per 32 rows (2 or 4)
+__global__ void __launch_bounds__(32 * (4 * WPQ + 1)) plora_expand_tma_kernel(const float* __restrict__ S, size_t s_stride, int lds, int K,
                                                                 int ksplit, const int* __restrict__ segs, SegLayout lay,
                                                                 const plora_desc* __restrict__ table,
                                                                 const __grid_constant__ ExpandYMaps ymaps, void* Y, int ldy,
                                                                 int nb_per_cta, int op_bytes, int nst,
                                                                 int* __restrict__ status) {
     extern __shared__ unsigned char dsm_raw[];
-    __shared__ __align__(8) uint64_t done[2], acc_free[2], a_full, ybar[8][EXP_RING_MAX];
+    __shared__ __align__(8) uint64_t done[2], acc_free[2], a_full, ybar[4 * WPQ][EXP_RING_MAX];
     __shared__ uint32_t tmem_slot;
     constexpr int CW = F32 ? 32 : 64;  // y columns per slot
     constexpr int CH = 128 / CW;       // slots per block of 128 columns
@@ -583,11 +585,11 @@ __global__ void __launch_bounds__(288) plora_expand_tma_kernel(const float* __re
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     unsigned char* dsm = dsm_raw + ((1024u - (smem_u32(dsm_raw) & 1023u)) & 1023u);
     unsigned char* ring = dsm + (size_t)warp * nst * EXP_SLOT_BYTES;  // this warp's slots
-    unsigned char* ops = dsm + (size_t)8 * nst * EXP_SLOT_BYTES;
+    constexpr int NW = 4 * WPQ;  // warps that add; warp NW copies B and issues the MMAs
+    unsigned char* ops = dsm + (size_t)NW * nst * EXP_SLOT_BYTES;
     // Eight warps: warps w and w + 4 read the same 32 lanes of tensor memory (rows 32 (w % 4) ...) and take
     // the even and the odd slots of every column block.
     const int wq = warp & 3, wh = warp >> 2;
-    constexpr int CPW = CH / 2;  // slots per column block and warp
     unsigned char* Ahi = ops;
     unsigned char* Alo = ops + op_bytes;
     unsigned char* Bs[2] = {ops + 2 * (size_t)op_bytes, ops + 3 * (size_t)op_bytes};
@@ -605,19 +607,20 @@ __global__ void __launch_bounds__(288) plora_expand_tma_kernel(const float* __re
             for (int j = 0; j < P; j++) cp_async16(drow + j * 128, src + j * 8, valid);
         }
     };
-    const int live_warps = 2 * min(4, (len + 31) / 32);  // warps that have rows of the tile
+    // warps that have rows of the tile and a slot in every full column block
+    const int live_warps = (WPQ < CH ? WPQ : CH) * min(4, (len + 31) / 32);
 
     if (tid == 0) {
         mbar_init(&done[0], 1);
         mbar_init(&done[1], 1);
         mbar_init(&acc_free[0], live_warps);
         mbar_init(&acc_free[1], live_warps);
-        mbar_init(&a_full, 256);
-        for (int w = 0; w < 8; w++)
+        mbar_init(&a_full, 32 * NW);
+        for (int w = 0; w < NW; w++)
             for (int i = 0; i < nst; i++) mbar_init(&ybar[w][i], 1);
         mbar_fence_init();
     }
-    if (warp == 8) {
+    if (warp == NW) {
         tmem_alloc(&tmem_slot, 256);
         load_b(cb0, Bs[0]);  // B is a slab: it may be fetched before the kernels ahead have finished
         cp_async_commit();
@@ -629,7 +632,7 @@ __global__ void __launch_bounds__(288) plora_expand_tma_kernel(const float* __re
     pdl_wait();
     pdl_trigger();
 
-    if (warp == 8) {
+    if (warp == NW) {
         // ---- B copies and MMAs, running up to two column blocks ahead of the additions
         const uint32_t idesc = umma_idesc_bf16(MMA_M, 128);
         bool ok = mbar_wait_long(&a_full, 0, status);  // S staged by the other warps
@@ -673,7 +676,7 @@ __global__ void __launch_bounds__(288) plora_expand_tma_kernel(const float* __re
     const bool whole = wrow0 + 32 <= len;     // all its 32 rows are: results go back by tensor store
     const int ycol0 = d.off[p] + cb0 * 128;   // first y column of this block's range
     // the warp's i-th slot is slot q of the block's column range
-    auto slot_of = [&](int i) { return (i / CPW) * CH + wh + 2 * (i % CPW); };
+    auto slot_of = [&](int i) { return wh + WPQ * i; };
     int my_n = 0;  // slots this warp handles
     while (slot_of(my_n) < nchunks) my_n++;
     auto load_y = [&](int i) {                // lane 0 only
@@ -692,7 +695,7 @@ __global__ void __launch_bounds__(288) plora_expand_tma_kernel(const float* __re
         const int s_eff = min(ksplit, plora_tile_chunks(K, d.rank));  // planes the shrink wrote for this slot
         unsigned char* ahi = Ahi + (size_t)(row >> 3) * sbo + (row & 7) * 16;
         unsigned char* alo = Alo + (size_t)(row >> 3) * sbo + (row & 7) * 16;
-        for (int j = tid >> 7; j < P; j += 2) {
+        for (int j = tid >> 7; j < P; j += WPQ) {
             float f[8];
             if (valid && s_eff > 1) {
                 float v[PLORA_TILE_SPLIT_MAX][8];
@@ -734,16 +737,16 @@ __global__ void __launch_bounds__(288) plora_expand_tma_kernel(const float* __re
     mbar_arrive(&a_full);
 
     bool ok = true;
-    for (int nb = 0; ok && live && nb < nblk; nb++) {
-        ok = mbar_wait_long(&done[nb & 1], (nb >> 1) & 1, status);  // block nb's MMAs are complete
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t acc = tmem + ((uint32_t)wrow0 << 16) + (uint32_t)(nb & 1) * 128u;
 #pragma unroll 1
-        for (int ci = 0; ci < CPW; ci++) {
-            const int i = nb * CPW + ci;  // the warp's slot counter
-            if (i >= my_n) break;
-            const int ch = wh + 2 * ci, q = nb * CH + ch;
+    for (int i = 0; ok && live && i < my_n; i++) {  // the warp's slots, in column order
+        const int q = slot_of(i), nb = q / CH, ch = q % CH;
+        if (ch < WPQ) {  // the warp's first slot of column block nb: its MMAs must be complete
+            ok = mbar_wait_long(&done[nb & 1], (nb >> 1) & 1, status);
+            if (!ok) break;
+            tc_fence_after();
+        }
+        const uint32_t acc = tmem + ((uint32_t)wrow0 << 16) + (uint32_t)(nb & 1) * 128u;
+        {
             unsigned char* sl = ring + (size_t)(i % nst) * EXP_SLOT_BYTES;
             if (!mbar_wait(&ybar[warp][i % nst], (i / nst) & 1, status)) {
                 ok = false;
@@ -826,10 +829,11 @@ __global__ void __launch_bounds__(288) plora_expand_tma_kernel(const float* __re
                 }
             }
         }
-        // this warp is done with block nb's accumulator
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_free[nb & 1]);
+        if (ch + WPQ >= CH) {  // the warp's last slot of column block nb: it is done with that accumulator
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_free[nb & 1]);
+        }
     }
     if (lane == 0) bulk_wait_all();
     tc_fence_before();
@@ -859,9 +863,10 @@ cudaError_t plora_mma_init() {
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(plora_expand_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 172 * 1024);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(plora_expand_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(plora_expand_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if ((e = cudaFuncSetAttribute(plora_expand_tma_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024))) return e;
+    if ((e = cudaFuncSetAttribute(plora_expand_tma_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024))) return e;
+    if ((e = cudaFuncSetAttribute(plora_expand_tma_kernel<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024))) return e;
+    return cudaFuncSetAttribute(plora_expand_tma_kernel<true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
 }
 
 namespace {
@@ -940,9 +945,14 @@ cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int l
     const int elt = f32_out ? 4 : 2;
     bool aligned = g_encode && ((uintptr_t)y & 15) == 0 && ((size_t)ldy * elt) % 16 == 0 && rows_total > 0;
     for (int p = 0; p < parts; p++) aligned = aligned && ((size_t)part_off[p] * elt) % 16 == 0;
-    // ring slots per warp: what two blocks per SM leave room for, else what one block per SM does
+    // Two blocks per SM of eight adding warps with the ring slots that leaves room for; where the operands are too
+    // large for that, one block per SM of sixteen adding warps.
+    int wpq = 2;
     int nst = (111 * 1024 - 1024 - 4 * op_bytes) / (8 * EXP_SLOT_BYTES);
-    if (nst < 1) nst = (216 * 1024 - 1024 - 4 * op_bytes) / (8 * EXP_SLOT_BYTES);
+    if (nst < 1) {
+        wpq = 4;
+        nst = (216 * 1024 - 1024 - 4 * op_bytes) / (16 * EXP_SLOT_BYTES);
+    }
     nst = nst > 4 ? 4 : nst;
     if (aligned && nst >= 1) {
         ExpandYMaps maps;
@@ -958,12 +968,18 @@ cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int l
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
         }
         if (aligned) {
-            const size_t smem_tma = 1024 + (size_t)8 * nst * EXP_SLOT_BYTES + (size_t)4 * op_bytes;
-            if (f32_out)
-                return launch_pdl(plora_expand_tma_kernel<true>, grid, dim3(288), smem_tma, st, pdl, S, s_stride_elems, lds, K,
-                                  tile_split, segs, lay, table, maps, y, ldy, nb_per_cta, op_bytes, nst, status);
-            return launch_pdl(plora_expand_tma_kernel<false>, grid, dim3(288), smem_tma, st, pdl, S, s_stride_elems, lds, K,
-                              tile_split, segs, lay, table, maps, y, ldy, nb_per_cta, op_bytes, nst, status);
+            const size_t smem_tma = 1024 + (size_t)4 * wpq * nst * EXP_SLOT_BYTES + (size_t)4 * op_bytes;
+            const dim3 block(32 * (4 * wpq + 1));
+#define PLORA_EXPAND_TMA(F32, WPQ)                                                                                      \
+    return launch_pdl(plora_expand_tma_kernel<F32, WPQ>, grid, block, smem_tma, st, pdl, S, s_stride_elems, lds, K, \
+                      tile_split, segs, lay, table, maps, y, ldy, nb_per_cta, op_bytes, nst, status)
+            if (wpq == 2) {
+                if (f32_out) PLORA_EXPAND_TMA(true, 2);
+                PLORA_EXPAND_TMA(false, 2);
+            }
+            if (f32_out) PLORA_EXPAND_TMA(true, 4);
+            PLORA_EXPAND_TMA(false, 4);
+#undef PLORA_EXPAND_TMA
         }
     }
     // at least 48 KB of shared memory per block: no more than four blocks, 128 tensor-memory columns each,
