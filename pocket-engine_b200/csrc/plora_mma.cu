@@ -934,11 +934,22 @@ cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int l
     const int max_rank = lds / PLORA_MAX_PARTS;
     const int op_bytes = MMA_M * max_rank * 2;
     const int nblocks = (max_rows + 127) / 128;
-    // each block walks up to 8 column blocks with one staging of its S tile; fewer when the step has so few
-    // tiles that the blocks would not fill the SMs twice over
-    const long long total = (long long)(tile_cap + 1) / 2 * nblocks * parts;  // tile_cap counts 64-token halves
-    int nb_per_cta = (int)(total / (2 * 148));
-    nb_per_cta = nb_per_cta < 1 ? 1 : nb_per_cta > 8 ? 8 : nb_per_cta;
+    // Column blocks per thread block (one staging of its S tile each): the count, up to 16, that minimises
+    // waves x (start-up + blocks walked) for the step's estimated tile count, two thread blocks per SM; start-up
+    // (tensor-memory allocation, staging S, the first MMAs) costs about as much as two and a half column blocks.
+    const long long tiles_est = (tile_cap + 1) / 2;  // tile_cap counts 64-token halves
+    int nb_per_cta = 1;
+    double best = 1e30;
+    for (int nb = 1; nb <= 16; nb++) {
+        long long groups = 0;
+        for (int p = 0; p < parts; p++) groups += ((part_rows[p] + 127) / 128 + nb - 1) / nb;
+        const long long waves = (tiles_est * groups + 2 * 148 - 1) / (2 * 148);
+        const double cost = (double)waves * (2.5 + nb);
+        if (cost < best) {
+            best = cost;
+            nb_per_cta = nb;
+        }
+    }
     if (nb_per_cta > nblocks) nb_per_cta = nblocks;
     dim3 grid((unsigned)((nblocks + nb_per_cta - 1) / nb_per_cta), (unsigned)parts, (unsigned)tile_cap);
     // y by tensor copies where its base, pitch and part offsets are 16-byte aligned
