@@ -170,8 +170,10 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
                                                                 const int* __restrict__ segs, SegLayout lay,
                                                                 const plora_desc* __restrict__ table,
                                                                 float* __restrict__ S, size_t s_stride, int lds,
-                                                                int ksplit, int nstage, int stage_bytes,
+                                                                int ksplit, int nstage, int stage_bytes, int sub,
                                                                 int* __restrict__ status) {
+    // `sub` steps of 64 inputs share a stage (1 or 2): with two, a token row's two adjacent 128-byte pieces are
+    // requested together. A stage is then [x box][x box][slab box][slab box] and stage_bytes covers all of it.
     extern __shared__ unsigned char dsm_raw[];
     __shared__ __align__(8) uint64_t full[SHR_MAX_STAGES], empty[SHR_MAX_STAGES], acc_bar;
     __shared__ uint32_t tmem_slot;
@@ -211,7 +213,9 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
     const int nk_all = (K + SHR_KSTEP - 1) / SHR_KSTEP;
     const int spc = (nk_all + n_chunks - 1) / n_chunks;  // steps per chunk
     const int k_first = (int)blockIdx.x * n_acc * spc;
-    const int nk = min(nk_all, k_first + n_acc * spc) - k_first;  // this block's steps
+    const int nk1 = min(nk_all, k_first + n_acc * spc) - k_first;  // this block's steps of 64 inputs
+    const int nk = (nk1 + sub - 1) / sub;                          // and its stages
+    const uint32_t a_box_bytes = (uint32_t)R * 128u;
     // the slab's rows arrive as one box of R rows, or two of R / 2 when R is over the 256-row limit of a box
     const int nbox = R > 256 ? 2 : 1, box_rows = R / nbox;
     pdl_wait();  // x comes from the kernels before
@@ -221,18 +225,33 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
         // producer: one thread feeds the ring, waiting for a stage's MMAs before refilling it
         if (elect_one()) {
             tmap_acquire(amap);
+            // (both role threads are single threads whose instruction latencies are on the critical path: stage
+            // index, barrier parity and chunk position are carried along instead of divided out every step)
+            int st = 0;
+            uint32_t par = 0;  // parity of the "empty" phase to wait for, from the ring's second round on
+            bool round2 = false;
+            int k0 = k_first * SHR_KSTEP;
+            const uint32_t tx = (uint32_t)sub * (SHR_X_BYTES + a_box_bytes);
             for (int ks = 0; ks < nk; ks++) {
-                const int st = ks % nstage;
-                if (ks >= nstage && !mbar_wait(&empty[st], ((ks / nstage) - 1) & 1, status)) {
+                if (ks >= nstage && !mbar_wait(&empty[st], par, status)) {
                     s_fail = 1;
                     break;
                 }
                 unsigned char* xs = ring + (size_t)st * stage_bytes;
-                unsigned char* as = xs + SHR_X_BYTES;
-                const int k0 = (k_first + ks) * SHR_KSTEP;
-                mbar_expect_tx(&full[st], SHR_X_BYTES + (uint32_t)R * 128u);
-                tma_load_2d(xs, &xmap, k0, start, &full[st]);
-                for (int b = 0; b < nbox; b++) tma_load_2d(as + (size_t)b * box_rows * 128, amap, k0, b * box_rows, &full[st]);
+                unsigned char* as = xs + (size_t)sub * SHR_X_BYTES;
+                mbar_expect_tx(&full[st], tx);
+                for (int u = 0; u < sub; u++)  // a step past the block's range reads zeros or unused columns
+                    tma_load_2d(xs + (size_t)u * SHR_X_BYTES, &xmap, k0 + u * SHR_KSTEP, start, &full[st]);
+                for (int u = 0; u < sub; u++)
+                    for (int b = 0; b < nbox; b++)
+                        tma_load_2d(as + (size_t)u * a_box_bytes + (size_t)b * box_rows * 128, amap, k0 + u * SHR_KSTEP,
+                                    b * box_rows, &full[st]);
+                k0 += sub * SHR_KSTEP;
+                if (++st == nstage) {
+                    st = 0;
+                    if (round2) par ^= 1;
+                    round2 = true;
+                }
             }
         }
         __syncwarp();
@@ -241,29 +260,41 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
         if (elect_one()) {
             const uint32_t idesc_lo = umma_idesc_bf16(MMA_M, R > 256 ? 256 : R);
             const uint32_t idesc_hi = umma_idesc_bf16(MMA_M, R > 256 ? R - 256 : 16);
+            // descriptors of stage 0's first x and slab boxes; every other operand is a constant number of 16-byte
+            // units further on (the address field is the low 14 bits: shared memory is under 256 KB)
+            const uint64_t dx0 = umma_desc(smem_u32(ring), 16, 1024, 2);
+            const uint64_t da0 = umma_desc(smem_u32(ring) + (uint32_t)sub * SHR_X_BYTES, 16, 1024, 2);
+            const uint32_t stage16 = (uint32_t)stage_bytes >> 4, abox16 = a_box_bytes >> 4;
+            int st = 0, step = 0, first = 0;  // stage, 64-input step of this block, position inside the K chunk
+            uint32_t par = 0, st16 = 0;
+            uint32_t dacc = tmem;
             for (int it = 0; it < nk; it++) {
-                const int st = it % nstage;
-                if (!mbar_wait(&full[st], (it / nstage) & 1, status)) {
+                if (!mbar_wait(&full[st], par, status)) {
                     s_fail = 1;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t xs = smem_u32(ring + (size_t)st * stage_bytes);
-                const uint32_t as = xs + SHR_X_BYTES;
-                const int acc = it / spc, first = it - acc * spc;
-                const uint32_t dacc = tmem + (uint32_t)acc * acc_cols;
+                for (int u = 0; u < sub && step < nk1; u++, step++) {
+                    const uint64_t dx = dx0 + st16 + (uint32_t)u * (SHR_X_BYTES >> 4);
+                    const uint64_t da = da0 + st16 + (uint32_t)u * abox16;
 #pragma unroll
-                for (int kk = 0; kk < SHR_KSTEP / 16; kk++) {
-                    const uint64_t da = umma_desc(xs + kk * 32, 16, 1024, 2);
-                    const uint64_t db = umma_desc(as + kk * 32, 16, 1024, 2);
-                    umma_bf16(dacc, da, db, idesc_lo, (first | kk) != 0);
-                    if (R > 256) {
-                        const uint64_t db2 = umma_desc(as + 256 * 128 + kk * 32, 16, 1024, 2);
-                        umma_bf16(dacc + 256, da, db2, idesc_hi, (first | kk) != 0);
+                    for (int kk = 0; kk < SHR_KSTEP / 16; kk++) {
+                        umma_bf16(dacc, dx + 2 * kk, da + 2 * kk, idesc_lo, (first | kk) != 0);
+                        if (R > 256) umma_bf16(dacc + 256, dx + 2 * kk, da + (256 * 128 >> 4) + 2 * kk, idesc_hi, (first | kk) != 0);
+                    }
+                    if (++first == spc) {  // the next step starts the next chunk's accumulator
+                        first = 0;
+                        dacc += acc_cols;
                     }
                 }
                 umma_commit(&empty[st]);
                 if (it == nk - 1) umma_commit(&acc_bar);
+                st16 += stage16;
+                if (++st == nstage) {
+                    st = 0;
+                    st16 = 0;
+                    par ^= 1;
+                }
             }
         }
         __syncwarp();
@@ -917,14 +948,17 @@ cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, con
                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    const int stage_bytes = SHR_X_BYTES + ((max_rank_total * 128 + 1023) / 1024) * 1024;
+    int stage_bytes = SHR_X_BYTES + ((max_rank_total * 128 + 1023) / 1024) * 1024;
+    // two steps of 64 inputs per stage where at least three such stages fit
+    const int sub = 3 * 2 * stage_bytes <= 190 * 1024 ? 2 : 1;
+    stage_bytes *= sub;
     int nstage = (190 * 1024) / stage_bytes;
     nstage = nstage > SHR_MAX_STAGES ? SHR_MAX_STAGES : nstage;
     if (nstage < 2) return cudaErrorInvalidValue;
     const size_t smem = (size_t)nstage * stage_bytes + 1024;
     return launch_pdl(plora_shrink_mma_kernel, dim3((unsigned)tile_split, 1, (unsigned)tile_cap), dim3(128), smem, st, pdl,
                       map, reinterpret_cast<const CUtensorMap*>(amaps), K, segs, lay, table, S, s_stride_elems, lds, tile_split,
-                      nstage, stage_bytes, status);
+                      nstage, stage_bytes, sub, status);
 }
 
 cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int lds, int K, int tile_split,
