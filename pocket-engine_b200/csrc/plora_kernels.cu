@@ -454,8 +454,11 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
 // its two rows of B once per group of 4 tokens and writes y back.
 #define EXP_SPAD 12  // floats per 8-wide piece of an S row in shared memory (conflict-free for rotated reads)
 
-template <bool PASSES>  // whether the tile buffer is smaller than a block's columns at the maximum rank
-__global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float* __restrict__ S, size_t s_stride,
+// PASSES: whether the tile buffer is smaller than a block's columns at the maximum rank. NH: column pairs per
+// thread, half a block's width apart (2 for the 512-column blocks of wide layers: 128 threads instead of 256
+// hold the block's registers, so more blocks, and more bytes in flight, share an SM).
+template <bool PASSES, int NH>
+__global__ void __launch_bounds__(256 / NH, 4 * NH) plora_expand_gather_kernel(const float* __restrict__ S, size_t s_stride,
                                                                       int lds, int nsplit,
                                                                       const int* __restrict__ segs, SegLayout lay,
                                                                       const plora_desc* __restrict__ table, void* Y,
@@ -503,8 +506,8 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
     }
     if (threadIdx.x < PLORA_WORK_TOKENS) stok[threadIdx.x] = mytok;
     const int r_off = d.r_off[p];
-    const int c = 2 * threadIdx.x;
-    bool mine = c < ncols;
+    const int c = 2 * threadIdx.x;       // the thread's first column pair; pair h is h * HALF columns further
+    const int HALF = 2 * blockDim.x;
     size_t ycol = (size_t)d.off[p] + c0 + c;
     TRACE_K(2, 3);
     __syncthreads();
@@ -513,18 +516,25 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
         pdl_trigger();
         waited = true;
     }
-    // y of the first token group: on its way before anything else is waited for
-    float2 yv[4];
-    if (mine) {
+    // y of a group of 4 tokens, all of the thread's pairs
+    float2 yv[4][NH];
+    auto load_y = [&](int tg) {
 #pragma unroll
-        for (int t = 0; t < 4; t++) {
-            if (t < cnt) {
-                const size_t at = (size_t)stok[t] * ldy + ycol;
-                if (f32_out) yv[t] = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(Y) + at);
-                else yv[t] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(Y) + at));
+        for (int h = 0; h < NH; h++) {
+            if (c + h * HALF < ncols) {
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    if (tg + t < cnt) {
+                        const size_t at = (size_t)stok[tg + t] * ldy + ycol + h * HALF;
+                        if (f32_out) yv[t][h] = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(Y) + at);
+                        else yv[t][h] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(Y) + at));
+                    }
+                }
             }
         }
-    }
+    };
+    // y of the first token group: on its way before anything else is waited for
+    load_y(0);
     if (!waited) {
         pdl_wait();
         pdl_trigger();
@@ -558,75 +568,58 @@ __global__ void __launch_bounds__(256, 4) plora_expand_gather_kernel(const float
             mbar_expect_tx(&bar, bytes);
             bulk_g2s(Bs, reinterpret_cast<const bf16*>(d.b[p]) + (size_t)(c0 + cs) * r, bytes, &bar);
         }
-        mine = c < ncols;
         ycol = (size_t)d.off[p] + c0 + cs + c;
-        if (mine) {
-#pragma unroll
-            for (int t = 0; t < 4; t++) {
-                if (t < cnt) {
-                    const size_t at = (size_t)stok[t] * ldy + ycol;
-                    if (f32_out) yv[t] = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(Y) + at);
-                    else yv[t] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(Y) + at));
-                }
-            }
-        }
+        load_y(0);
     }
     if (!mbar_wait(&bar, phase, status)) return;
     phase ^= 1;
     TRACE_K(2, 6);
-    if (mine) {
     const int rot = (P >= 8 ? threadIdx.x : threadIdx.x >> 1) % P;
-    const unsigned char* b0 = Bs + (size_t)c * r * 2;
-    const unsigned char* b1 = b0 + (size_t)r * 2;
     const int sstride = P * EXP_SPAD;
     for (int tg = 0; tg < cnt; tg += 4) {
-        if (tg > 0) {
+        if (tg > 0) load_y(tg);
 #pragma unroll
-            for (int t = 0; t < 4; t++) {
-                if (tg + t < cnt) {
-                    const size_t at = (size_t)stok[tg + t] * ldy + ycol;
-                    if (f32_out) yv[t] = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(Y) + at);
-                    else yv[t] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(Y) + at));
-                }
-            }
-        }
-        float acc[4][2];
+        for (int h = 0; h < NH; h++) {
+            if (c + h * HALF >= ncols) continue;
+            const unsigned char* b0 = Bs + (size_t)(c + h * HALF) * r * 2;
+            const unsigned char* b1 = b0 + (size_t)r * 2;
+            float acc[4][2];
 #pragma unroll
-        for (int t = 0; t < 4; t++) acc[t][0] = acc[t][1] = 0.f;
-        int jp = rot;
-        for (int q = 0; q < P; q++) {
-            float f0[8], f1[8];
-            unpack8(lds16(b0 + jp * 16), f0);
-            unpack8(lds16(b1 + jp * 16), f1);
+            for (int t = 0; t < 4; t++) acc[t][0] = acc[t][1] = 0.f;
+            int jp = rot;
+            for (int q = 0; q < P; q++) {
+                float f0[8], f1[8];
+                unpack8(lds16(b0 + jp * 16), f0);
+                unpack8(lds16(b1 + jp * 16), f1);
 #pragma unroll
-            for (int t = 0; t < 4; t++) {
-                if (tg + t < cnt) {
-                    const float* sp = ss + (tg + t) * sstride + jp * EXP_SPAD;
-                    const float4 s0 = *reinterpret_cast<const float4*>(sp);
-                    const float4 s1 = *reinterpret_cast<const float4*>(sp + 4);
-                    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                for (int t = 0; t < 4; t++) {
+                    if (tg + t < cnt) {
+                        const float* sp = ss + (tg + t) * sstride + jp * EXP_SPAD;
+                        const float4 s0 = *reinterpret_cast<const float4*>(sp);
+                        const float4 s1 = *reinterpret_cast<const float4*>(sp + 4);
+                        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        acc[t][0] = fmaf(sv[e], f0[e], acc[t][0]);
-                        acc[t][1] = fmaf(sv[e], f1[e], acc[t][1]);
+                        for (int e = 0; e < 8; e++) {
+                            acc[t][0] = fmaf(sv[e], f0[e], acc[t][0]);
+                            acc[t][1] = fmaf(sv[e], f1[e], acc[t][1]);
+                        }
                     }
                 }
+                jp = jp + 1 == P ? 0 : jp + 1;
             }
-            jp = jp + 1 == P ? 0 : jp + 1;
-        }
 #pragma unroll
-        for (int t = 0; t < 4; t++) {
-            if (tg + t < cnt) {
-                const size_t at = (size_t)stok[tg + t] * ldy + ycol;
-                if (f32_out)
-                    *reinterpret_cast<float2*>(reinterpret_cast<float*>(Y) + at) =
-                        make_float2(yv[t].x + acc[t][0], yv[t].y + acc[t][1]);
-                else
-                    *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<bf16*>(Y) + at) =
-                        __floats2bfloat162_rn(yv[t].x + acc[t][0], yv[t].y + acc[t][1]);
+            for (int t = 0; t < 4; t++) {
+                if (tg + t < cnt) {
+                    const size_t at = (size_t)stok[tg + t] * ldy + ycol + h * HALF;
+                    if (f32_out)
+                        *reinterpret_cast<float2*>(reinterpret_cast<float*>(Y) + at) =
+                            make_float2(yv[t][h].x + acc[t][0], yv[t][h].y + acc[t][1]);
+                    else
+                        *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<bf16*>(Y) + at) =
+                            __floats2bfloat162_rn(yv[t][h].x + acc[t][0], yv[t][h].y + acc[t][1]);
+                }
             }
         }
-    }
     }
     }
     TRACE_K(2, 7);
@@ -651,16 +644,24 @@ size_t plora_meta_group_smem(const SegLayout& lay) {
 
 // One-time function attributes (dynamic shared memory above 48 KB). Called from plora_create, never from
 // the launch path, so launches stay legal inside a stream capture.
+static int g_sms = 148;  // SMs of the device the kernels were set up for
+
 cudaError_t plora_kernels_init(const SegLayout& lay) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaError_t e = cudaFuncSetAttribute(plora_meta_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)plora_meta_group_smem(lay) > 48 * 1024 ? (int)plora_meta_group_smem(lay)
                                                                                        : 48 * 1024);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(plora_shrink_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 136 * 1024);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(plora_expand_gather_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    e = cudaFuncSetAttribute(plora_expand_gather_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(plora_expand_gather_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    e = cudaFuncSetAttribute(plora_expand_gather_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(plora_expand_gather_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(plora_expand_gather_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
 }
 
 cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status,
@@ -727,9 +728,20 @@ cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, 
     dim3 grid((unsigned)((max_rows + nc - 1) / nc), (unsigned)parts,
               (unsigned)(work_cap < PLORA_GRID_Z_CAP ? work_cap : PLORA_GRID_Z_CAP));
     const size_t smem = (size_t)bs_bytes + (size_t)PLORA_WORK_TOKENS * (size_t)(max_rank / 8) * EXP_SPAD * sizeof(float);
-    if (bs_bytes < nc * max_rank * 2)
-        return launch_pdl(plora_expand_gather_kernel<true>, grid, dim3((unsigned)(nc / 2)), smem, st, pdl, S, s_stride_elems, lds,
-                          nsplit, segs, lay, table, y, ldy, f32_out, nc, bs_bytes, early ? 1 : 0, status);
-    return launch_pdl(plora_expand_gather_kernel<false>, grid, dim3((unsigned)(nc / 2)), smem, st, pdl, S, s_stride_elems, lds,
-                      nsplit, segs, lay, table, y, ldy, f32_out, nc, bs_bytes, early ? 1 : 0, status);
+    // 512-column blocks take two column pairs per thread (128 threads instead of 256) where that makes the whole
+    // launch resident at once (8 such blocks of 64 registers per thread share an SM, shared memory permitting):
+    // a launch this small is a chain of dependent fetches per block, and a second wave of blocks pays it again.
+    // Larger launches are bound by their arithmetic and keep one pair per thread.
+    const bool passes = bs_bytes < nc * max_rank * 2;
+    int per_sm = (int)((size_t)(227 * 1024) / (smem + 1024));
+    if (per_sm > 8) per_sm = 8;
+    const int nh = nc >= 512 && (long long)grid.x * grid.y * grid.z <= (long long)per_sm * g_sms ? 2 : 1;
+    const dim3 block((unsigned)(nc / (2 * nh)));
+#define PLORA_EXPAND_ARGS S, s_stride_elems, lds, nsplit, segs, lay, table, y, ldy, f32_out, nc, bs_bytes, early ? 1 : 0, status
+    if (nh == 2)
+        return passes ? launch_pdl(plora_expand_gather_kernel<true, 2>, grid, block, smem, st, pdl, PLORA_EXPAND_ARGS)
+                      : launch_pdl(plora_expand_gather_kernel<false, 2>, grid, block, smem, st, pdl, PLORA_EXPAND_ARGS);
+    return passes ? launch_pdl(plora_expand_gather_kernel<true, 1>, grid, block, smem, st, pdl, PLORA_EXPAND_ARGS)
+                  : launch_pdl(plora_expand_gather_kernel<false, 1>, grid, block, smem, st, pdl, PLORA_EXPAND_ARGS);
+#undef PLORA_EXPAND_ARGS
 }
