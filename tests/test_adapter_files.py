@@ -417,3 +417,53 @@ def test_unload_waits_for_the_requests_that_use_the_adapter(pe, tmp_path):
     assert not mgr.loading() and loras.names() == []
     mgr.close()
     loras.close()
+
+
+def test_readers_survive_damaged_files(pe, tmp_path):
+    """Damaged adapter files (bytes flipped in the headers, truncation, absurd 64-bit sizes and offsets, characters
+    dropped from the JSON) end in an error or in an adapter, never in an out-of-bounds read: both readers check
+    every length and offset against the file before using it."""
+    rng = np.random.default_rng(11)
+    sites = block_sites(pe)
+    loras = pe.Loras(sites, 2, 16, 64, base_gguf=True, device=-1)
+    mods = random_modules(pe, sites, 8, rng)
+    write_peft(pe, tmp_path / "peft", mods, 8)
+    kv = {"general.architecture": (8, "qwen35"), "general.type": (8, "adapter"), "adapter.type": (8, "lora"),
+          "tokenizer.list": (9, ["a", "bc"]), "adapter.lora.alpha": (6, 16.0)}
+    write_gguf(str(tmp_path / "a.gguf"), kv, gguf_tensors(pe, mods, "f16"))
+    good = [(tmp_path / "peft" / "adapter_model.safetensors").read_bytes(), (tmp_path / "a.gguf").read_bytes(),
+            (tmp_path / "peft" / "adapter_config.json").read_bytes()]
+    huge = [2 ** 63, 2 ** 64 - 1, 2 ** 40, 2 ** 32 + 5, 0]
+    read = failed = 0
+    for i in range(400):
+        kind = int(rng.integers(0, 3))
+        b = bytearray(good[kind])
+        head = min(len(b), 4096)
+        mode = int(rng.integers(0, 4))
+        if mode == 0:
+            for _ in range(int(rng.integers(1, 8))):
+                b[int(rng.integers(0, head))] = int(rng.integers(0, 256))
+        elif mode == 1:
+            b = b[:int(rng.integers(0, len(b)))]
+        elif mode == 2:
+            at = int(rng.integers(0, max(1, head - 8)))
+            b[at:at + 8] = struct.pack("<Q", huge[int(rng.integers(0, 5))])
+        else:
+            at = int(rng.integers(0, head))
+            del b[at:at + int(rng.integers(1, 4))]
+        if kind == 1:
+            path = tmp_path / f"c{i}.gguf"
+            path.write_bytes(bytes(b))
+        else:
+            path = tmp_path / f"c{i}"
+            path.mkdir()
+            (path / "adapter_model.safetensors").write_bytes(bytes(b) if kind == 0 else good[0])
+            (path / "adapter_config.json").write_bytes(bytes(b) if kind == 2 else good[2])
+        try:
+            loras.prep().read("x", path).drop()
+            read += 1
+        except Exception as e:
+            assert str(e)  # a message, not an empty error
+            failed += 1
+    assert failed > 200 and read + failed == 400
+    loras.close()
