@@ -269,16 +269,17 @@ void plora_destroy(plora_t* h) {
 const char* plora_last_error(const plora_t* h) { return h ? h->err.c_str() : g_create_err.c_str(); }
 
 uint64_t plora_bytes(const plora_t* h) {  // src/lora.rs:526-528
+    if (!h) return 0;
     return (uint64_t)(h->slot_bytes * (size_t)h->max_slots + h->table_bytes + h->s_bytes);
 }
-uint64_t plora_slot_bytes(const plora_t* h) { return (uint64_t)h->slot_bytes; }
-uint64_t plora_pool_ptr(const plora_t* h) { return (uint64_t)(uintptr_t)h->pool; }
-uint64_t plora_tables_ptr(const plora_t* h) { return (uint64_t)(uintptr_t)h->tables; }
-uint64_t plora_s_ptr(const plora_t* h) { return (uint64_t)(uintptr_t)h->s; }
-uint64_t plora_tiles_ptr(const plora_t* h) { return (uint64_t)(uintptr_t)h->meta; }
-int plora_max_lora_tiles(const plora_t* h) { return h->cap_tiles; }
+uint64_t plora_slot_bytes(const plora_t* h) { return h ? (uint64_t)h->slot_bytes : 0; }
+uint64_t plora_pool_ptr(const plora_t* h) { return h ? (uint64_t)(uintptr_t)h->pool : 0; }
+uint64_t plora_tables_ptr(const plora_t* h) { return h ? (uint64_t)(uintptr_t)h->tables : 0; }
+uint64_t plora_s_ptr(const plora_t* h) { return h ? (uint64_t)(uintptr_t)h->s : 0; }
+uint64_t plora_tiles_ptr(const plora_t* h) { return h ? (uint64_t)(uintptr_t)h->meta : 0; }
+int plora_max_lora_tiles(const plora_t* h) { return h ? h->cap_tiles : 0; }
 int plora_site_splits(const plora_t* h, int site) {
-    if (site < 0 || site >= (int)h->sites.size()) return -1;
+    if (!h || site < 0 || site >= (int)h->sites.size()) return -1;
     return h->sites[(size_t)site].nsplit;
 }
 
@@ -462,6 +463,7 @@ int plora_id(const plora_t* h, const char* name, uint32_t* id) {
 
 // src/lora.rs:544-548
 int plora_names(const plora_t* h, char* buf, size_t cap) {
+    if (!h) return 0;
     std::string all;
     for (auto& kv : h->names) {  // std::map iterates sorted
         if (!all.empty()) all += "\n";
@@ -548,12 +550,14 @@ plora_slots_t* plora_slots_new(int slots) {
 void plora_slots_free(plora_slots_t* s) { delete s; }
 
 int plora_slots_holding(const plora_slots_t* s, uint32_t a) {
+    if (!s) return 0;
     for (size_t i = 1; i < s->held.size(); i++)
         if (s->held[i] == a) return (int)i;
     return 0;
 }
 
 int plora_slots_can_place(const plora_slots_t* s, uint32_t a) {
+    if (!s) return 0;
     if (plora_slots_holding(s, a)) return 1;
     for (size_t i = 1; i < s->held.size(); i++)
         if (s->refs[i] == 0) return 1;
@@ -563,7 +567,7 @@ int plora_slots_can_place(const plora_slots_t* s, uint32_t a) {
 // The slot holding the adapter, else among slots nobody runs on: an empty one first, then the least
 // recently placed; the first of equals (src/sched.rs:430-448).
 int plora_slots_place(plora_slots_t* s, uint32_t a) {
-    if (!plora_slots_can_place(s, a)) return -1;
+    if (!s || !plora_slots_can_place(s, a)) return -1;
     s->clock += 1;
     int i = plora_slots_holding(s, a);
     if (!i) {
@@ -583,15 +587,17 @@ int plora_slots_place(plora_slots_t* s, uint32_t a) {
 }
 
 void plora_slots_release(plora_slots_t* s, int slot) {
-    if (slot > 0 && (size_t)slot < s->refs.size() && s->refs[(size_t)slot] > 0) s->refs[(size_t)slot] -= 1;
+    if (s && slot > 0 && (size_t)slot < s->refs.size() && s->refs[(size_t)slot] > 0) s->refs[(size_t)slot] -= 1;
 }
 
 void plora_slots_forget(plora_slots_t* s, uint32_t a) {
+    if (!s) return;
     int i = plora_slots_holding(s, a);
     if (i) s->held[(size_t)i] = 0;
 }
 
 int plora_slots_take_loads(plora_slots_t* s, int32_t* slot_out, uint32_t* id_out, int cap) {
+    if (!s || !slot_out || !id_out || cap <= 0) return 0;
     int n = std::min<int>(cap, (int)s->loads.size());
     for (int i = 0; i < n; i++) {
         slot_out[i] = s->loads[(size_t)i].first;
@@ -604,16 +610,21 @@ int plora_slots_take_loads(plora_slots_t* s, int32_t* slot_out, uint32_t* id_out
 // ---------------------------------------------------------------- tile rule
 
 int plora_plan_tiles(const int32_t* row_n, const int32_t* row_slot, int n_rows) {
+    if (n_rows > 0 && (!row_n || !row_slot)) return -1;
     int tiles = 0;
-    for (int i = 0; i < n_rows; i++)
+    for (int i = 0; i < n_rows; i++) {
+        if (row_n[i] < 0) return -1;
         if (row_slot[i] != 0) tiles += (row_n[i] + PLORA_TILE - 1) / PLORA_TILE;
+    }
     return tiles;
 }
 
 int plora_fill_tiles(const int32_t* row_n, const int32_t* row_slot, int n_rows, int32_t* words, int cap_tiles) {
+    if (!words || (n_rows > 0 && (!row_n || !row_slot))) return -1;
     int tiles = 0, t = 0;
     for (int i = 0; i < n_rows; i++) {
         const int n = row_n[i];
+        if (n < 0) return -1;
         if (row_slot[i] != 0)
             for (int k = 0; k < n; k += PLORA_TILE) {
                 if (tiles >= cap_tiles) return -1;

@@ -23,6 +23,21 @@ def test_library_exports_every_declared_symbol(pe):
         assert getattr(lib, name) is not None
 
 
+def test_null_arguments_are_refused_not_dereferenced(pe):
+    """Every entry point called with null pointers and zero sizes returns (an error status, 0 or null): a
+    binding that passes a handle it failed to create must get a status back, not a crash."""
+    ints = (C.c_int, C.c_uint32, C.c_uint64, C.c_size_t)
+    for name, (res, args) in sorted(pe.SYMBOLS.items()):
+        if name == "plora_create":
+            continue
+        out = getattr(pe.lib, name)(*[0 if a in ints else None for a in args])
+        handle_first = args and args[0] is C.c_void_p and name not in ("plora_adapter_drop",)
+        if res is C.c_int and handle_first and name.startswith(("plora_shrink", "plora_expand", "plora_apply", "plora_upload",
+                                                                "plora_insert", "plora_meta", "plora_step_begin",
+                                                                "plora_linear", "plora_s_", "plora_exchange")):
+            assert out != 0, name
+
+
 def test_compute_fails_loudly_without_a_device(pe):
     import torch
     if torch.cuda.is_available():
