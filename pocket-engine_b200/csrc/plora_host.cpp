@@ -219,6 +219,7 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
             if (h->mma_ok) h->seg.run_min = PLORA_RUN_MIN_DEFAULT;
             if (const char* e = getenv("PLORA_PDL")) h->pdl = e[0] != '0';
             if (const char* e = getenv("PLORA_FUSED_TILE_ROWS")) h->fused_tile_rows = std::max(1, atoi(e));
+            if (const char* e = getenv("PLORA_TILE_LATE")) h->tile_late = e[0] != '0';
             if (rc == PLORA_OK) {
                 memset(h->host_tables, 0, h->table_bytes);
                 check("zero tables", cudaMemset(h->tables, 0, h->table_bytes));  // src/lora.rs:494
@@ -725,7 +726,7 @@ static int shrink_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
                                    h->seg, (const plora_desc*)(uintptr_t)hook->table,
                                    h->amaps + (size_t)hook->site * (size_t)(h->max_slots + 1), (float*)(uintptr_t)step->s,
                                    (size_t)(step->s_stride / 4), step->lds, hook->parts * h->max_rank, std::max(1, rows / 64),
-                                   tile_split(h, rows), h->status, h->pdl, as_stream(stream)));
+                                   tile_split(h, rows), h->status, h->pdl, h->tile_late, as_stream(stream)));
     return PLORA_OK;
 }
 
@@ -775,7 +776,7 @@ int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint
                                    h->seg, (const plora_desc*)(uintptr_t)hook->table,
                                    h->amaps + (size_t)hook->site * (size_t)(h->max_slots + 1), (float*)(uintptr_t)step->s,
                                    (size_t)(step->s_stride / 4), step->lds, hook->parts * h->max_rank, std::max(1, rows / 64),
-                                   tile_split(h, rows), h->status, h->pdl, as_stream(stream)));
+                                   tile_split(h, rows), h->status, h->pdl, false, as_stream(stream)));
         CU(h, "expand (tile path)",
            plora_launch_expand_mma((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.cols,
                                    tile_split(h, rows), (const int32_t*)(uintptr_t)step->segs, h->seg,

@@ -124,6 +124,7 @@ struct plora {
     bool fp8_ok = false;    // the fused FP8 layer can run
     bool gemm_ok = false;   // the one-kernel layer for prefill-sized steps can run
     int fused_tile_rows = 1;  // steps with at least this many rows take it (plora_set_fused_tile_rows)
+    bool tile_late = true;    // the tile shrink runs beside the gather shrink launched right before it (PLORA_TILE_LATE=0: behind it)
     bool mma_ok = false;    // the tensor-core tile kernels can run (max_rank <= 128 and the driver entry point exists)
     bool pdl_armed = false;  // false right after the step's grouping kernel: the next launch is a plain one
 };
@@ -196,7 +197,7 @@ cudaError_t plora_launch_gemm_fused(int kind, const void* x, const float* st_, c
 cudaError_t plora_mma_encode_slab(void* out128, const void* a, int K, int R);
 cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, const int32_t* segs, SegLayout lay,
                                     const plora_desc* table, const PloraTmap* amaps, float* S, size_t s_stride_elems, int lds,
-                                    int max_rank_total, int tile_cap, int tile_split, int* status, bool pdl,
+                                    int max_rank_total, int tile_cap, int tile_split, int* status, bool pdl, bool late,
                                     cudaStream_t st);
 cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int lds, int K, int tile_split,
                                     const int32_t* segs, SegLayout lay, const plora_desc* table, void* y, int ldy,

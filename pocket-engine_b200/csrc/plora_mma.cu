@@ -171,7 +171,12 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
                                                                 const plora_desc* __restrict__ table,
                                                                 float* __restrict__ S, size_t s_stride, int lds,
                                                                 int ksplit, int nstage, int stage_bytes, int sub,
-                                                                int* __restrict__ status) {
+                                                                int late, int* __restrict__ status) {
+    // late != 0: the kernel launched right before this one is the same layer's gather shrink, whose blocks let
+    // this grid start only after they have themselves waited for the kernels before (or whose caller vouches
+    // that x is older than those). x is then complete when this grid starts, the gather shrink writes other
+    // rows of S, and only this grid's stores have to come after the dependency wait: the whole main loop runs
+    // beside the gather shrink instead of behind it.
     // `sub` steps of 64 inputs share a stage (1 or 2): with two, a token row's two adjacent 128-byte pieces are
     // requested together. A stage is then [x box][x box][slab box][slab box] and stage_bytes covers all of it.
     extern __shared__ unsigned char dsm_raw[];
@@ -218,7 +223,7 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
     const uint32_t a_box_bytes = (uint32_t)R * 128u;
     // the slab's rows arrive as one box of R rows, or two of R / 2 when R is over the 256-row limit of a box
     const int nbox = R > 256 ? 2 : 1, box_rows = R / nbox;
-    pdl_wait();  // x comes from the kernels before
+    if (!late) pdl_wait();  // x comes from the kernels before
     pdl_trigger();
 
     if (warp == 0) {
@@ -302,6 +307,7 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
     // everyone: the accumulators are complete once the last commit has arrived
     bool ok = mbar_wait_long(&acc_bar, 0, status);
     __syncthreads();
+    if (late) pdl_wait();  // before any store, and on every path: this grid must outlast the ones before it
     if (ok && !s_fail) {
         tc_fence_after();
         const int row = tid;
@@ -936,7 +942,7 @@ cudaError_t plora_mma_encode_slab(void* out128, const void* a, int K, int R) {
 
 cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, const int32_t* segs, SegLayout lay,
                                     const plora_desc* table, const PloraTmap* amaps, float* S, size_t s_stride_elems, int lds,
-                                    int max_rank_total, int tile_cap, int tile_split, int* status, bool pdl,
+                                    int max_rank_total, int tile_cap, int tile_split, int* status, bool pdl, bool late,
                                     cudaStream_t st) {
     if (!g_encode) return cudaErrorNotSupported;
     CUtensorMap map;
@@ -958,7 +964,7 @@ cudaError_t plora_launch_shrink_mma(const void* x, int rows, int ldx, int K, con
     const size_t smem = (size_t)nstage * stage_bytes + 1024;
     return launch_pdl(plora_shrink_mma_kernel, dim3((unsigned)tile_split, 1, (unsigned)tile_cap), dim3(128), smem, st, pdl,
                       map, reinterpret_cast<const CUtensorMap*>(amaps), K, segs, lay, table, S, s_stride_elems, lds, tile_split,
-                      nstage, stage_bytes, sub, status);
+                      nstage, stage_bytes, sub, late && pdl ? 1 : 0, status);
 }
 
 cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int lds, int K, int tile_split,
