@@ -467,3 +467,30 @@ def test_readers_survive_damaged_files(pe, tmp_path):
             failed += 1
     assert failed > 200 and read + failed == 400
     loras.close()
+
+
+def test_many_loads_in_flight_at_once(pe, tmp_path):
+    """Twelve adapters started back to back (one worker thread each, two of them unreadable) while the engine
+    thread keeps calling finish_loads: every ticket gets its own answer, every good adapter is registered exactly
+    once, and closing the manager leaves no thread behind."""
+    sites = block_sites(pe, layers=2)
+    loras = pe.Loras(sites, 4, 16, 64, device=-1)
+    mgr = pe.AdapterManager(loras)
+    names = [f"ad{i}" for i in range(10)]
+    make_dirs(pe, tmp_path, sites, names)
+    (tmp_path / "broken").mkdir()
+    (tmp_path / "broken" / "adapter_config.json").write_text("{")
+    tickets = {n: mgr.load(n, tmp_path / n) for n in names}
+    tickets["broken"] = mgr.load("broken", tmp_path / "broken")
+    tickets["missing"] = mgr.load("missing", tmp_path / "missing")
+    joined = {n: mgr.load(n, tmp_path / n, on_demand=True) for n in names[:3]}  # wait for the loads in flight
+    answers = {n: mgr.settle(t) for n, t in tickets.items()}
+    for n in names:
+        assert answers[n] == (pe.OK, ""), (n, answers[n])
+    for n in names[:3]:
+        assert mgr.settle(joined[n]) == (pe.OK, "")
+    assert answers["broken"][0] == pe.ERR_CONFIG and answers["missing"][0] == pe.ERR_CONFIG
+    assert sorted(loras.names()) == sorted(names) and not mgr.loading()
+    assert sorted(loras.id(n) for n in names) == list(range(1, 11))
+    mgr.close()
+    loras.close()
