@@ -156,6 +156,9 @@ int plora_free(plora_t* h, uint32_t id);
 int plora_id(const plora_t* h, const char* name, uint32_t* id);
 /* names, sorted, '\n'-separated into buf; returns the count */
 int plora_names(const plora_t* h, char* buf, size_t cap);
+/* Loras::adapter (src/lora.rs:625-627): the registered adapter, still owned by the registry (valid until
+ * plora_free of that id; never pass it to plora_adapter_drop), or NULL when the id is not loaded */
+const plora_adapter_t* plora_adapter_of(const plora_t* h, uint32_t id);
 /* Loras::upload (src/lora.rs:589-623): slab and descriptors, stream-ordered */
 int plora_upload(plora_t* h, int slot, uint32_t id, void* stream);
 /* Loras::hook (src/lora.rs:530-538) */

@@ -114,6 +114,7 @@ SYMBOLS = {
     "plora_free": (_I, [_P, C.c_uint32]),
     "plora_id": (_I, [_P, C.c_char_p, _U32P]),
     "plora_names": (_I, [_P, C.c_char_p, C.c_size_t]),
+    "plora_adapter_of": (_P, [_P, C.c_uint32]),
     "plora_upload": (_I, [_P, _I, C.c_uint32, _P]),
     "plora_hook_of": (_I, [_P, _I, C.POINTER(Hook)]),
     "plora_desc_of": (_I, [_P, _I, _I, C.POINTER(Desc)]),
@@ -275,9 +276,9 @@ class Adapter:
         return np.ctypeslib.as_array(lib.plora_adapter_data(self._ptr), shape=(n,)).copy()
 
     def drop(self):
-        if self._ptr:
+        if self._ptr and not getattr(self, "_borrowed", False):
             lib.plora_adapter_drop(self._ptr)
-            self._ptr = None
+        self._ptr = None
 
 
 class Prep:
@@ -467,6 +468,15 @@ class Loras:
         buf = C.create_string_buffer(1 << 16)
         n = lib.plora_names(self._h, buf, len(buf))
         return buf.value.decode().split("\n") if n else []
+
+    def adapter(self, id):  # src/lora.rs:625-627
+        """The registered adapter (owned by the registry: valid until free(id)), or None."""
+        ptr = lib.plora_adapter_of(self._h, id)
+        if not ptr:
+            return None
+        a = Adapter(ptr, None)
+        a._borrowed = True
+        return a
 
     def insert(self, adapter):  # src/lora.rs:562-574
         v = C.c_uint32()

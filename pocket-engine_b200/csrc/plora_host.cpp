@@ -478,6 +478,13 @@ int plora_names(const plora_t* h, char* buf, size_t cap) {
     return (int)h->names.size();
 }
 
+// src/lora.rs:625-627
+const plora_adapter_t* plora_adapter_of(const plora_t* h, uint32_t id) {
+    if (!h) return nullptr;
+    auto it = h->adapters.find(id);
+    return it == h->adapters.end() ? nullptr : it->second;
+}
+
 // src/lora.rs:589-623
 int plora_upload(plora_t* h, int slot, uint32_t id, void* stream) {
     if (!h) return PLORA_ERR_ARG;

@@ -472,7 +472,7 @@ def test_readers_survive_damaged_files(pe, tmp_path):
 def test_many_loads_in_flight_at_once(pe, tmp_path):
     """Twelve adapters started back to back (one worker thread each, two of them unreadable) while the engine
     thread keeps calling finish_loads: every ticket gets its own answer, every good adapter is registered exactly
-    once, and closing the manager leaves no thread behind."""
+    once with the slab a direct read gives, and closing the manager leaves no thread behind."""
     sites = block_sites(pe, layers=2)
     loras = pe.Loras(sites, 4, 16, 64, device=-1)
     mgr = pe.AdapterManager(loras)
@@ -487,6 +487,9 @@ def test_many_loads_in_flight_at_once(pe, tmp_path):
     answers = {n: mgr.settle(t) for n, t in tickets.items()}
     for n in names:
         assert answers[n] == (pe.OK, ""), (n, answers[n])
+        want = loras.prep().read(n, tmp_path / n)
+        assert np.array_equal(loras.adapter(loras.id(n)).bytes(), want.bytes())
+        want.drop()
     for n in names[:3]:
         assert mgr.settle(joined[n]) == (pe.OK, "")
     assert answers["broken"][0] == pe.ERR_CONFIG and answers["missing"][0] == pe.ERR_CONFIG

@@ -110,6 +110,10 @@ def test_registry_semantics(pe):
     a, b = adapter("alpha"), adapter("beta")
     assert lay.insert(a) == 1 and lay.insert(b) == 2  # ids from 1 (src/lora.rs:507,569-570)
     assert lay.names() == ["alpha", "beta"] and lay.id("beta") == 2 and lay.id("gamma") is None
+    got = lay.adapter(2)  # src/lora.rs:625-627
+    assert got.rank == 8 and got.len == (16 * 64 + 32 * 16) * 2 and lay.adapter(9) is None
+    got.drop()  # a borrowed view: dropping it leaves the registry's adapter alone
+    assert lay.adapter(2).rank == 8
     with pytest.raises(pe.PloraError) as e:  # src/lora.rs:563-568
         lay.insert(adapter("alpha"))
     assert e.value.code == pe.ERR_DUPLICATE
