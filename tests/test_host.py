@@ -217,3 +217,18 @@ def test_workload_accounting(pe):
     assert abs(w["bytes"] / 1e6 - 48.67) < 0.05
     w3 = workloads.config3().work()
     assert abs(w3["bytes"] / 1e6 - 3491.7) < 1.0 and abs(w3["flops"] / 1e9 - 158.9) < 0.2
+
+
+def test_a_plain_c_program_can_use_the_library(pe, tmp_path):
+    """include/plora.h compiles as C99 and a C program linked against libplora.so sees the struct layouts, the
+    registry, descriptors, slot policy and tile rule the header promises (tests/cabi_consumer.c)."""
+    import subprocess
+    exe = tmp_path / "cabi_consumer"
+    lib_dir = os.path.dirname(pe.LIB_PATH)
+    build = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"),
+                            os.path.join(ROOT, "tests", "cabi_consumer.c"), "-o", str(exe), "-L", lib_dir,
+                            "-l:" + os.path.basename(pe.LIB_PATH), "-Wl,-rpath," + lib_dir],
+                           capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0 and run.stdout.strip() == "ok", run.stderr
