@@ -27,6 +27,11 @@
 extern "C" {
 #endif
 
+/* Bumped whenever a struct layout or a signature below changes; a binding compares it with
+ * plora_abi_version() of the library it loaded before making any other call. */
+#define PLORA_ABI_VERSION 1
+int plora_abi_version(void);
+
 #define PLORA_MAX_PARTS 4  /* src/lora.rs:14 */
 #define PLORA_RANK_STEP 16 /* src/lora.rs:16 */
 #define PLORA_TILE 16      /* src/lora.rs:18 */

@@ -113,6 +113,7 @@ SYMBOLS = {
     "plora_retire": (_I, [_P, C.c_char_p, _U32P]),
     "plora_free": (_I, [_P, C.c_uint32]),
     "plora_id": (_I, [_P, C.c_char_p, _U32P]),
+    "plora_abi_version": (_I, []),
     "plora_names": (_I, [_P, C.c_char_p, C.c_size_t]),
     "plora_adapter_of": (_P, [_P, C.c_uint32]),
     "plora_upload": (_I, [_P, _I, C.c_uint32, _P]),
@@ -174,6 +175,10 @@ def _load():
 
 
 lib = _load()
+ABI_VERSION = 1  # include/plora.h PLORA_ABI_VERSION
+if lib.plora_abi_version() != ABI_VERSION:
+    raise ImportError(f"{LIB_PATH} has ABI version {lib.plora_abi_version()}, this binding was written for {ABI_VERSION}: "
+                      "rebuild it with `python pocket-engine_b200/build.py --force`")
 
 
 # ------------------------------------------------------------------------------------------ bf16

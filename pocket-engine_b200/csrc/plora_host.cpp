@@ -267,6 +267,8 @@ void plora_destroy(plora_t* h) {
     delete h;
 }
 
+int plora_abi_version(void) { return PLORA_ABI_VERSION; }
+
 const char* plora_last_error(const plora_t* h) { return h ? h->err.c_str() : g_create_err.c_str(); }
 
 uint64_t plora_bytes(const plora_t* h) {  // src/lora.rs:526-528

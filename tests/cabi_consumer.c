@@ -17,6 +17,7 @@
     } while (0)
 
 int main(void) {
+    CHECK(plora_abi_version() == PLORA_ABI_VERSION);
     CHECK(sizeof(plora_desc) == 112); /* src/lora.rs:59-70 */
     CHECK(sizeof(plora_hook) == 32);
     CHECK(sizeof(plora_step) == 48);
