@@ -122,9 +122,11 @@ def kernel_bytes(wl, si, which, f32_out=False):
         r = wl.ranks[s - 1]
         if which == "shrink":
             b += 2 * np_ * r * site.cols + ta * np_ * r * 4
-        else:
+        elif which == "expand":
             b += 2 * n_tot * r + ta * np_ * r * 4 + ta * n_tot * ye
-    if which == "shrink":
+        else:  # "site": one kernel per layer, the intermediate never leaves the chip
+            b += 2 * np_ * r * site.cols + 2 * n_tot * r + ta * n_tot * ye
+    if which in ("shrink", "site"):
         b += 2 * int((tslot > 0).sum()) * site.cols
     return b
 
@@ -178,7 +180,8 @@ def run_ours(args, rank, world, local_rank):
         L.meta_build(cu.data_ptr(), ss.data_ptr(), wl.n_seqs, main.cuda_stream)
         step = L.lora_step(L.max_lora_tiles(), main.cuda_stream, decode=decode)
         lins = [pe.Linear(L, si) for si in range(ns)]
-        L.set_apply_mode(1 if args.path == "cluster" else 0)
+        L.set_apply_mode(0 if args.path == "apply-pair" else 1)
+        L.set_early_x(args.early_x)
         return {"L": L, "x": x, "y": y, "cu": cu, "ss": ss, "step": step, "lins": lins, "pack": pack,
                 "meta": meta_dev, "yreg": pack[int(y_off[0]):]}
 
@@ -286,14 +289,17 @@ def run_ours(args, rank, world, local_rank):
     with torch.cuda.stream(main):
         m = main.cuda_stream
         for si in range(ns):
-            for which in ("shrink", "expand"):
+            for which in (("site",) if args.path == "apply" and decode else ("shrink", "expand")):
                 def launches():
                     for S in sets:
                         hook = S["lins"][si].lora
                         if which == "shrink":
                             S["L"].shrink(hook, S["step"], S["x"][si].data_ptr(), wl.tokens, m)
-                        else:
+                        elif which == "expand":
                             S["L"].expand(hook, S["step"], wl.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1], False, m)
+                        else:
+                            S["L"].apply(hook, S["step"], S["x"][si].data_ptr(), wl.tokens, S["y"][si].data_ptr(),
+                                         S["y"][si].shape[1], False, m)
                 launches()
                 main.synchronize()
                 g = torch.cuda.CUDAGraph()
@@ -343,10 +349,11 @@ def run_ours(args, rank, world, local_rank):
                    "l2": f"inputs larger than L2: {copies} rotating copies of pool+x+y = "
                          f"{copies * (pool_bytes + d2h + h2d // 2) / 2 ** 20:.0f} MiB",
                    "partitioning": "adapter-affine, one batch per GPU, no collective",
-                   "graph": f"one CUDA graph per copy, {args.streams} stream(s)", "path": args.path},
+                   "graph": f"one CUDA graph per copy, {args.streams} stream(s)", "path": args.path,
+                   "early_x": bool(args.early_x)},
         "e2e": {"value": world * wl.tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps, "steps_in_flight": depth},
-        "gpu_launches": (8 if decode else 16) * args.steps,
+        "gpu_launches": ((4 if args.path == "apply" else 8) if decode else 16) * args.steps,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                      "peak_kind": peak_kind, "traffic": NCU_TRAFFIC.get((wl.name, dom)), "us_per_launch": kern[dom]["us"],
                      "algorithmic_bytes_per_launch": kern[dom]["bytes"]},
@@ -857,10 +864,12 @@ def main():
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="tp workload only: how the row-parallel shrink partials are summed over the ranks: the "
                          "library's one-kernel exchange over peer memory, or an NCCL all-reduce")
-    ap.add_argument("--path", default="apply", choices=["apply", "cluster", "pair"],
-                    help="apply: plora_apply after the layer's own matrix multiply (shrink and expand fetch x and y "
-                         "ahead of their dependency waits); cluster: plora_apply as one cluster kernel per layer; "
-                         "pair: the engine's shrink-before / expand-after bracket")
+    ap.add_argument("--path", default="apply", choices=["apply", "apply-pair", "pair"],
+                    help="apply: plora_apply after the layer's own matrix multiply, one cluster kernel per layer; "
+                         "apply-pair: plora_apply as the shrink / expand pair; pair: the engine's shrink-before / "
+                         "expand-after bracket (plora_shrink, plora_expand)")
+    ap.add_argument("--early-x", action="store_true",
+                    help="plora_set_early_x(1): the caller vouches for x, which is then read ahead of the dependency wait")
     ap.add_argument("--streams", type=int, default=1, choices=[1, 2],
                     help="1: one stream, kernels chained by programmatic dependent launch; 2: the engine's "
                          "side-stream shrink with fork/join events")

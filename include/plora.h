@@ -29,7 +29,7 @@ extern "C" {
 
 /* Bumped whenever a struct layout or a signature below changes; a binding compares it with
  * plora_abi_version() of the library it loaded before making any other call. */
-#define PLORA_ABI_VERSION 1
+#define PLORA_ABI_VERSION 2
 int plora_abi_version(void);
 
 #define PLORA_MAX_PARTS 4  /* src/lora.rs:14 */
@@ -227,7 +227,9 @@ int plora_meta_build(plora_t* h, uint64_t cu_dev, uint64_t seq_slot_dev, int n_s
 /* The engine's own route: tile words written on the host (pinned or pageable), copied stream-ordered. */
 int plora_meta_upload(plora_t* h, const int32_t* words, void* stream);
 /* Act::lora_step(l, max_tiles, decode): regroups the handle's tile words by slot on the device (once per
- * step, before the first layer) and returns the per-step handle. max_tiles bounds the launch grids
+ * step, before the first layer), resolves every few-token work item against each layer's descriptor table into
+ * the step's launch records, and returns the per-step handle. Slot uploads of a step therefore come before
+ * its plora_step_begin on the stream, as in the engine (src/lora.rs:589-623: "before the next step"). max_tiles bounds the launch grids
  * (src/engine.rs:448-451). decode != 0 says the step holds only tiles of a few tokens (the decoding graphs),
  * so the tensor-core tile kernels are neither fed nor launched. */
 int plora_step_begin(plora_t* h, int max_tiles, int decode, void* stream, plora_step* out);
@@ -269,14 +271,24 @@ int plora_set_fused_tile_rows(plora_t* h, int rows); /* PLORA_FUSED_TILE_ROWS in
 /* Shrink and expand of one layer in one call, for callers whose x and y are both ready (that is, after the
  * layer's own matrix multiply, where Linear::forward issues lora_expand: src/linear.rs:844-847). Same results
  * as plora_shrink + plora_expand (bitwise in mode 0; within the stated tolerance in mode 1, whose summation
- * order differs); deterministic. */
+ * order differs); deterministic.
+ *
+ * What runs ahead of the kernel before. The kernels of this call are launched with programmatic stream
+ * serialization and release their own dependents at once, so consecutive calls overlap: before its dependency
+ * wait a kernel reads only slabs and the step's launch records and sends L2 prefetch hints for the x and y
+ * lines it will touch. It binds no value of x or y and stores nothing until the kernel launched before it on
+ * the stream (typically the matrix multiply that wrote y) has completed. So any producer of x and y is safe,
+ * whether or not it releases its dependents early itself. */
 int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, int rows, uint64_t y, int ldy,
                 int f32_out, void* stream);
-/* How plora_apply runs the few-token work items: 0 (default) = the shrink / expand pair, each fetching its
- * activations ahead of its dependency wait (x and y must not be outputs of the kernel launched right before
- * plora_apply on the same stream: true after the layer's own matrix multiply, whose kernels do not write x, and
- * y is only read by the second of the two kernels); 1 = one cluster kernel per layer where the shapes fit. */
+/* How plora_apply runs the few-token work items: 1 (default) = one cluster kernel per layer where the layer's
+ * shapes fit its shared memory, else as mode 0; 0 = the shrink / expand pair. */
 int plora_set_apply_mode(plora_t* h, int mode);
+/* on != 0: the caller vouches that x, at every later plora_apply, was complete before the kernel launched right
+ * before plora_apply STARTED (true when that kernel is the layer's matrix multiply launched in plain stream
+ * order, which reads x itself): x is then also read ahead of the dependency wait and only the y update comes
+ * after it. Default off. y is never read early. */
+int plora_set_early_x(plora_t* h, int on);
 
 /* Tensor-parallel row-parallel layers (no counterpart in the single-GPU engine): plora_s_reduce adds the
  * shrink's K-split partials into plane 0 of S ([max_tokens, lds] f32 at plora_s_ptr), the caller all-reduces

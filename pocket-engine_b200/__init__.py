@@ -142,6 +142,7 @@ SYMBOLS = {
     "plora_set_fused_tile_rows": (_I, [_P, _I]),
     "plora_apply": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _U64, _I, _U64, _I, _I, _P]),
     "plora_set_apply_mode": (_I, [_P, _I]),
+    "plora_set_early_x": (_I, [_P, _I]),
     "plora_s_reduce": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _P]),
     "plora_expand_reduced": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _U64, _I, _I, _P]),
     "plora_exchange_create": (_I, [_P, _I, _I, _I]),
@@ -175,7 +176,7 @@ def _load():
 
 
 lib = _load()
-ABI_VERSION = 1  # include/plora.h PLORA_ABI_VERSION
+ABI_VERSION = 2  # include/plora.h PLORA_ABI_VERSION
 if lib.plora_abi_version() != ABI_VERSION:
     raise ImportError(f"{LIB_PATH} has ABI version {lib.plora_abi_version()}, this binding was written for {ABI_VERSION}: "
                       "rebuild it with `python pocket-engine_b200/build.py --force`")
@@ -562,8 +563,13 @@ class Loras:
         self._check(lib.plora_apply(self._h, C.byref(hook), C.byref(step), x, rows, y, ldy, int(f32_out), _P(stream)))
 
     def set_apply_mode(self, mode):
-        """0: apply() = shrink / expand pair with early activation loads; 1: one cluster kernel per layer."""
+        """1 (default): apply() = one cluster kernel per layer where the shapes fit; 0: the shrink / expand pair."""
         self._check(lib.plora_set_apply_mode(self._h, mode))
+
+    def set_early_x(self, on):
+        """The caller vouches that x is complete before the kernel right before apply() starts: apply() then reads
+        x ahead of its dependency wait. y is never read early."""
+        self._check(lib.plora_set_early_x(self._h, int(on)))
 
     def linear_bf16_fused(self, hook, step, x, w, rows, y, ldy, f32_out=False, stream=0):
         """y = x w^T + adapter term in one tensor-core kernel (bf16 x [rows, cols] and w [width, cols]); shrink first."""

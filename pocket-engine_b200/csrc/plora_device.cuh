@@ -6,55 +6,6 @@
 
 #include "../../include/plora.h"
 
-#ifdef PLORA_TRACE
-// Debug build only: time stamps from the global nanosecond timer. Two sinks: 16 slots per block of one launch
-// (g_plora_trace), or an append-only ring of (time, kernel tag, point, block) records across launches
-// (g_plora_ring, first word = write position).
-static __device__ unsigned long long* g_plora_trace = nullptr;
-static __device__ unsigned long long* g_plora_ring = nullptr;
-#ifndef PLORA_TRACE_TAG
-#define PLORA_TRACE_TAG 0
-#endif
-#define PLORA_TRACE_SETTER(name)                                                  \
-    extern "C" int name(unsigned long long* buf) {                                \
-        return (int)cudaMemcpyToSymbol(g_plora_trace, &buf, sizeof(buf));         \
-    }                                                                             \
-    extern "C" int name##_ring(unsigned long long* buf) {                         \
-        return (int)cudaMemcpyToSymbol(g_plora_ring, &buf, sizeof(buf));          \
-    }
-#define TRACE_K(tag, i)                                                                                  \
-    do {                                                                                                 \
-        if (threadIdx.x == 0 && (g_plora_trace || g_plora_ring)) {                                       \
-            unsigned long long gt_;                                                                      \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                                      \
-            const size_t lb_ = (size_t)blockIdx.z * gridDim.y * gridDim.x + blockIdx.y * gridDim.x + blockIdx.x; \
-            if (g_plora_trace) g_plora_trace[lb_ * 16 + (i)] = gt_;                                      \
-            if (g_plora_ring) {                                                                          \
-                const unsigned long long at_ = atomicAdd(g_plora_ring, 1ull);                            \
-                if (at_ < (1ull << 20)) {                                                                \
-                    g_plora_ring[1 + 2 * at_] = gt_;                                                     \
-                    g_plora_ring[2 + 2 * at_] = ((unsigned long long)(tag) << 56) | ((unsigned long long)(i) << 48) | lb_; \
-                }                                                                                        \
-            }                                                                                            \
-        }                                                                                                \
-    } while (0)
-#define TRACE(i) TRACE_K(PLORA_TRACE_TAG, i)
-#define TRACE_T(t, i)                                                                                    \
-    do {                                                                                                 \
-        if (threadIdx.x == (t) && g_plora_trace) {                                                       \
-            unsigned long long gt_;                                                                      \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                                      \
-            const size_t lb_ = (size_t)blockIdx.z * gridDim.y * gridDim.x + blockIdx.y * gridDim.x + blockIdx.x; \
-            g_plora_trace[lb_ * 16 + (i)] = gt_;                                                         \
-        }                                                                                                \
-    } while (0)
-#else
-#define PLORA_TRACE_SETTER(name)
-#define TRACE(i)
-#define TRACE_K(tag, i)
-#define TRACE_T(t, i)
-#endif
-
 namespace {
 
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
@@ -127,5 +78,42 @@ __device__ __forceinline__ void pdl_exit_idle() {
 }
 
 __device__ __forceinline__ uint4 lds16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+
+// 16 values per lane -> their 16 warp-wide sums in 16 shuffles; returns the sum of value (lane >> 1) & 15.
+__device__ __forceinline__ float reduce16(float (&v)[16], int lane) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float send = (lane & 16) ? v[i] : v[i + 8];
+        const float keep = (lane & 16) ? v[i + 8] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float send = (lane & 8) ? v[i] : v[i + 4];
+        const float keep = (lane & 8) ? v[i + 4] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const float send = (lane & 4) ? v[i] : v[i + 2];
+        const float keep = (lane & 4) ? v[i + 2] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+    {
+        const float send = (lane & 2) ? v[0] : v[1];
+        const float keep = (lane & 2) ? v[1] : v[0];
+        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+    }
+    return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
+
+// Hints that the 128-byte line holding `p` will be read soon: the line is brought into L2, no value is bound,
+// so it is safe on memory an earlier kernel may still be writing.
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// The same for `bytes` (a multiple of 16) from a 16-byte aligned address, as one request.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
 
 }  // namespace

@@ -23,7 +23,6 @@
 
 typedef __nv_bfloat16 bf16;
 
-PLORA_TRACE_SETTER(plora_trace_set_fp8)
 
 namespace {
 
@@ -247,7 +246,6 @@ __global__ void __launch_bounds__(224) plora_fp8_fused_kernel(const __grid_const
     const int nk = (K + F8_BK - 1) / F8_BK;
     pdl_wait();  // S, xq and the scales come from the kernels before
     pdl_trigger();
-    TRACE_T(0, 0);
     // columns of this tile inside each part: [p_lo, p_hi) relative to the part
     int p_lo[PLORA_MAX_PARTS], p_hi[PLORA_MAX_PARTS];
 #pragma unroll
@@ -365,7 +363,6 @@ __global__ void __launch_bounds__(224) plora_fp8_fused_kernel(const __grid_const
         const int row = m0 + et;
         // tokens of the tile sorted by slot (stable); slot 0 (no adapter) and rows past T first
         const int myslot = row < T ? segs[lay.tslot() + row] : 0;
-        TRACE_T(64, 2);
         s_slot[et] = myslot;
         for (int i = et; i < F8_BM * F8_DPITCH; i += 128) delta[i] = 0.f;
         epi_sync();
@@ -412,7 +409,6 @@ __global__ void __launch_bounds__(224) plora_fp8_fused_kernel(const __grid_const
             }
             if (et == 127) s_nunits = base + incl;
         }
-        TRACE_T(64, 3);
         mbar_arrive(&lists_bar);  // the ring's producer may start
         epi_sync();
         const int nunits = s_nunits;
@@ -423,7 +419,6 @@ __global__ void __launch_bounds__(224) plora_fp8_fused_kernel(const __grid_const
         for (int q = 0; q < parts.n; q++)
             if (n >= parts.off[q] && n < parts.off[q] + parts.rows[q]) p = q;
         const int cl = p >= 0 ? n - parts.off[p] - p_lo[p] : 0;  // column inside the tile's block of part p
-        TRACE_T(64, 4);
         bool alive = true;
         for (int u = half; u < nunits; u += 2) {
             const int q = u % F8_NQ;
@@ -479,10 +474,8 @@ __global__ void __launch_bounds__(224) plora_fp8_fused_kernel(const __grid_const
             if (lane == 0) mbar_arrive(&q_empty[q]);  // this warp is done with the unit's bytes
         }
         epi_sync();
-        TRACE_T(64, 5);
         // ---- epilogue: accumulator row by row out of tensor memory, scaled, plus the adapter term
         const bool ok = mbar_wait(&acc_bar, 0, status) && alive;
-        TRACE_T(64, 6);
         tc_fence_after();
         const int q4 = warp & 3;  // this warp's quarter of the 128 tensor-memory lanes
         const int lrow = q4 * 32 + lane;
@@ -521,7 +514,6 @@ __global__ void __launch_bounds__(224) plora_fp8_fused_kernel(const __grid_const
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, F8_BN);
-    TRACE_T(64, 7);
 }
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

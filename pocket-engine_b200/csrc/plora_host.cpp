@@ -32,6 +32,10 @@ int cuda_fail(const plora_t* h, const char* what, cudaError_t e) {
 
 int next_mult(int x, int m) { return (x + m - 1) / m * m; }
 
+// words the tile list [count, (start, len, slot) x cap_tiles] takes at the head of the step metadata, rounded up
+// so that the grouping output behind it (and with it every 32-word work item) starts on a 128-byte line
+size_t tile_words(const plora_t* h) { return (size_t)next_mult(1 + 3 * h->cap_tiles, 32); }
+
 // bf16 with round-to-nearest-even, as half::bf16::from_f32 does for finite values (src/lora.rs:141-145)
 inline uint16_t bf16_bits(float x) {
     uint32_t u;
@@ -190,7 +194,7 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
                           "; this library holds sm_100a code only");
         } else {
             h->sm_count = prop.multiProcessorCount;
-            size_t meta_words = (size_t)(1 + 3 * h->cap_tiles) + (size_t)h->seg.words();
+            size_t meta_words = tile_words(h) + (size_t)h->seg.words();
             check("alloc pool", cudaMalloc((void**)&h->pool, h->slot_bytes * (size_t)max_slots));
             check("alloc tables", cudaMalloc((void**)&h->tables, h->table_bytes));
             check("pinned tables", cudaMallocHost((void**)&h->host_tables, h->table_bytes));
@@ -204,15 +208,30 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
             check("alloc S", cudaMalloc((void**)&h->s, h->s_bytes));
             check("alloc meta", cudaMalloc((void**)&h->meta, meta_words * 4));
             check("pinned meta", cudaMallocHost((void**)&h->host_meta, (size_t)(1 + 3 * h->cap_tiles) * 4));
+            // launch records: at most one gather work item per slot plus one per 16 tokens, never more than tiles
+            h->rec_cap = std::min(h->cap_tiles, max_slots + max_tokens / PLORA_WORK_TOKENS) + 1;
+            const size_t rec_bytes = sizeof(PloraRec) * h->sites.size() * (size_t)h->rec_cap;
+            check("alloc launch records", cudaMalloc((void**)&h->recs, rec_bytes));
+            check("alloc layer widths", cudaMalloc((void**)&h->site_cols, 2 * h->sites.size() * sizeof(int32_t)));
+            if (rc == PLORA_OK) check("zero launch records", cudaMemset(h->recs, 0, rec_bytes));
             check("alloc status", cudaMalloc((void**)&h->status, 64));
             check("kernel attributes", plora_kernels_init(h->seg));
             if (rc == PLORA_OK && h->max_rank <= 128) h->mma_ok = plora_mma_init() == cudaSuccess;
             if (rc == PLORA_OK) h->site_ok = plora_site_init() == cudaSuccess;
+            std::vector<int32_t> info;
             for (auto& s : h->sites) {
-                int a, b, c, d2, e, total = 0;
+                int nsub = 1, total = 0;
                 for (auto& p : s.parts) total += p.rows;
-                s.cluster_ok = h->site_ok && plora_site_plan(s.cols, (int)s.parts.size(), h->max_rank, total, &a, &b, &c, &d2, &e) > 0;
+                s.cluster_ok = h->site_ok && plora_site_plan(s.cols, (int)s.parts.size(), h->max_rank, total, &nsub) > 0;
+                if (s.cluster_ok) {
+                    s.max_clusters = plora_site_max_clusters(s.cols, (int)s.parts.size(), h->max_rank, total);
+                    if (s.max_clusters < nsub) s.cluster_ok = false;
+                }
+                info.push_back(s.cols);
+                info.push_back(s.cluster_ok ? 8 * nsub : 0);
             }
+            if (rc == PLORA_OK)
+                check("upload layer widths", cudaMemcpy(h->site_cols, info.data(), info.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
             if (rc == PLORA_OK && h->max_rank <= 128) h->fp8_ok = plora_fp8_init(h->max_rank) == cudaSuccess;
             if (rc == PLORA_OK && h->mma_ok) h->gemm_ok = plora_gemm_init() == cudaSuccess;
             // runs of 64 or more contiguous tokens of one slot take the tensor-core tile kernels
@@ -220,6 +239,7 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
             if (const char* e = getenv("PLORA_PDL")) h->pdl = e[0] != '0';
             if (const char* e = getenv("PLORA_FUSED_TILE_ROWS")) h->fused_tile_rows = std::max(1, atoi(e));
             if (const char* e = getenv("PLORA_TILE_LATE")) h->tile_late = e[0] != '0';
+            if (const char* e = getenv("PLORA_PREFETCH_NEXT")) h->prefetch_next = e[0] != '0';
             if (rc == PLORA_OK) {
                 memset(h->host_tables, 0, h->table_bytes);
                 check("zero tables", cudaMemset(h->tables, 0, h->table_bytes));  // src/lora.rs:494
@@ -254,6 +274,8 @@ void plora_destroy(plora_t* h) {
         if (h->host_amaps) cudaFreeHost(h->host_amaps);
         if (h->s) cudaFree(h->s);
         if (h->meta) cudaFree(h->meta);
+        if (h->recs) cudaFree(h->recs);
+        if (h->site_cols) cudaFree(h->site_cols);
         if (h->host_meta) cudaFreeHost(h->host_meta);
         if (h->status) cudaFree(h->status);
         for (int p = 0; p < PLORA_XCHG_MAX_WORLD; p++)
@@ -279,6 +301,7 @@ uint64_t plora_slot_bytes(const plora_t* h) { return h ? (uint64_t)h->slot_bytes
 uint64_t plora_pool_ptr(const plora_t* h) { return h ? (uint64_t)(uintptr_t)h->pool : 0; }
 uint64_t plora_tables_ptr(const plora_t* h) { return h ? (uint64_t)(uintptr_t)h->tables : 0; }
 uint64_t plora_s_ptr(const plora_t* h) { return h ? (uint64_t)(uintptr_t)h->s : 0; }
+uint64_t plora_recs_ptr(const plora_t* h) { return h ? (uint64_t)(uintptr_t)h->recs : 0; }
 uint64_t plora_tiles_ptr(const plora_t* h) { return h ? (uint64_t)(uintptr_t)h->meta : 0; }
 int plora_max_lora_tiles(const plora_t* h) { return h ? h->cap_tiles : 0; }
 int plora_site_splits(const plora_t* h, int site) {
@@ -675,11 +698,13 @@ int plora_step_begin(plora_t* h, int max_tiles, int decode, void* stream, plora_
     if (!h || !out) return PLORA_ERR_ARG;
     if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
     if (max_tiles < 0) return fail(h, PLORA_ERR_ARG, "max_tiles is negative");
-    int32_t* segs = h->meta + (1 + 3 * h->cap_tiles);
+    int32_t* segs = h->meta + tile_words(h);
     h->pdl_armed = false;
     SegLayout lay = h->seg;
     if (decode) lay.run_min = 1 << 30;
     CU(h, "meta_group", plora_launch_meta_group(h->meta, segs, lay, h->status, as_stream(stream)));
+    CU(h, "meta_records", plora_launch_meta_records(segs, lay, h->tables, h->site_cols, (int)h->sites.size(), h->recs,
+                                                    h->rec_cap, as_stream(stream)));
     out->run_min = lay.run_min;
     out->pad_ = 0;
     out->tiles = (uint64_t)(uintptr_t)h->meta;
@@ -704,14 +729,17 @@ static int tile_split(const plora_t* h, int rows) {
 }
 
 static int shrink_impl(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, int rows, bool early,
-                       void* stream);
+                       bool early_x, void* stream);
 
 int plora_shrink(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, int rows, void* stream) {
-    return shrink_impl(h, hook, step, x, rows, false, stream);
+    return shrink_impl(h, hook, step, x, rows, false, false, stream);
 }
 
+// the launch records of a layer for this step
+static const PloraRec* recs_of(const plora_t* h, int site) { return h->recs + (size_t)site * (size_t)h->rec_cap; }
+
 static int shrink_impl(plora_t* h, const plora_hook* hook, const plora_step* step, uint64_t x, int rows, bool early,
-                       void* stream) {
+                       bool early_x, void* stream) {
     if (!h || !hook || !step) return PLORA_ERR_ARG;
     if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
     if (hook->site < 0 || hook->site >= (int)h->sites.size()) return fail(h, PLORA_ERR_ARG, "hook names no site");
@@ -725,17 +753,17 @@ static int shrink_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
     const bool pdl = h->pdl && h->pdl_armed;
     h->pdl_armed = true;
     CU(h, "shrink",
-       plora_launch_shrink((const void*)(uintptr_t)x, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
-                           h->seg, (const plora_desc*)(uintptr_t)hook->table, (float*)(uintptr_t)step->s,
-                           (size_t)(step->s_stride / 4), step->lds, site.kchunk, site.nsplit, work_cap,
-                           hook->parts * h->max_rank, h->status, pdl, early, as_stream(stream)));
+       plora_launch_shrink((const void*)(uintptr_t)x, site.cols, site.cols, recs_of(h, hook->site), h->rec_cap,
+                           (float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.kchunk, site.nsplit,
+                           work_cap, hook->parts * h->max_rank, h->status, pdl, early, early_x, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min)
         CU(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
                                    h->seg, (const plora_desc*)(uintptr_t)hook->table,
                                    h->amaps + (size_t)hook->site * (size_t)(h->max_slots + 1), (float*)(uintptr_t)step->s,
                                    (size_t)(step->s_stride / 4), step->lds, hook->parts * h->max_rank, std::max(1, rows / 64),
-                                   tile_split(h, rows), h->status, h->pdl, h->tile_late, as_stream(stream)));
+                                   tile_split(h, rows), h->status, h->pdl, h->tile_late && (!early || early_x),
+                                   as_stream(stream)));
     return PLORA_OK;
 }
 
@@ -763,7 +791,7 @@ int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint
     const SiteInfo& site = h->sites[(size_t)hook->site];
     if (!site.cluster_ok || h->apply_mode == 0) {
         // x and y are both older than the kernel before each launch: fetch them ahead of the dependency waits
-        int rc = shrink_impl(h, hook, step, x, rows, true, stream);
+        int rc = shrink_impl(h, hook, step, x, rows, true, h->early_x, stream);
         return rc != PLORA_OK ? rc : expand_impl(h, hook, step, rows, y, ldy, f32_out, false, true, stream);
     }
     if (rows < 0 || rows > h->max_tokens) return fail(h, PLORA_ERR_CAPACITY, "more rows than max_tokens");
@@ -776,9 +804,10 @@ int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint
     int total = 0;
     for (auto& p : site.parts) total += p.rows;
     CU(h, "site kernel",
-       plora_launch_site((const void*)(uintptr_t)x, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs, h->seg,
-                         (const plora_desc*)(uintptr_t)hook->table, (void*)(uintptr_t)y, ldy, f32_out, (int)site.parts.size(),
-                         h->max_rank, total, work_cap, h->status, pdl, as_stream(stream)));
+       plora_launch_site((const void*)(uintptr_t)x, site.cols, site.cols, recs_of(h, hook->site), h->rec_cap,
+                         h->prefetch_next && hook->site + 1 < (int)h->sites.size() ? recs_of(h, hook->site + 1) : nullptr,
+                         (void*)(uintptr_t)y, ldy, f32_out, (int)site.parts.size(), h->max_rank, total, work_cap,
+                         site.max_clusters, h->early_x, h->status, pdl, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min) {
         CU(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
@@ -828,8 +857,7 @@ static int expand_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
     h->pdl_armed = true;
     CU(h, "expand",
        plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds,
-                           reduced ? 1 : site.nsplit,
-                           (const int32_t*)(uintptr_t)step->segs, h->seg, (const plora_desc*)(uintptr_t)hook->table,
+                           reduced ? 1 : site.nsplit, recs_of(h, hook->site), h->rec_cap,
                            (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap, h->status, pdl,
                            early, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min)
@@ -877,9 +905,8 @@ static int gemm_layer(plora_t* h, const plora_hook* hook, const plora_step* step
     if (work_cap > 0)
         CU(h, "expand (tokens outside long runs)",
            plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
-                               (const int32_t*)(uintptr_t)step->segs, h->seg, (const plora_desc*)(uintptr_t)hook->table,
-                               (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap, h->status, h->pdl,
-                               false, as_stream(stream)));
+                               recs_of(h, hook->site), h->rec_cap, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
+                               hook->max_rows, work_cap, h->status, h->pdl, false, as_stream(stream)));
     return PLORA_OK;
 }
 
@@ -971,6 +998,12 @@ int plora_join(plora_t* h, void* main_stream, void* side_stream) {
 int plora_set_apply_mode(plora_t* h, int mode) {
     if (!h || mode < 0 || mode > 1) return PLORA_ERR_ARG;
     h->apply_mode = mode;
+    return PLORA_OK;
+}
+
+int plora_set_early_x(plora_t* h, int on) {
+    if (!h) return PLORA_ERR_ARG;
+    h->early_x = on != 0;
     return PLORA_OK;
 }
 

@@ -43,6 +43,24 @@ struct SegLayout {
     __host__ __device__ int words() const { return tslot() + max_tokens; }
 };
 
+// ---- per-step launch records: one per (layer, gather work item), written once per step by the records
+// kernel right after the grouping. A record carries everything a block of the few-token kernels needs about
+// its work item (the slot's resolved descriptor and the token rows), so the block makes one metadata fetch
+// and then issues its slab copies, instead of walking header -> work item -> descriptor table -> slab.
+// Record w of a layer is valid while cnt > 0; the records kernel ends the list with cnt == 0.
+#define PLORA_REC_TERM 128  // cleared records after the last valid one (>= the z extent of every grid that walks them)
+struct alignas(256) PloraRec {
+    int32_t cnt, slot, rank, cols;  // tokens (1..16), slot, stacked rows of A, the layer's input width
+    uint64_t a;
+    uint64_t b[PLORA_MAX_PARTS];
+    int32_t r[PLORA_MAX_PARTS], r_off[PLORA_MAX_PARTS], off[PLORA_MAX_PARTS], rows[PLORA_MAX_PARTS];
+    int32_t ntot, share;  // output columns over the targeted parts; columns per block of the layer's cluster kernel
+    int32_t tok[PLORA_WORK_TOKENS];
+    int32_t cat[PLORA_MAX_PARTS];  // where each targeted part starts when the targeted parts are laid end to end
+    int32_t pad2[12];
+};
+static_assert(sizeof(PloraRec) == 256, "one record is two 128-byte lines");
+
 struct alignas(64) PloraTmap {  // a CUtensorMap, opaque to the host registry
     unsigned char b[128];
 };
@@ -64,6 +82,7 @@ struct SiteInfo {
     // K-split of the shrink: fixed per site so results do not depend on the batch
     int kchunk = 0, nsplit = 1;
     bool cluster_ok = false;  // the one-kernel-per-layer cluster path fits this layer's shapes
+    int max_clusters = 0;     // clusters of that kernel the device runs at once
 };
 
 struct SiteData {  // src/lora.rs:74-79
@@ -102,7 +121,10 @@ struct plora {
     size_t s_bytes = 0, s_stride = 0;
     int lds = 0, nsplit_max = 1;
     int32_t* meta = nullptr;  // device: tile words, then segs
+    PloraRec* recs = nullptr;  // device: [sites][rec_cap] launch records of the step
+    int rec_cap = 0;
     int32_t* host_meta = nullptr;  // pinned staging for plora_meta_upload
+    int32_t* site_cols = nullptr;  // device: per layer {input width, column pieces of the cluster kernel} (for the launch records)
     int cap_tiles = 0;
     SegLayout seg;
     int* status = nullptr;  // device status word
@@ -119,7 +141,9 @@ struct plora {
     uint8_t* xchg_peer[PLORA_XCHG_MAX_WORLD] = {};   // base of every rank's allocation as mapped in this process
     bool xchg_ipc[PLORA_XCHG_MAX_WORLD] = {};        // opened from an IPC handle (closed on destroy)
     int tile_split_force = 0;  // plora_set_tile_split: 0 = chosen per launch
-    int apply_mode = 0;     // plora_apply: 0 = shrink/expand pair with early loads, 1 = one cluster kernel per layer
+    int apply_mode = 1;     // plora_apply: 0 = shrink / expand pair, 1 = one cluster kernel per layer where it fits
+    bool early_x = false;   // plora_set_early_x: plora_apply may read x ahead of its dependency wait
+    bool prefetch_next = true;  // the cluster kernel asks L2 for the next layer's slabs of its work item (PLORA_PREFETCH_NEXT=0: off)
     bool site_ok = false;   // the cluster kernel's attributes were set
     bool fp8_ok = false;    // the fused FP8 layer can run
     bool gemm_ok = false;   // the one-kernel layer for prefill-sized steps can run
@@ -170,13 +194,16 @@ cudaError_t plora_launch_meta_tiles(const int32_t* cu, const int32_t* seq_slot, 
                                     int cap_tiles, int* status, cudaStream_t st);
 cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status,
                                     cudaStream_t st);
+// site_info: per layer {input width, blocks that share a work item's output columns in the cluster kernel (0: none)}
+cudaError_t plora_launch_meta_records(const int32_t* segs, SegLayout lay, const plora_desc* tables, const int32_t* site_info,
+                                      int n_sites, PloraRec* recs, int rec_cap, cudaStream_t st);
 cudaError_t plora_kernels_init(const SegLayout& lay);
 cudaError_t plora_site_init();
-size_t plora_site_plan(int K, int parts, int max_rank, int total_rows, int* kchunk, int* rmax, int* a_bytes,
-                       int* x_bytes, int* b_bytes);
-cudaError_t plora_launch_site(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay, const plora_desc* table,
+size_t plora_site_plan(int K, int parts, int max_rank, int total_rows, int* nsub);
+int plora_site_max_clusters(int K, int parts, int max_rank, int total_rows);
+cudaError_t plora_launch_site(const void* x, int ldx, int K, const PloraRec* recs, int rec_cap, const PloraRec* next_recs,
                               void* y, int ldy, int f32_out, int parts, int max_rank, int total_rows, int work_cap,
-                              int* status, bool pdl, cudaStream_t st);
+                              int max_clusters, bool early_x, int* status, bool pdl, cudaStream_t st);
 cudaError_t plora_mma_init();
 cudaError_t plora_fp8_init(int max_rank);
 cudaError_t plora_launch_fp8_quant(const void* x, int rows, int ldx, int K, void* xq, float* st, cudaStream_t stream);
@@ -203,10 +230,11 @@ cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int l
                                     const int32_t* segs, SegLayout lay, const plora_desc* table, void* y, int ldy,
                                     int f32_out, int parts, const int* part_off, const int* part_rows, int rows_total,
                                     int max_rows, int tile_cap, int* status, bool pdl, cudaStream_t st);
-cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay,
-                                const plora_desc* table, float* S, size_t s_stride_elems, int lds, int kchunk,
-                                int nsplit, int work_cap, int max_rank_total, int* status, bool pdl, bool early,
-                                cudaStream_t st);
-cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, int nsplit, const int32_t* segs,
-                                SegLayout lay, const plora_desc* table, void* y, int ldy, int f32_out, int parts,
-                                int max_rows, int work_cap, int* status, bool pdl, bool early, cudaStream_t st);
+// early: dependents are released at kernel start and slabs are requested ahead of the dependency wait (used by
+// plora_apply, whose kernels follow one another); early_x: x too may be read ahead of the wait
+cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const PloraRec* recs, int rec_cap, float* S,
+                                size_t s_stride_elems, int lds, int kchunk, int nsplit, int work_cap, int max_rank_total,
+                                int* status, bool pdl, bool early, bool early_x, cudaStream_t st);
+cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, int nsplit, const PloraRec* recs,
+                                int rec_cap, void* y, int ldy, int f32_out, int parts, int max_rows, int work_cap,
+                                int* status, bool pdl, bool early, cudaStream_t st);

@@ -15,7 +15,6 @@
 
 typedef __nv_bfloat16 bf16;
 
-PLORA_TRACE_SETTER(plora_trace_set)
 
 namespace {
 
@@ -297,54 +296,80 @@ __global__ void __launch_bounds__(1024) plora_meta_group_kernel(const int* __res
 }
 
 // ---------------------------------------------------------------------------------------------
-// 16 values per lane -> their 16 warp-wide sums in 16 shuffles; returns the sum of value (lane >> 1) & 15.
-__device__ __forceinline__ float reduce16(float (&v)[16], int lane) {
+// Launch records of the step: block `site` resolves every gather work item against that layer's descriptor
+// table, once, so that the kernels of the layers make one metadata fetch per block. The list of a layer ends
+// with records whose cnt is 0.
+__global__ void __launch_bounds__(256) plora_meta_records_kernel(const int* __restrict__ segs, SegLayout lay,
+                                                                  const plora_desc* __restrict__ tables,
+                                                                  const int* __restrict__ site_cols, PloraRec* __restrict__ recs,
+                                                                  int rec_cap) {
+    const int site = blockIdx.x;
+    pdl_wait();  // the grouping kernel's output
+    const int n_work = min(segs[SEG_N_WORK], rec_cap - 1);
+    const plora_desc* table = tables + (size_t)site * (size_t)(lay.max_slots + 1);
+    PloraRec* out = recs + (size_t)site * (size_t)rec_cap;
+    const int cols = site_cols[2 * site], pieces = site_cols[2 * site + 1];
+    const int end = min(rec_cap, n_work + PLORA_REC_TERM);
+    for (int w = threadIdx.x; w < end; w += blockDim.x) {
+        uint4* o = reinterpret_cast<uint4*>(out + w);
+        if (w >= n_work) {
+            o[0] = make_uint4(0u, 0u, 0u, (uint32_t)cols);
+            continue;
+        }
+        const uint4* work = reinterpret_cast<const uint4*>(segs + lay.work() + PLORA_WORK_WORDS * w);
+        const uint4 head = work[0];  // slot, perm start, count, 0
+        const int slot = (int)head.x;
+        const uint4* d = reinterpret_cast<const uint4*>(table + slot);  // 112 bytes: a, b[4], rank, r, r_off, off, rows
+        uint4 dv[7];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const float send = (lane & 16) ? v[i] : v[i + 8];
-        const float keep = (lane & 16) ? v[i + 8] : v[i];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-    }
+        for (int i = 0; i < 7; i++) dv[i] = d[i];
+        // Desc: a | b0 b1 | b2 b3 | rank r0 r1 r2 | r3 ro0 ro1 ro2 | ro3 o0 o1 o2 | o3 rows0 rows1 rows2 | rows3 pad
+        const uint32_t* dw = reinterpret_cast<const uint32_t*>(dv);
+        o[0] = make_uint4(head.z, head.x, dw[10], (uint32_t)cols);  // cnt, slot, rank, cols
+        o[1] = make_uint4(dw[0], dw[1], dw[2], dw[3]);              // a, b[0]
+        o[2] = make_uint4(dw[4], dw[5], dw[6], dw[7]);              // b[1], b[2]
+        o[3] = make_uint4(dw[8], dw[9], dw[11], dw[12]);            // b[3], r[0], r[1]
+        o[4] = make_uint4(dw[13], dw[14], dw[15], dw[16]);          // r[2], r[3], r_off[0], r_off[1]
+        o[5] = make_uint4(dw[17], dw[18], dw[19], dw[20]);          // r_off[2], r_off[3], off[0], off[1]
+        o[6] = make_uint4(dw[21], dw[22], dw[23], dw[24]);          // off[2], off[3], rows[0], rows[1]
+        // the slot's output columns over its targeted parts laid end to end, and the even share of them that
+        // one block of the layer's cluster kernel expands
+        uint32_t cat[PLORA_MAX_PARTS], ntot = 0;
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const float send = (lane & 8) ? v[i] : v[i + 4];
-        const float keep = (lane & 8) ? v[i + 4] : v[i];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+        for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+            cat[p] = ntot;
+            if ((int)dw[11 + p] > 0) ntot += dw[23 + p];
+        }
+        const uint32_t share = pieces > 0 ? (((ntot + pieces - 1) / pieces + 1) & ~1u) : 0u;
+        o[7] = make_uint4(dw[25], dw[26], ntot, share);             // rows[2], rows[3], ntot, share
+        o[8] = work[1];                                             // the token rows
+        o[9] = work[2];
+        o[10] = work[3];
+        o[11] = work[4];
+        o[12] = make_uint4(cat[0], cat[1], cat[2], cat[3]);
     }
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-        const float send = (lane & 4) ? v[i] : v[i + 2];
-        const float keep = (lane & 4) ? v[i + 2] : v[i];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-    }
-    {
-        const float send = (lane & 2) ? v[0] : v[1];
-        const float keep = (lane & 2) ? v[1] : v[0];
-        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
-    }
-    return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
 }
 
 // Shrink over gather work items. Grid (K-splits x row tiles, 1, work items); 128 threads. A work item is up
-// to 16 tokens of one slot, described by one 128-byte record. The block's rows of the slot's stacked A (one
+// to 16 tokens of one slot, described by one launch record. The block's rows of the slot's stacked A (one
 // K-chunk wide) arrive in shared memory by bulk async copies issued before the dependency wait; the tokens'
 // x chunks follow right after it. Each warp takes 4 of every 16 rows and 4 tokens at a time, its lanes 8
 // inputs each per 256-wide step; sums cross the warp by shuffles. Every (token, row, split) is written
 // exactly once.
 __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __restrict__ X, int ldx, int K,
-                                                                   const int* __restrict__ segs, SegLayout lay,
-                                                                   const plora_desc* __restrict__ table,
+                                                                   const PloraRec* __restrict__ recs, int rec_cap,
                                                                    float* __restrict__ S, size_t s_stride, int lds,
-                                                                   int kchunk, int rps, int rt_max, int early,
+                                                                   int kchunk, int rps, int rt_max, int early, int early_x,
                                                                    int* __restrict__ status) {
-    // early != 0: the caller vouches that x was not written by the kernel right before this one, so x is
-    // fetched and the partial sums computed before the dependency wait; only the stores into S (which the
-    // expand before may still be reading) come after it.
+    // early != 0: dependents are released at kernel start (every store of the path comes after a wait).
+    // early_x != 0: the caller vouches that x is older than every kernel still in flight, so x is fetched and
+    // the partial sums computed before the dependency wait; only the stores into S (which the expand before may
+    // still be reading) come after it.
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ __align__(8) uint64_t bars[2];
-    __shared__ int stok[PLORA_WORK_TOKENS];
+    __shared__ PloraRec srec;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_work = segs[SEG_N_WORK];
+    if (early) pdl_trigger();
     if (threadIdx.x == 0) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
@@ -352,54 +377,49 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
     }
     bool waited = false;
     uint32_t phase = 0;
-    // In early mode the next kernels may start their own prologues at once: before their waits they touch only
-    // slabs, the step's grouping and activations that no kernel of this path writes; every store of the path
-    // comes after a wait, and every grid still waits for its predecessor before it completes.
-    if (early) pdl_trigger();
-    // the grid's z extent is capped: a block walks the work items z, z + gridDim.z, ...
-    for (int w = blockIdx.z; w < n_work; w += gridDim.z) {
-    const int* work = segs + lay.work() + PLORA_WORK_WORDS * w;
-    // independent loads first: the record's head, this lane's token
-    const int slot = work[0], cnt = work[2];
-    const int mytok = work[4 + (lane & 15)];
-    TRACE_K(1, 0);
-    TRACE_K(1, 1);
-    const plora_desc& d = table[slot];
-    const int rank = d.rank;
     const int split = blockIdx.x / rt_max, rt = blockIdx.x - split * rt_max;
     const int row0 = rt * rps;
-    if (row0 >= rank) continue;
-    TRACE_K(1, 2);
-    const int rows = min(rps, rank - row0);
     const int k0 = split * kchunk, klen = min(kchunk, K - k0);
     const uint32_t kbytes = (uint32_t)klen * 2u;
+    // the grid's z extent is capped: a block walks the work items z, z + gridDim.z, ...
+    for (int w = blockIdx.z; w < rec_cap; w += gridDim.z) {
+    if (threadIdx.x < 12) reinterpret_cast<uint4*>(&srec)[threadIdx.x] = __ldg(reinterpret_cast<const uint4*>(recs + w) + threadIdx.x);
+    __syncthreads();
+    const int cnt = srec.cnt, rank = srec.rank;
+    if (cnt == 0) break;
+    if (row0 >= rank) {
+        __syncthreads();
+        continue;
+    }
+    const int rows = min(rps, rank - row0);
     unsigned char* As = dsm;
     unsigned char* Xs = dsm + (size_t)rps * kchunk * 2;
-    if (threadIdx.x < PLORA_WORK_TOKENS) stok[threadIdx.x] = mytok;
-    __syncthreads();
     if (warp == 0) {
-        const bf16* A = reinterpret_cast<const bf16*>(d.a) + (size_t)row0 * K + k0;
+        const bf16* A = reinterpret_cast<const bf16*>(srec.a) + (size_t)row0 * K + k0;
         if (lane == 0) mbar_expect_tx(&bars[0], (uint32_t)rows * kbytes);
         __syncwarp();
         for (int r = lane; r < rows; r += 32) bulk_g2s(As + (size_t)r * kbytes, A + (size_t)r * K, kbytes, &bars[0]);
+    } else if (!waited && !early_x) {
+        // hint only: the x lines this block will copy once the kernel before is done
+        const int lines = (int)((kbytes + 127) / 128);
+        for (int i = threadIdx.x - 32; i < cnt * lines; i += 96) {
+            const int t = i / lines, l = i - t * lines;
+            prefetch_l2(reinterpret_cast<const unsigned char*>(X + (size_t)srec.tok[t] * ldx + k0) + (size_t)l * 128);
+        }
     }
-    TRACE_K(1, 3);
-    if (!early && !waited) {
+    if (!early_x && !waited) {
         pdl_wait();
-        pdl_trigger();
+        if (!early) pdl_trigger();
         waited = true;
     }
-    TRACE_K(1, 4);
     if (warp == 0) {
         if (lane == 0) mbar_expect_tx(&bars[1], (uint32_t)cnt * kbytes);
         __syncwarp();
-        if (lane < cnt) bulk_g2s(Xs + (size_t)lane * kbytes, X + (size_t)mytok * ldx + k0, kbytes, &bars[1]);
+        if (lane < cnt) bulk_g2s(Xs + (size_t)lane * kbytes, X + (size_t)srec.tok[lane] * ldx + k0, kbytes, &bars[1]);
     }
     if (!mbar_wait(&bars[0], phase, status)) return;
-    TRACE_K(1, 5);
     if (!mbar_wait(&bars[1], phase, status)) return;
     phase ^= 1;
-    TRACE_K(1, 6);
     float* Sout = S + (size_t)split * s_stride;
     float res[PLORA_WORK_TOKENS / 4];  // rows == 16: one 4-row group per warp, one value per token pass
 #pragma unroll
@@ -432,16 +452,15 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
     }
     if (!waited) {
         pdl_wait();
-        pdl_trigger();
+        if (!early) pdl_trigger();
         waited = true;
     }
     if ((lane & 1) == 0) {
         const int i = lane >> 1, r = i >> 2, t = i & 3;
 #pragma unroll
         for (int tq = 0; tq < PLORA_WORK_TOKENS / 4; tq++)
-            if (4 * tq + t < cnt) Sout[(size_t)stok[4 * tq + t] * lds + row0 + warp * 4 + r] = res[tq];
+            if (4 * tq + t < cnt) Sout[(size_t)srec.tok[4 * tq + t] * lds + row0 + warp * 4 + r] = res[tq];
     }
-    TRACE_K(1, 7);
     __syncthreads();  // shared memory is reused by the next work item
     }
     if (!waited) pdl_exit_idle();
@@ -449,9 +468,9 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
 
 // Expand over gather work items. Grid (column blocks, parts, work items); 128 threads, two adjacent output
 // columns each. The block's rows of B arrive in shared memory by one bulk async copy issued before the
-// dependency wait. After it, the work item's S rows (K-split partials, all in flight together, added in
-// split order) go to shared memory while the y values are already on their way; every thread then walks
-// its two rows of B once per group of 4 tokens and writes y back.
+// dependency wait, together with L2 prefetch hints for its y lines. After the wait, the work item's S rows
+// (K-split partials, all in flight together, added in split order) go to shared memory while the y values are
+// on their way; every thread then walks its two rows of B once per group of 4 tokens and writes y back.
 #define EXP_SPAD 12  // floats per 8-wide piece of an S row in shared memory (conflict-free for rotated reads)
 
 // PASSES: whether the tile buffer is smaller than a block's columns at the maximum rank. NH: column pairs per
@@ -460,37 +479,34 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
 template <bool PASSES, int NH>
 __global__ void __launch_bounds__(256 / NH, 4 * NH) plora_expand_gather_kernel(const float* __restrict__ S, size_t s_stride,
                                                                       int lds, int nsplit,
-                                                                      const int* __restrict__ segs, SegLayout lay,
-                                                                      const plora_desc* __restrict__ table, void* Y,
-                                                                      int ldy, int f32_out, int nc, int bs_bytes,
+                                                                      const PloraRec* __restrict__ recs, int rec_cap,
+                                                                      void* Y, int ldy, int f32_out, int nc, int bs_bytes,
                                                                       int early, int* __restrict__ status) {
-    // early != 0: the caller vouches that y was not written by the kernel right before this one, so the
-    // first tokens' y is fetched before the dependency wait.
+    // early != 0: dependents are released at kernel start. No value of y is bound before the dependency wait
+    // (the kernel before, the layer's matrix multiply, may still be writing it): only L2 prefetch hints.
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ __align__(8) uint64_t bar;
-    __shared__ int stok[PLORA_WORK_TOKENS];
-    const int n_work = segs[SEG_N_WORK];
+    __shared__ PloraRec srec;
+    if (early) pdl_trigger();
     if (threadIdx.x == 0) {
         mbar_init(&bar, 1);
         mbar_fence_init();
     }
     bool waited = false;
     uint32_t phase = 0;
-    // In early mode the next kernel may start its own prologue at once (see the shrink).
-    if (early) pdl_trigger();
+    const int esize = f32_out ? 4 : 2;
     // the grid's z extent is capped: a block walks the work items z, z + gridDim.z, ...
-    for (int w = blockIdx.z; w < n_work; w += gridDim.z) {
-    const int* work = segs + lay.work() + PLORA_WORK_WORDS * w;
-    const int slot = work[0], cnt = work[2];
-    const int mytok = work[4 + (threadIdx.x & 15)];
-    TRACE_K(2, 0);
-    TRACE_K(2, 1);
-    const plora_desc& d = table[slot];
-    const int p = blockIdx.y, r = d.r[p];
-    if (r == 0) continue;
-    TRACE_K(2, 2);
-    const int rows = d.rows[p], c0 = blockIdx.x * nc;
-    if (c0 >= rows) continue;
+    for (int w = blockIdx.z; w < rec_cap; w += gridDim.z) {
+    if (threadIdx.x < 12) reinterpret_cast<uint4*>(&srec)[threadIdx.x] = __ldg(reinterpret_cast<const uint4*>(recs + w) + threadIdx.x);
+    __syncthreads();
+    const int cnt = srec.cnt;
+    if (cnt == 0) break;
+    const int p = blockIdx.y, r = srec.r[p];
+    const int rows = srec.rows[p], c0 = blockIdx.x * nc;
+    if (r == 0 || c0 >= rows) {
+        __syncthreads();
+        continue;
+    }
     const int ncols_all = min(nc, rows - c0);
     // The tile buffer holds bs_bytes of B: all the block's columns for ranks up to bs_bytes / (2 nc), fewer
     // columns per pass (a multiple of 32) for higher ranks, so that a high maximum rank does not cost every
@@ -499,21 +515,28 @@ __global__ void __launch_bounds__(256 / NH, 4 * NH) plora_expand_gather_kernel(c
     int ncols = min(sub, ncols_all);
     unsigned char* Bs = dsm;
     float* ss = reinterpret_cast<float*>(dsm + bs_bytes);
+    const bf16* Bp = reinterpret_cast<const bf16*>(srec.b[p]);
     if (threadIdx.x == 0) {
         const uint32_t bytes = (uint32_t)ncols * (uint32_t)r * 2u;
         mbar_expect_tx(&bar, bytes);
-        bulk_g2s(Bs, reinterpret_cast<const bf16*>(d.b[p]) + (size_t)c0 * r, bytes, &bar);
+        bulk_g2s(Bs, Bp + (size_t)c0 * r, bytes, &bar);
     }
-    if (threadIdx.x < PLORA_WORK_TOKENS) stok[threadIdx.x] = mytok;
-    const int r_off = d.r_off[p];
+    const int r_off = srec.r_off[p];
     const int c = 2 * threadIdx.x;       // the thread's first column pair; pair h is h * HALF columns further
     const int HALF = 2 * blockDim.x;
-    size_t ycol = (size_t)d.off[p] + c0 + c;
-    TRACE_K(2, 3);
-    __syncthreads();
-    if (!early && !waited) {
+    size_t ycol = (size_t)srec.off[p] + c0 + c;
+    if (!waited) {
+        // hints for the block's y lines, then the dependency wait
+        const size_t len = (size_t)ncols_all * esize;
+        const int lines = (int)((len + 127) / 128) + 1;
+        for (int i = threadIdx.x; i < cnt * lines; i += blockDim.x) {
+            const int t = i / lines, l = i - t * lines;
+            const size_t start = ((size_t)srec.tok[t] * ldy + srec.off[p] + c0) * esize;
+            const size_t at = (start & ~(size_t)127) + (size_t)l * 128;
+            if (at < start + len) prefetch_l2(reinterpret_cast<const unsigned char*>(Y) + at);
+        }
         pdl_wait();
-        pdl_trigger();
+        if (!early) pdl_trigger();
         waited = true;
     }
     // y of a group of 4 tokens, all of the thread's pairs
@@ -525,7 +548,7 @@ __global__ void __launch_bounds__(256 / NH, 4 * NH) plora_expand_gather_kernel(c
 #pragma unroll
                 for (int t = 0; t < 4; t++) {
                     if (tg + t < cnt) {
-                        const size_t at = (size_t)stok[tg + t] * ldy + ycol + h * HALF;
+                        const size_t at = (size_t)srec.tok[tg + t] * ldy + ycol + h * HALF;
                         if (f32_out) yv[t][h] = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(Y) + at);
                         else yv[t][h] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(Y) + at));
                     }
@@ -535,16 +558,10 @@ __global__ void __launch_bounds__(256 / NH, 4 * NH) plora_expand_gather_kernel(c
     };
     // y of the first token group: on its way before anything else is waited for
     load_y(0);
-    if (!waited) {
-        pdl_wait();
-        pdl_trigger();
-        waited = true;
-    }
-    TRACE_K(2, 4);
     const int P = r >> 3;  // 16-byte pieces per row of B
     for (int i = threadIdx.x; i < cnt * r; i += blockDim.x) {
         const int t = i / r, j = i - t * r;
-        const float* sp = S + (size_t)stok[t] * lds + r_off + j;
+        const float* sp = S + (size_t)srec.tok[t] * lds + r_off + j;
         float acc = 0.f;
         for (int s0 = 0; s0 < nsplit; s0 += 8) {
             float v[8];
@@ -557,7 +574,6 @@ __global__ void __launch_bounds__(256 / NH, 4 * NH) plora_expand_gather_kernel(c
         ss[t * P * EXP_SPAD + (j >> 3) * EXP_SPAD + (j & 7)] = acc;
     }
     __syncthreads();
-    TRACE_K(2, 5);
     for (int cs = 0; cs < ncols_all; cs += sub) {
     if (cs > 0) {
         // the next columns of the block: the tile buffer is free once every thread is through the pass before
@@ -566,14 +582,13 @@ __global__ void __launch_bounds__(256 / NH, 4 * NH) plora_expand_gather_kernel(c
         if (threadIdx.x == 0) {
             const uint32_t bytes = (uint32_t)ncols * (uint32_t)r * 2u;
             mbar_expect_tx(&bar, bytes);
-            bulk_g2s(Bs, reinterpret_cast<const bf16*>(d.b[p]) + (size_t)(c0 + cs) * r, bytes, &bar);
+            bulk_g2s(Bs, Bp + (size_t)(c0 + cs) * r, bytes, &bar);
         }
-        ycol = (size_t)d.off[p] + c0 + cs + c;
+        ycol = (size_t)srec.off[p] + c0 + cs + c;
         load_y(0);
     }
     if (!mbar_wait(&bar, phase, status)) return;
     phase ^= 1;
-    TRACE_K(2, 6);
     const int rot = (P >= 8 ? threadIdx.x : threadIdx.x >> 1) % P;
     const int sstride = P * EXP_SPAD;
     for (int tg = 0; tg < cnt; tg += 4) {
@@ -610,7 +625,7 @@ __global__ void __launch_bounds__(256 / NH, 4 * NH) plora_expand_gather_kernel(c
 #pragma unroll
             for (int t = 0; t < 4; t++) {
                 if (tg + t < cnt) {
-                    const size_t at = (size_t)stok[tg + t] * ldy + ycol + h * HALF;
+                    const size_t at = (size_t)srec.tok[tg + t] * ldy + ycol + h * HALF;
                     if (f32_out)
                         *reinterpret_cast<float2*>(reinterpret_cast<float*>(Y) + at) =
                             make_float2(yv[t][h].x + acc[t][0], yv[t][h].y + acc[t][1]);
@@ -622,7 +637,6 @@ __global__ void __launch_bounds__(256 / NH, 4 * NH) plora_expand_gather_kernel(c
         }
     }
     }
-    TRACE_K(2, 7);
     __syncthreads();  // shared memory is reused by the next work item
     }
     if (!waited) pdl_exit_idle();
@@ -688,6 +702,12 @@ cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t 
 }
 }  // namespace
 
+cudaError_t plora_launch_meta_records(const int32_t* segs, SegLayout lay, const plora_desc* tables, const int32_t* site_cols,
+                                      int n_sites, PloraRec* recs, int rec_cap, cudaStream_t st) {
+    return launch_pdl(plora_meta_records_kernel, dim3((unsigned)n_sites), dim3(256), 0, st, true, segs, lay, tables, site_cols,
+                      recs, rec_cap);
+}
+
 #define PLORA_GRID_Z_CAP 64  // blocks along the work-item axis; more work items are walked in a loop
 
 // rows of A per block: 16 (one 4-row group per warp), so that a slot's rows spread over many blocks and
@@ -697,16 +717,15 @@ int plora_shrink_rps(int kchunk) {
     return 16;
 }
 
-cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay,
-                                const plora_desc* table, float* S, size_t s_stride_elems, int lds, int kchunk,
-                                int nsplit, int work_cap, int max_rank_total, int* status, bool pdl, bool early,
-                                cudaStream_t st) {
+cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const PloraRec* recs, int rec_cap, float* S,
+                                size_t s_stride_elems, int lds, int kchunk, int nsplit, int work_cap, int max_rank_total,
+                                int* status, bool pdl, bool early, bool early_x, cudaStream_t st) {
     const int rps = plora_shrink_rps(kchunk);
     const int rt_max = (max_rank_total + rps - 1) / rps;
     dim3 grid((unsigned)(nsplit * rt_max), 1, (unsigned)(work_cap < PLORA_GRID_Z_CAP ? work_cap : PLORA_GRID_Z_CAP));
     const size_t smem = (size_t)(rps + PLORA_WORK_TOKENS) * (size_t)kchunk * 2;
     return launch_pdl(plora_shrink_gather_kernel, grid, dim3(128), smem, st, pdl, reinterpret_cast<const bf16*>(x), ldx,
-                      K, segs, lay, table, S, s_stride_elems, lds, kchunk, rps, rt_max, early ? 1 : 0, status);
+                      K, recs, rec_cap, S, s_stride_elems, lds, kchunk, rps, rt_max, early ? 1 : 0, early_x ? 1 : 0, status);
 }
 
 // output columns per block (two per thread): 512 for wide layers so the grid stays near one wave, 256
@@ -717,9 +736,9 @@ int plora_expand_nc(int max_rank, int max_rows) {
     return nc;
 }
 
-cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, int nsplit, const int32_t* segs,
-                                SegLayout lay, const plora_desc* table, void* y, int ldy, int f32_out, int parts,
-                                int max_rows, int work_cap, int* status, bool pdl, bool early, cudaStream_t st) {
+cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, int nsplit, const PloraRec* recs,
+                                int rec_cap, void* y, int ldy, int f32_out, int parts, int max_rows, int work_cap,
+                                int* status, bool pdl, bool early, cudaStream_t st) {
     const int max_rank = lds / PLORA_MAX_PARTS;
     const int nc = plora_expand_nc(max_rank, max_rows);
     // tile buffer: all of a block's columns at the maximum rank, up to 32 KB; blocks of higher-rank slots take
@@ -737,7 +756,7 @@ cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, 
     if (per_sm > 8) per_sm = 8;
     const int nh = nc >= 512 && (long long)grid.x * grid.y * grid.z <= (long long)per_sm * g_sms ? 2 : 1;
     const dim3 block((unsigned)(nc / (2 * nh)));
-#define PLORA_EXPAND_ARGS S, s_stride_elems, lds, nsplit, segs, lay, table, y, ldy, f32_out, nc, bs_bytes, early ? 1 : 0, status
+#define PLORA_EXPAND_ARGS S, s_stride_elems, lds, nsplit, recs, rec_cap, y, ldy, f32_out, nc, bs_bytes, early ? 1 : 0, status
     if (nh == 2)
         return passes ? launch_pdl(plora_expand_gather_kernel<true, 2>, grid, block, smem, st, pdl, PLORA_EXPAND_ARGS)
                       : launch_pdl(plora_expand_gather_kernel<false, 2>, grid, block, smem, st, pdl, PLORA_EXPAND_ARGS);

@@ -18,7 +18,6 @@
 
 typedef __nv_bfloat16 bf16;
 
-PLORA_TRACE_SETTER(plora_trace_set_mma)
 
 namespace {
 
@@ -381,7 +380,6 @@ __global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __re
     const int cb0 = blockIdx.x * nb_per_cta;
     if (cb0 * 128 >= rows) return pdl_exit_idle();
     const int nblk = min(nb_per_cta, (rows - cb0 * 128 + 127) / 128);
-    TRACE(0);
     const int tid = threadIdx.x, warp = tid >> 5;
     unsigned char* Ahi = dsm;
     unsigned char* Alo = dsm + op_bytes;
@@ -410,7 +408,6 @@ __global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __re
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
     pdl_wait();
-    TRACE(1);
     pdl_trigger();
 
     // this thread's token row of S, split into a bf16 high part and the bf16 of what is left
@@ -459,7 +456,6 @@ __global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __re
         }
     }
     const uint32_t idesc = umma_idesc_bf16(MMA_M, 128);
-    TRACE(2);
     const int lane = tid & 31;
     // Epilogue layout: the accumulator leaves tensor memory one token row per thread, is transposed through a
     // warp-private shared-memory tile, and meets y with one 128-byte (bf16) or 256-byte (f32) row segment per
@@ -476,7 +472,6 @@ __global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __re
         cp_async_wait<1>();  // everything but the block just requested has landed
         fence_async_smem();
         __syncthreads();
-        if (nb == 0) TRACE(3);
         if (warp == 0) {
             if (elect_one()) {
                 tc_fence_after();
@@ -496,21 +491,17 @@ __global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __re
         const size_t yblk = ybase + (size_t)cb * 128;
         uint32_t yb0[32], yb1[32];
         float2 yf[32];
-        if (nb == 0) TRACE(4);
         if (F32) {
             load_rows_f32(yf, reinterpret_cast<const float*>(Y) + yblk, ldy, nrows, 2 * lane < ncols);
         } else {
             load_rows_bf16(yb0, reinterpret_cast<const bf16*>(Y) + yblk, ldy, nrows, 2 * lane < ncols);
             load_rows_bf16(yb1, reinterpret_cast<const bf16*>(Y) + yblk + 64, ldy, nrows, 64 + 2 * lane < ncols);
         }
-        if (nb == 0) TRACE(8);
         ok = mbar_wait(&done, nb & 1, status);
-        if (nb == 0) TRACE(9);
         if (!__syncthreads_and(ok)) {
             ok = false;
             break;
         }
-        if (nb == 0) TRACE(5);
         tc_fence_after();
 #pragma unroll
         for (int ch = 0; ch < 2; ch++) {
@@ -552,13 +543,11 @@ __global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __re
         }
         tc_fence_before();
         __syncthreads();  // the accumulator and this B buffer are free again
-        if (nb == 0) TRACE(6);
     }
     cp_async_wait<0>();
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 128);
-    TRACE(7);
 }
 
 // ------------------------------------------------------------------------------------------------------

@@ -1,22 +1,38 @@
-// One kernel per layer for the gather path: a thread-block cluster of 8 blocks takes one work item (up to 16
-// tokens of one slot). Block q of the cluster shrinks over the q-th eighth of the input features; the
-// partial sums meet through distributed shared memory (no trip through global memory, no second launch);
-// every block then expands its eighth of the output columns. All of the slot's A and B rows the cluster
-// needs are requested by bulk async copies at kernel start, before the dependency wait, so that the slab
-// traffic of this layer overlaps the tail of the kernel before. Replaces the lora_shrink + lora_expand pair
-// of src/kernels/lora.cuh:23-126 when x and y are both ready at the call.
+// One kernel per layer for the few-token work items: a thread-block cluster of 8 blocks takes one work item (up
+// to 16 tokens of one slot) and one group of its output columns. Block q of the cluster shrinks over the q-th
+// eighth of the input features; the partial sums meet through distributed shared memory (no trip through global
+// memory, no second launch); every block then expands its eighth of the cluster's columns. Replaces the
+// lora_shrink + lora_expand pair of src/kernels/lora.cuh:23-126 when x and y are both ready at the call (after
+// the layer's own matrix multiply).
+//
+// Order of events in a block, chosen so that nothing that can be known early waits for anything:
+//   1. dependents are released at once (their prologues touch only slabs and launch records);
+//   2. one fetch of the work item's launch record (descriptor and token rows, written once per step);
+//   3. bulk async copies of the block's rows of A and of its share of B into shared memory, L2 prefetch hints
+//      for the x and y lines it will touch, and an L2 prefetch of the same work item's slabs of the next layer;
+//   4. the dependency wait (the kernel before, typically the layer's matrix multiply, wrote y);
+//   5. x into shared memory, shrink, exchange, expand, y read-modify-write.
+// Nothing before step 4 binds a value of x or y, unless the caller vouched for x (early_x).
+//
+// Arithmetic: 16-token tiles on the warp-level tensor-core instruction (m16n8k16, bf16 in, f32 accumulate), the
+// shape the engine's own kernels use for their 16-token tiles. On the CUDA cores the step is bound by
+// instruction issue (one conversion per bf16 element plus one multiply-add per token), not by memory; a 128-row
+// tcgen05 tile would spend 1/8 or less of its rows on a work item. The f32 intermediate enters the expand as
+// three bf16 terms (high, middle, low part), whose products with bf16 B are exact in f32, so no precision is
+// given up against an f32 multiply-add chain.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <type_traits>
 
 #include "plora_internal.h"
 #include "plora_device.cuh"
 
 typedef __nv_bfloat16 bf16;
 
-PLORA_TRACE_SETTER(plora_trace_set_site)
-
 #define SITE_CLUSTER 8
 #define SITE_THREADS 256
+#define SITE_WARPS 8
 
 namespace {
 
@@ -36,301 +52,647 @@ __device__ __forceinline__ float ld_peer_f32(const float* p, uint32_t rank) {
     return v;
 }
 
-// 16 values per lane -> their 16 warp-wide sums in 16 shuffles; returns the sum of value (lane >> 1) & 15.
-__device__ __forceinline__ float reduce16(float (&v)[16], int lane) {
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const float send = (lane & 16) ? v[i] : v[i + 8];
-        const float keep = (lane & 16) ? v[i + 8] : v[i];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const float send = (lane & 8) ? v[i] : v[i + 4];
-        const float keep = (lane & 8) ? v[i + 4] : v[i];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-    }
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-        const float send = (lane & 4) ? v[i] : v[i + 2];
-        const float keep = (lane & 4) ? v[i + 2] : v[i];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-    }
-    {
-        const float send = (lane & 2) ? v[0] : v[1];
-        const float keep = (lane & 2) ? v[1] : v[0];
-        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
-    }
-    return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+// four 8x8 bf16 matrices from shared memory: lane l gives the address of row (l % 8) of matrix l / 8
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+// D (16 x 8, f32) += A (16 x 16, bf16, row-major) . B (16 x 8, bf16, column-major)
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 struct SiteShape {
-    int kchunk;   // input features per block of the cluster (a multiple of 8)
-    int rmax;     // floats per S row in shared memory (parts * max_rank)
-    int a_bytes;  // shared-memory bytes for the block's A rows
-    int x_bytes;  // ... for the tokens' x chunks
-    int b_bytes;  // ... for the block's share of B
+    int kchunk;    // input features per block of the cluster (a multiple of 8)
+    int kb_pad;    // bytes between rows of the A and x tiles in shared memory (an odd number of 16-byte pieces)
+    int rmax;      // floats per partial S row in shared memory (parts * max_rank)
+    int sp_pad;    // bytes between rows of a bf16 plane of the summed S
+    int aw_bytes;  // shared-memory bytes for the block's A rows, reused for the warps' partial sums
+    int g_rows;    // rows of A per group (64, or all of them when there are fewer)
+    int g_stride;  // bytes between groups: room for g_rows rows of A and for the 8 warps' partials of those rows
+    int x_bytes;   // ... for the tokens' x chunks
+    int b_bytes;   // ... for the block's share of B
+    int nsub;      // column groups per work item (grid y): each is one cluster
 };
 
-__global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THREADS)
-    plora_site_gather_kernel(const bf16* __restrict__ X, int ldx, int K, const int* __restrict__ segs, SegLayout lay,
-                             const plora_desc* __restrict__ table, void* Y, int ldy, int f32_out, SiteShape sh,
+// this block's share [lo, hi) of each part's output columns, and where its rows of B start in shared memory
+struct Share {
+    int lo[PLORA_MAX_PARTS], hi[PLORA_MAX_PARTS], boff[PLORA_MAX_PARTS];
+};
+
+// The slot's output columns, over the targeted parts laid end to end (rec.cat, rec.ntot), are cut into even shares of
+// rec.share columns, one per block of the cluster kernel. Run by lanes 0..3 of one warp, lane p for part p.
+__device__ __forceinline__ void column_share(const PloraRec& rec, int piece, int p, Share& s) {
+    const int c_lo = min(rec.ntot, piece * rec.share), c_hi = min(rec.ntot, c_lo + rec.share);
+    const int lo = max(c_lo, rec.cat[p]) - rec.cat[p];
+    int hi = rec.r[p] > 0 ? min(c_hi, rec.cat[p] + rec.rows[p]) - rec.cat[p] : 0;
+    hi = hi > lo ? hi : lo;
+    const int bytes = (hi - lo) * rec.r[p] * 2;
+    // where the part's rows of B start in shared memory: the bytes of the parts before it
+    int off = 0;
+#pragma unroll
+    for (int q = 0; q < PLORA_MAX_PARTS - 1; q++) {
+        const int b = __shfl_sync(0xfu, bytes, q);
+        if (q < p) off += b;
+    }
+    s.lo[p] = lo;
+    s.hi[p] = hi;
+    s.boff[p] = off;
+}
+
+// L2 prefetch of this block's eighth of `bytes` at `base` (both multiples of 16), 32 KB per request, one warp
+__device__ __forceinline__ void prefetch_eighth(uint64_t base, uint64_t bytes, uint32_t crank, int lane) {
+    const uint64_t per = ((bytes / SITE_CLUSTER) + 15) & ~(uint64_t)15;
+    const uint64_t lo = min(bytes, per * crank), hi = min(bytes, lo + per);
+    for (uint64_t o = lo + (uint64_t)lane * 32768; o < hi; o += 32 * 32768) {
+        const uint32_t n = (uint32_t)min((uint64_t)32768, hi - o) & ~15u;
+        if (n) bulk_prefetch_l2(reinterpret_cast<const unsigned char*>(base) + o, n);
+    }
+}
+
+// remote arrival on the same barrier in block `rank` of the cluster, releasing this thread's (and, through the
+// block barrier before it, the block's) shared-memory writes to the cluster
+__device__ __forceinline__ void mbar_arrive_peer(uint64_t* bar, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(bar)), "r"(rank));
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(a) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, int* status) {
+    for (int i = 0; i < (1 << 20); i++)
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+    atomicMax(status, PLORA_ERR_TIMEOUT);
+    return false;
+}
+// "my reads of your shared memory are done": no memory ordering is asked of the arrival itself
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+
+// The shrink's inner loop for one warp: n 16-wide steps, SITE_WARPS steps apart, over PAIRS pairs of 8-row tiles of A
+template <int PAIRS>
+__device__ __forceinline__ void shrink_steps(float (&acc)[8][4], uint32_t xs_w, uint32_t as_w, uint32_t kb_pad, int n) {
+#pragma unroll 2
+    for (int i = 0; i < n; i++) {
+        uint32_t xa[4];
+        ldmatrix_x4(xa, xs_w + (uint32_t)i * (SITE_WARPS * 32u));
+#pragma unroll
+        for (int pr = 0; pr < PAIRS; pr++) {
+            uint32_t bb[4];
+            ldmatrix_x4(bb, as_w + (uint32_t)(pr * 16) * kb_pad + (uint32_t)i * (SITE_WARPS * 32u));
+            mma_16816(acc[2 * pr], xa, bb[0], bb[1]);
+            mma_16816(acc[2 * pr + 1], xa, bb[2], bb[3]);
+        }
+    }
+}
+
+// y of one 16-column step: the lane's two token rows (g and g + 8) times its two column pairs
+template <bool F32>
+struct YStep {
+    float2 v[2][2];
+};
+
+// One part's share of the output columns: y[tok, off + lo + c] += S3[tok, r_off ..] . B[c, :]^T for c in [0, ncols).
+// NK: 16-wide steps over the part's rank held as fragments in registers (0: fetched from shared memory per step).
+template <int NK, bool F32>
+__device__ __forceinline__ void expand_part(uint32_t s3_part, uint32_t plane_bytes, uint32_t bs_lane, int r, int ncols,
+                                            void* Y, int ldy, size_t ybase, int tok0, int tok1, int warp, int t2) {
+    typedef typename std::conditional<F32, float, bf16>::type ytype;
+    const int nk = NK > 0 ? NK : r >> 4;
+    uint32_t sa[NK > 0 ? NK : 1][3][4];
+    if (NK > 0) {
+#pragma unroll
+        for (int ks = 0; ks < NK; ks++)
+#pragma unroll
+            for (int pl = 0; pl < 3; pl++) ldmatrix_x4(sa[ks][pl], s3_part + (uint32_t)pl * plane_bytes + (uint32_t)ks * 32u);
+    }
+    ytype* y0 = tok0 >= 0 ? reinterpret_cast<ytype*>(Y) + (size_t)tok0 * ldy + ybase + t2 : nullptr;
+    ytype* y1 = tok1 >= 0 ? reinterpret_cast<ytype*>(Y) + (size_t)tok1 * ldy + ybase + t2 : nullptr;
+    auto load = [&](YStep<F32>& q, int c) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const ytype* yp = h ? y1 : y0;
+#pragma unroll
+            for (int n = 0; n < 2; n++) {
+                if (yp != nullptr && c + n * 8 + t2 < ncols) {
+                    if (F32) q.v[h][n] = *reinterpret_cast<const float2*>(yp + c + n * 8);
+                    else q.v[h][n] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(yp + c + n * 8));
+                }
+            }
+        }
+    };
+    // 16 columns (two tiles of 8) per step; warp q takes the steps q, q + 8, ...; y is fetched two steps ahead
+    int c = warp * 16;
+    YStep<F32> q0, q1, q2;
+    load(q0, c);
+    load(q1, c + SITE_WARPS * 16);
+    for (; c < ncols; c += SITE_WARPS * 16) {
+        load(q2, c + 2 * SITE_WARPS * 16);
+        float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < (NK > 0 ? NK : 8); ks++) {
+            if (ks < nk) {
+                uint32_t bb[4];
+                ldmatrix_x4(bb, bs_lane + (uint32_t)c * (uint32_t)r * 2u + (uint32_t)ks * 32u);
+                // low, middle, high term: the small ones first
+#pragma unroll
+                for (int pl = 2; pl >= 0; pl--) {
+                    if (NK > 0) {
+                        mma_16816(d0, sa[ks][pl], bb[0], bb[1]);
+                        mma_16816(d1, sa[ks][pl], bb[2], bb[3]);
+                    } else {
+                        uint32_t st[4];
+                        ldmatrix_x4(st, s3_part + (uint32_t)pl * plane_bytes + (uint32_t)ks * 32u);
+                        mma_16816(d0, st, bb[0], bb[1]);
+                        mma_16816(d1, st, bb[2], bb[3]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            ytype* yp = h ? y1 : y0;
+#pragma unroll
+            for (int n = 0; n < 2; n++) {
+                if (yp != nullptr && c + n * 8 + t2 < ncols) {
+                    const float* d = n ? d1 : d0;
+                    const float v0 = q0.v[h][n].x + d[2 * h], v1 = q0.v[h][n].y + d[2 * h + 1];
+                    if (F32) *reinterpret_cast<float2*>(yp + c + n * 8) = make_float2(v0, v1);
+                    else *reinterpret_cast<__nv_bfloat162*>(yp + c + n * 8) = __floats2bfloat162_rn(v0, v1);
+                }
+            }
+        }
+        q0 = q1;
+        q1 = q2;
+    }
+}
+
+// The same for work items of at most 8 tokens whose y rows can move in 16-byte pieces (the common decoding case):
+// 32 columns per step. Rows 0-7 of the token tile carry one bf16 term of S and rows 8-15 another, so the three terms
+// take two multiplies per 8-column tile ([high | middle], [low | zero]) and a lane adds its two rows. The B rows
+// are fed to the step's four tiles in an order that leaves every lane with 8 adjacent columns of its token row:
+// y is read and written as 16-byte pieces, 64 contiguous bytes per row and instruction (bf16).
+template <int NK, bool F32>
+__device__ __forceinline__ void expand_fast(uint32_t s3_part, uint32_t sp_pad, uint32_t plane_bytes, uint32_t bs_part, int r,
+                                            int ncols, void* Y, int ldy, size_t ybase, int tok, int warp, int lane, bool pre,
+                                            uint4 pre0, uint4 pre1) {
+    typedef typename std::conditional<F32, float, bf16>::type ytype;
+    const int nk = NK > 0 ? NK : r >> 4;
+    const uint32_t a_lane = s3_part + (uint32_t)(lane & 7) * sp_pad + (uint32_t)((lane >> 3) & 1) * plane_bytes + (uint32_t)(lane >> 4) * 16u;
+    uint32_t sa[NK > 0 ? NK : 1][2][4];
+    if (NK > 0) {
+#pragma unroll
+        for (int ks = 0; ks < NK; ks++) {
+            ldmatrix_x4(sa[ks][0], a_lane + (uint32_t)ks * 32u);
+            ldmatrix_x4(sa[ks][1], a_lane + 2u * plane_bytes + (uint32_t)ks * 32u);
+        }
+    }
+    const bool live = tok >= 0;
+    ytype* y = reinterpret_cast<ytype*>(Y) + (size_t)(live ? tok : 0) * ldy + ybase + 8 * (lane & 3);
+    // four-matrix load: matrices 0,1 = tile n (inputs 0-7, 8-15 of the step), matrices 2,3 = tile n + 1; row j of tile
+    // n is column 8 (j / 2) + 2 n + (j % 2) of the step
+    const int j = lane & 7, half = (lane >> 3) & 1, tsel = lane >> 4;
+    const uint32_t b01 = bs_part + (uint32_t)(8 * (j >> 1) + 2 * tsel + (j & 1)) * (uint32_t)r * 2u + (uint32_t)half * 16u;
+    const uint32_t b23 = b01 + 4u * (uint32_t)r * 2u;
+    const int c8 = 8 * (lane & 3);
+    int c = warp * 32;
+    uint4 q0 = make_uint4(0u, 0u, 0u, 0u), q1 = q0, n0 = q0, n1 = q0;
+    auto fetch = [&](uint4& a, uint4& b, int cc) {
+        if (live && cc + c8 < ncols) {
+            a = __ldcg(reinterpret_cast<const uint4*>(y + cc));
+            if (F32) b = __ldcg(reinterpret_cast<const uint4*>(y + cc) + 1);
+        }
+    };
+    if (pre) {  // the first step's y was asked for right after the dependency wait
+        q0 = pre0;
+        q1 = pre1;
+    } else {
+        fetch(q0, q1, c);
+    }
+    for (; c < ncols; c += SITE_WARPS * 32) {
+        fetch(n0, n1, c + SITE_WARPS * 32);
+        float d[4][4];
+#pragma unroll
+        for (int n = 0; n < 4; n++) d[n][0] = d[n][1] = d[n][2] = d[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < (NK > 0 ? NK : 8); ks++) {
+            if (ks < nk) {
+                uint32_t ba[4], bc[4];
+                ldmatrix_x4(ba, b01 + (uint32_t)c * (uint32_t)r * 2u + (uint32_t)ks * 32u);
+                ldmatrix_x4(bc, b23 + (uint32_t)c * (uint32_t)r * 2u + (uint32_t)ks * 32u);
+                // [low | zero] first, then [high | middle]
+#pragma unroll
+                for (int f = 1; f >= 0; f--) {
+                    uint32_t st[4];
+                    if (NK == 0) ldmatrix_x4(st, a_lane + (uint32_t)f * 2u * plane_bytes + (uint32_t)ks * 32u);
+                    const uint32_t(&a)[4] = NK > 0 ? sa[NK > 0 ? ks : 0][f] : st;
+                    mma_16816(d[0], a, ba[0], ba[1]);
+                    mma_16816(d[1], a, ba[2], ba[3]);
+                    mma_16816(d[2], a, bc[0], bc[1]);
+                    mma_16816(d[3], a, bc[2], bc[3]);
+                }
+            }
+        }
+        if (live && c + c8 < ncols) {
+            if (F32) {
+                const float4 a = *reinterpret_cast<const float4*>(&q0), b = *reinterpret_cast<const float4*>(&q1);
+                *reinterpret_cast<float4*>(y + c) = make_float4(a.x + (d[0][0] + d[0][2]), a.y + (d[0][1] + d[0][3]),
+                                                                 a.z + (d[1][0] + d[1][2]), a.w + (d[1][1] + d[1][3]));
+                *(reinterpret_cast<float4*>(y + c) + 1) = make_float4(b.x + (d[2][0] + d[2][2]), b.y + (d[2][1] + d[2][3]),
+                                                                       b.z + (d[3][0] + d[3][2]), b.w + (d[3][1] + d[3][3]));
+            } else {
+                const uint32_t w[4] = {q0.x, q0.y, q0.z, q0.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int n = 0; n < 4; n++) {
+                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[n]));
+                    const __nv_bfloat162 v = __floats2bfloat162_rn(f.x + (d[n][0] + d[n][2]), f.y + (d[n][1] + d[n][3]));
+                    o[n] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+                *reinterpret_cast<uint4*>(y + c) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+        q0 = n0;
+        q1 = n1;
+    }
+}
+
+template <bool F32>
+__global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THREADS, 2)
+    plora_site_gather_kernel(const bf16* __restrict__ X, int ldx, int K, const PloraRec* __restrict__ recs, int rec_cap,
+                             const PloraRec* __restrict__ next_recs, void* Y, int ldy, SiteShape sh, int early_x,
                              int* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char dsm[];
-    __shared__ __align__(8) uint64_t bars[3];  // A rows, x chunks, B rows
-    __shared__ int stok[PLORA_WORK_TOKENS];
-    __shared__ int s_boff[PLORA_MAX_PARTS], s_lo[PLORA_MAX_PARTS], s_hi[PLORA_MAX_PARTS], s_cat[PLORA_MAX_PARTS];
+    __shared__ __align__(8) uint64_t bars[4];  // A rows, x chunks, B rows, the cluster's partials
+    __shared__ PloraRec srec;
+    __shared__ Share sshare;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t crank = cluster_rank();
+    // A rows in groups of g_rows: group q at q * g_stride, its rows kb_pad apart. Once a group's rows are used up,
+    // the warps' partial sums of those rows [warp][16][g_rows] take their place.
     unsigned char* As = dsm;
-    unsigned char* Xs = As + sh.a_bytes;
-    unsigned char* Bs = Xs + sh.x_bytes;
+    unsigned char* Xs = As + sh.aw_bytes;                   // x chunks [16][kb_pad]
+    unsigned char* Bs = Xs + sh.x_bytes;                    // this block's rows of B, part after part
     float* Sp = reinterpret_cast<float*>(Bs + sh.b_bytes);  // this block's partial S [16][rmax]
-    float* Ss = Sp + PLORA_WORK_TOKENS * sh.rmax;           // the summed S [16][rmax]
-    const int n_work = segs[SEG_N_WORK];
+    // the summed S as three bf16 planes [16][sp_pad] (high, middle, low term) and a fourth plane that stays zero
+    unsigned char* S3 = reinterpret_cast<unsigned char*>(Sp + PLORA_WORK_TOKENS * sh.rmax);
+    const uint32_t plane_bytes = PLORA_WORK_TOKENS * (uint32_t)sh.sp_pad;
+    for (uint32_t i = tid * 16u; i < plane_bytes; i += SITE_THREADS * 16u)
+        *reinterpret_cast<uint4*>(S3 + 3u * plane_bytes + i) = make_uint4(0u, 0u, 0u, 0u);
+    // The kernels after this one may start their prologues now: before their own waits they touch slabs and
+    // launch records only (and x, where their caller vouched for it); every store of the path comes after a
+    // wait, and every grid waits for its predecessor before it completes.
+    pdl_trigger();
     if (tid == 0) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
         mbar_init(&bars[2], 1);
+        mbar_init(&bars[3], SITE_CLUSTER);  // one arrival per block of the cluster
         mbar_fence_init();
     }
-    bool waited = false;
-    uint32_t ph_ax = 0, ph_b = 0;  // phases of the A/x barriers and of the B barrier (each flips only when used)
-    bool alive = true;             // false once a bounded wait ran out: keep meeting the cluster, do no more work
+    cluster_arrive();  // the barriers exist; met (cluster_wait) before the first remote arrival
+    bool met = false, waited = false;
+    uint32_t ph_ax = 0, ph_b = 0, ph_s = 0;  // barrier phases (each flips only when its barrier was used)
+    bool alive = true;                       // false once a bounded wait ran out: keep meeting the cluster, do no more work
     const int k0 = (int)crank * sh.kchunk;
     const int klen = max(0, min(sh.kchunk, K - k0));
     const uint32_t kbytes = (uint32_t)klen * 2u;
-    for (int w = blockIdx.z; w < n_work; w += gridDim.z) {
-        const int* work = segs + lay.work() + PLORA_WORK_WORDS * w;
-        const int slot = work[0], cnt = work[2];
-        const int mytok = work[4 + (lane & 15)];
-        const plora_desc& d = table[slot];
-        TRACE(0);
-        const int R = d.rank;
-        if (R == 0) continue;  // the same decision in every block of the cluster
-        // this block's share of the slot's output columns, over the targeted parts laid end to end
+    const int nks = (klen + 15) >> 4;  // 16-wide steps over this block's inputs (a half step reads zeros)
+    const int esize = F32 ? 4 : 2;
+    // fragment coordinates of the tensor-core tile: this lane holds rows g and g + 8, columns 2 t and 2 t + 1
+    const int g = lane >> 2, t2 = (lane & 3) * 2;
+    // row and 16-byte piece this lane names in a four-matrix load: A-side (16 rows x 16 inputs) and B-side (two
+    // 8-row tiles x 16 inputs)
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_piece = lane >> 4;
+    const int b_row = (lane & 7) + (lane >> 4) * 8, b_piece = (lane >> 3) & 1;
+    const uint32_t xs_lane = smem_u32(Xs) + (uint32_t)a_row * (uint32_t)sh.kb_pad + (uint32_t)a_piece * 16u;
+    const uint32_t as_lane = smem_u32(As) + (uint32_t)b_row * (uint32_t)sh.kb_pad + (uint32_t)b_piece * 16u;
+    const uint32_t s3_lane = smem_u32(S3) + (uint32_t)a_row * (uint32_t)sh.sp_pad + (uint32_t)a_piece * 16u;
+    for (int w = blockIdx.z; w < rec_cap; w += gridDim.z) {
+        // ---- the one metadata fetch: the record's 208 live bytes into shared memory
+        if (tid < 13) reinterpret_cast<uint4*>(&srec)[tid] = __ldg(reinterpret_cast<const uint4*>(recs + w) + tid);
+        __syncthreads();
+        const int cnt = srec.cnt, R = srec.rank;
+        if (cnt == 0) break;  // end of the list: the same decision in every block of the cluster
+        if (R == 0) {         // the slot's adapter skips this layer
+            __syncthreads();
+            continue;
+        }
+        if (warp == 1 && lane < PLORA_MAX_PARTS) column_share(srec, (int)blockIdx.y * SITE_CLUSTER + (int)crank, lane, sshare);
+        // ---- slab requests (before the dependency wait)
+        if (warp == 0 && klen > 0) {
+            const bf16* A = reinterpret_cast<const bf16*>(srec.a) + k0;
+            if (lane == 0) mbar_expect_tx(&bars[0], (uint32_t)R * kbytes);
+            __syncwarp();
+            for (int r = lane; r < R; r += 32)
+                bulk_g2s(As + (size_t)(r >> 6) * sh.g_stride + (size_t)(r & 63) * sh.kb_pad, A + (size_t)r * K, kbytes, &bars[0]);
+        }
+        // a half step at the end of the rows multiplies zeros
+        if ((klen & 15) != 0)
+            for (int r = tid; r < R + PLORA_WORK_TOKENS; r += SITE_THREADS)
+                *reinterpret_cast<uint4*>((r < R ? As + (size_t)(r >> 6) * sh.g_stride + (size_t)(r & 63) * sh.kb_pad
+                                                 : Xs + (size_t)(r - R) * sh.kb_pad) + kbytes) = make_uint4(0u, 0u, 0u, 0u);
+        __syncthreads();  // the share is known
         if (tid == 0) {
-            int ntot = 0;
-            for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-                s_cat[p] = ntot;
-                if (d.r[p] > 0) ntot += d.rows[p];
-            }
-            const int share = ((ntot + SITE_CLUSTER - 1) / SITE_CLUSTER + 1) & ~1;
-            const int c_lo = min(ntot, (int)crank * share), c_hi = min(ntot, c_lo + share);
-            int off = 0;
-            for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-                const int lo = max(c_lo, s_cat[p]) - s_cat[p];
-                const int hi = d.r[p] > 0 ? min(c_hi, s_cat[p] + d.rows[p]) - s_cat[p] : 0;
-                s_lo[p] = lo;
-                s_hi[p] = hi > lo ? hi : lo;
-                s_boff[p] = off;
-                if (hi > lo) off += (hi - lo) * d.r[p] * 2;
+            uint32_t total = 0;
+#pragma unroll
+            for (int p = 0; p < PLORA_MAX_PARTS; p++)
+                total += (uint32_t)(sshare.hi[p] - sshare.lo[p]) * (uint32_t)srec.r[p] * 2u;
+            if (total > 0) {
+                mbar_expect_tx(&bars[2], total);
+#pragma unroll
+                for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+                    const uint32_t bytes = (uint32_t)(sshare.hi[p] - sshare.lo[p]) * (uint32_t)srec.r[p] * 2u;
+                    if (bytes > 0)
+                        bulk_g2s(Bs + sshare.boff[p],
+                                 reinterpret_cast<const bf16*>(srec.b[p]) + (size_t)sshare.lo[p] * srec.r[p], bytes, &bars[2]);
+                }
             }
         }
-        if (tid < PLORA_WORK_TOKENS) stok[tid] = mytok;
-        __syncthreads();
-        // ---- slab requests (before the dependency wait)
-        if (warp == 0) {
-            if (klen > 0) {
-                const bf16* A = reinterpret_cast<const bf16*>(d.a) + k0;
-                if (lane == 0) mbar_expect_tx(&bars[0], (uint32_t)R * kbytes);
-                __syncwarp();
-                for (int r = lane; r < R; r += 32) bulk_g2s(As + (size_t)r * kbytes, A + (size_t)r * K, kbytes, &bars[0]);
+        // ---- hints: the x and y lines this block will touch, and the next layer's slabs of this work item
+        if (!waited && warp >= 2) {
+            const int t1 = tid - 64, n1 = SITE_THREADS - 64;
+            if (klen > 0 && !early_x) {
+                const int lines = (int)((kbytes + 127) / 128);
+                for (int i = t1; i < cnt * lines; i += n1) {
+                    const int t = i / lines, l = i - t * lines;
+                    prefetch_l2(reinterpret_cast<const unsigned char*>(X + (size_t)srec.tok[t] * ldx + k0) + (size_t)l * 128);
+                }
             }
-            if (lane == 0) {
-                uint32_t total = 0;
-                for (int p = 0; p < PLORA_MAX_PARTS; p++) total += (uint32_t)(s_hi[p] - s_lo[p]) * (uint32_t)d.r[p] * 2u;
-                if (total > 0) {
-                    mbar_expect_tx(&bars[2], total);
-                    for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-                        const uint32_t bytes = (uint32_t)(s_hi[p] - s_lo[p]) * (uint32_t)d.r[p] * 2u;
-                        if (bytes > 0)
-                            bulk_g2s(Bs + s_boff[p], reinterpret_cast<const bf16*>(d.b[p]) + (size_t)s_lo[p] * d.r[p], bytes,
-                                     &bars[2]);
+#pragma unroll 1
+            for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+                const int ncol = sshare.hi[p] - sshare.lo[p];
+                if (ncol <= 0) continue;
+                const size_t len = (size_t)ncol * esize;
+                const int lines = (int)((len + 127) / 128) + 1;
+                for (int i = t1; i < cnt * lines; i += n1) {
+                    const int t = i / lines, l = i - t * lines;
+                    const size_t start = ((size_t)srec.tok[t] * ldy + srec.off[p] + sshare.lo[p]) * esize;
+                    const size_t at = (start & ~(size_t)127) + (size_t)l * 128;
+                    if (at < start + len) prefetch_l2(reinterpret_cast<const unsigned char*>(Y) + at);
+                }
+            }
+        }
+        if (next_recs != nullptr && warp == 1 && blockIdx.y == 0) {
+            // an eighth of every slab of this work item at the next layer (same slot; the records are written
+            // for all layers at once)
+            const PloraRec* nr = next_recs + w;
+            if (crank == 0 && lane == 0) prefetch_l2(reinterpret_cast<const unsigned char*>(nr) + 128);  // the record's second line
+            const int4 head = __ldg(reinterpret_cast<const int4*>(nr));  // cnt, slot, rank, cols
+            if (head.x > 0 && head.z > 0) {
+                prefetch_eighth(__ldg(&nr->a), (uint64_t)head.z * (uint64_t)head.w * 2u, crank, lane);
+#pragma unroll 1
+                for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+                    const int rp = __ldg(&nr->r[p]);
+                    if (rp > 0) prefetch_eighth(__ldg(&nr->b[p]), (uint64_t)__ldg(&nr->rows[p]) * (uint64_t)rp * 2u, crank, lane);
+                }
+            }
+        }
+        if (!waited && !early_x) {
+            pdl_wait();
+            waited = true;
+        }
+        // y of this lane's first expand step (first part of the share), on its way while the shrink and the exchange run
+        uint4 pre0 = make_uint4(0u, 0u, 0u, 0u), pre1 = pre0;
+        int pre_part = -1;
+        if (waited) {
+#pragma unroll
+            for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+                if (pre_part < 0 && srec.r[p] > 0 && sshare.hi[p] > sshare.lo[p]) {
+                    pre_part = p;
+                    const size_t ybase = (size_t)srec.off[p] + sshare.lo[p];
+                    const int ncols = sshare.hi[p] - sshare.lo[p];
+                    const bool fast = cnt <= 8 && (ncols & 7) == 0 &&
+                                      ((reinterpret_cast<uintptr_t>(Y) | ((size_t)ldy * esize) | (ybase * esize)) & 15) == 0;
+                    const int c = warp * 32 + 8 * (lane & 3);
+                    if (fast && g < cnt && c < ncols) {
+                        const unsigned char* yp = reinterpret_cast<const unsigned char*>(Y) + ((size_t)srec.tok[g] * ldy + ybase + c) * esize;
+                        pre0 = __ldcg(reinterpret_cast<const uint4*>(yp));
+                        if (F32) pre1 = __ldcg(reinterpret_cast<const uint4*>(yp) + 1);
                     }
                 }
             }
         }
-        if (!waited) {
-            pdl_wait();
-            pdl_trigger();
-            waited = true;
-        }
-        TRACE(2);
-        // ---- shrink over this block's eighth of the inputs
+        // ---- shrink over this block's eighth of the inputs: warp q takes the 16-wide steps q, q + 8, ...
         if (klen > 0) {
             if (warp == 0) {
                 if (lane == 0) mbar_expect_tx(&bars[1], (uint32_t)cnt * kbytes);
                 __syncwarp();
-                if (lane < cnt) bulk_g2s(Xs + (size_t)lane * kbytes, X + (size_t)mytok * ldx + k0, kbytes, &bars[1]);
+                if (lane < cnt) bulk_g2s(Xs + (size_t)lane * sh.kb_pad, X + (size_t)srec.tok[lane] * ldx + k0, kbytes, &bars[1]);
             }
             if (alive) alive = mbar_wait(&bars[0], ph_ax, status) && mbar_wait(&bars[1], ph_ax, status);
             ph_ax ^= 1;
-            TRACE(3);
-            for (int tp = 0; alive && tp < cnt; tp += 4) {
-                const int nt = min(4, cnt - tp);
-                for (int n0 = warp * 4; n0 < R; n0 += 32) {
-                    float acc[16];
+        }
+        // rows of A in groups of 64 (8 tiles of 8): 32 accumulators per lane
+        for (int j0 = 0; j0 < R; j0 += 64) {
+            float acc[8][4];
 #pragma unroll
-                    for (int i = 0; i < 16; i++) acc[i] = 0.f;
-                    for (int k = lane * 8; k < klen; k += 256) {
-                        float xf[4][8];
+            for (int i = 0; i < 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+            const int pairs = min(4, (R - j0) >> 4);  // 16-row pairs of tiles in this group
+            const uint32_t grp = (uint32_t)(j0 >> 6) * (uint32_t)sh.g_stride;
+            if (alive && klen > 0) {
+                const uint32_t xs_w = xs_lane + (uint32_t)warp * 32u, as_w = as_lane + grp + (uint32_t)warp * 32u;
+                const int n = (nks - warp + SITE_WARPS - 1) / SITE_WARPS;  // this warp's steps
+                if (pairs == 1) shrink_steps<1>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
+                else if (pairs == 2) shrink_steps<2>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
+                else if (pairs == 3) shrink_steps<3>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
+                else shrink_steps<4>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
+            }
+            __syncthreads();  // every warp is through with this group's rows of A: their place takes the partials
+            float* wp = reinterpret_cast<float*>(As + grp) + (size_t)warp * PLORA_WORK_TOKENS * sh.g_rows + t2;
 #pragma unroll
-                        for (int t = 0; t < 4; t++)
-                            unpack8(lds16(Xs + (size_t)(tp + min(t, nt - 1)) * kbytes + k * 2), xf[t]);
-#pragma unroll
-                        for (int r = 0; r < 4; r++) {
-                            float af[8];
-                            unpack8(lds16(As + (size_t)(n0 + r) * kbytes + k * 2), af);
-#pragma unroll
-                            for (int t = 0; t < 4; t++)
-#pragma unroll
-                                for (int e = 0; e < 8; e++) acc[r * 4 + t] = fmaf(xf[t][e], af[e], acc[r * 4 + t]);
-                        }
-                    }
-                    const float v = reduce16(acc, lane);
-                    if ((lane & 1) == 0) {
-                        const int i = lane >> 1, r = i >> 2, t = i & 3;
-                        if (t < nt) Sp[(tp + t) * sh.rmax + n0 + r] = v;
-                    }
+            for (int i = 0; i < 8; i++) {
+                if (i < 2 * pairs) {
+                    if (g < cnt) *reinterpret_cast<float2*>(wp + g * sh.g_rows + i * 8) = make_float2(acc[i][0], acc[i][1]);
+                    if (g + 8 < cnt) *reinterpret_cast<float2*>(wp + (g + 8) * sh.g_rows + i * 8) = make_float2(acc[i][2], acc[i][3]);
                 }
             }
-        } else {
-            for (int i = tid; i < cnt * R; i += SITE_THREADS) Sp[(i / R) * sh.rmax + (i % R)] = 0.f;
         }
-        // ---- the eight partials meet: block q's Sp is read by everyone, added in block order
-        TRACE(4);
-        cluster_arrive();
-        cluster_wait();
-        TRACE(5);
-        for (int i = tid; i < cnt * R; i += SITE_THREADS) {
-            const int t = i / R, j = i - t * R;
-            const float* p = Sp + t * sh.rmax + j;
-            float v[SITE_CLUSTER];
-#pragma unroll
-            for (int q = 0; q < SITE_CLUSTER; q++) v[q] = ld_peer_f32(p, q);
-            float acc = v[0];
-#pragma unroll
-            for (int q = 1; q < SITE_CLUSTER; q++) acc += v[q];
-            Ss[t * sh.rmax + j] = acc;
-        }
-        cluster_arrive();  // my reads of the others' partials are done
         __syncthreads();
-        TRACE(6);
+        // the eight warps' partials, added in warp order: warp q takes the token rows q, q + 8
+        for (int t = warp; t < cnt; t += SITE_WARPS) {
+            for (int j = lane; j < R; j += 32) {
+                const float* p = reinterpret_cast<const float*>(As + (size_t)(j >> 6) * sh.g_stride) + t * sh.g_rows + (j & 63);
+                float acc = p[0];
+#pragma unroll
+                for (int q = 1; q < SITE_WARPS; q++) acc += p[(size_t)q * PLORA_WORK_TOKENS * sh.g_rows];
+                Sp[t * sh.rmax + j] = acc;
+            }
+        }
+        // ---- the eight partials meet: every block tells every block that its Sp is written, then reads all
+        // eight and adds them in block order
+        __syncthreads();
+        if (!met) {
+            cluster_wait();  // everybody's barriers exist
+            met = true;
+        }
+        if (tid < SITE_CLUSTER) mbar_arrive_peer(&bars[3], (uint32_t)tid);
+        if (alive) alive = mbar_wait_cluster(&bars[3], ph_s, status);
+        ph_s ^= 1;
+        for (int t = warp; t < cnt; t += SITE_WARPS) {
+            for (int j = lane; j < R; j += 32) {
+                const float* p = Sp + t * sh.rmax + j;
+                float v[SITE_CLUSTER];
+#pragma unroll
+                for (int q = 0; q < SITE_CLUSTER; q++) v[q] = ld_peer_f32(p, q);
+                float acc = v[0];
+#pragma unroll
+                for (int q = 1; q < SITE_CLUSTER; q++) acc += v[q];
+                // three bf16 terms whose sum is the f32 value
+                const bf16 hi = __float2bfloat16_rn(acc);
+                const float r1 = acc - __bfloat162float(hi);
+                const bf16 mid = __float2bfloat16_rn(r1);
+                const bf16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+                unsigned char* s3 = S3 + (size_t)t * sh.sp_pad + (size_t)j * 2;
+                *reinterpret_cast<bf16*>(s3) = hi;
+                *reinterpret_cast<bf16*>(s3 + plane_bytes) = mid;
+                *reinterpret_cast<bf16*>(s3 + 2 * plane_bytes) = lo;
+            }
+        }
+        cluster_arrive_relaxed();  // my reads of the others' partials are done
+        if (!waited) {             // early_x: everything so far ran ahead of the kernel before; y must not
+            pdl_wait();
+            waited = true;
+        }
+        __syncthreads();
         // ---- expand over this block's share of the output columns
         bool okb = true;
         {
             int total = 0;
-            for (int p = 0; p < PLORA_MAX_PARTS; p++) total += s_hi[p] - s_lo[p];
+#pragma unroll
+            for (int p = 0; p < PLORA_MAX_PARTS; p++) total += sshare.hi[p] - sshare.lo[p];
             if (total > 0) {
                 if (alive) okb = mbar_wait(&bars[2], ph_b, status);
                 ph_b ^= 1;
             }
         }
         if (!okb) alive = false;
-        TRACE(7);
         if (alive) {
+            const int tok0 = g < cnt ? srec.tok[g] : -1, tok1 = g + 8 < cnt ? srec.tok[g + 8] : -1;
+#pragma unroll 1
             for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-                const int r = d.r[p];
-                const int lo = s_lo[p], hi = s_hi[p];
+                const int r = srec.r[p];
+                const int lo = sshare.lo[p], hi = sshare.hi[p];
                 if (r == 0 || hi <= lo) continue;
-                const int r_off = d.r_off[p];
-                const unsigned char* bpart = Bs + s_boff[p];
-                for (int c = lo + 2 * tid; c < hi; c += 2 * SITE_THREADS) {
-                    const unsigned char* b0 = bpart + (size_t)(c - lo) * r * 2;
-                    const unsigned char* b1 = b0 + (size_t)r * 2;
-                    const size_t ycol = (size_t)d.off[p] + c;
-                    for (int tg = 0; tg < cnt; tg += 4) {
-                        float2 yv[4];
-#pragma unroll
-                        for (int t = 0; t < 4; t++) {
-                            if (tg + t < cnt) {
-                                const size_t at = (size_t)stok[tg + t] * ldy + ycol;
-                                if (f32_out) yv[t] = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(Y) + at);
-                                else
-                                    yv[t] = __bfloat1622float2(
-                                        *reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(Y) + at));
-                            }
-                        }
-                        float acc[4][2];
-#pragma unroll
-                        for (int t = 0; t < 4; t++) acc[t][0] = acc[t][1] = 0.f;
-                        for (int j = 0; j < r; j += 8) {
-                            float f0[8], f1[8];
-                            unpack8(lds16(b0 + j * 2), f0);
-                            unpack8(lds16(b1 + j * 2), f1);
-#pragma unroll
-                            for (int t = 0; t < 4; t++) {
-                                if (tg + t < cnt) {
-                                    const float* sp = Ss + (tg + t) * sh.rmax + r_off + j;
-                                    const float4 s0 = *reinterpret_cast<const float4*>(sp);
-                                    const float4 s1 = *reinterpret_cast<const float4*>(sp + 4);
-                                    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-                                    for (int e = 0; e < 8; e++) {
-                                        acc[t][0] = fmaf(sv[e], f0[e], acc[t][0]);
-                                        acc[t][1] = fmaf(sv[e], f1[e], acc[t][1]);
-                                    }
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int t = 0; t < 4; t++) {
-                            if (tg + t < cnt) {
-                                const size_t at = (size_t)stok[tg + t] * ldy + ycol;
-                                if (f32_out)
-                                    *reinterpret_cast<float2*>(reinterpret_cast<float*>(Y) + at) =
-                                        make_float2(yv[t].x + acc[t][0], yv[t].y + acc[t][1]);
-                                else
-                                    *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<bf16*>(Y) + at) =
-                                        __floats2bfloat162_rn(yv[t].x + acc[t][0], yv[t].y + acc[t][1]);
-                            }
-                        }
-                    }
-                }
+                const uint32_t s3_part = s3_lane + (uint32_t)srec.r_off[p] * 2u;
+                const uint32_t bs_lane = smem_u32(Bs) + (uint32_t)sshare.boff[p] + (uint32_t)b_row * (uint32_t)r * 2u + (uint32_t)b_piece * 16u;
+                const size_t ybase = (size_t)srec.off[p] + lo;
+                // fast form: at most 8 tokens, and y rows that move in 16-byte pieces
+                const bool fast = cnt <= 8 && ((hi - lo) & 7) == 0 && ((reinterpret_cast<uintptr_t>(Y) | ((size_t)ldy * esize) | (ybase * esize)) & 15) == 0;
+                if (fast) {
+                    const int tok = g < cnt ? srec.tok[g] : -1;
+                    const uint32_t s3p = smem_u32(S3) + (uint32_t)srec.r_off[p] * 2u, bsp = smem_u32(Bs) + (uint32_t)sshare.boff[p];
+                    const bool pre = p == pre_part;
+                    if (r == 16) expand_fast<1, F32>(s3p, (uint32_t)sh.sp_pad, plane_bytes, bsp, r, hi - lo, Y, ldy, ybase, tok, warp, lane, pre, pre0, pre1);
+                    else if (r == 32) expand_fast<2, F32>(s3p, (uint32_t)sh.sp_pad, plane_bytes, bsp, r, hi - lo, Y, ldy, ybase, tok, warp, lane, pre, pre0, pre1);
+                    else expand_fast<0, F32>(s3p, (uint32_t)sh.sp_pad, plane_bytes, bsp, r, hi - lo, Y, ldy, ybase, tok, warp, lane, pre, pre0, pre1);
+                } else if (r == 16) expand_part<1, F32>(s3_part, plane_bytes, bs_lane, r, hi - lo, Y, ldy, ybase, tok0, tok1, warp, t2);
+                else expand_part<0, F32>(s3_part, plane_bytes, bs_lane, r, hi - lo, Y, ldy, ybase, tok0, tok1, warp, t2);
             }
         }
         cluster_wait();   // nobody reads my partials any more: they may be overwritten (or the block may leave)
-        TRACE(8);
         __syncthreads();  // shared memory is reused by the next work item
     }
-    if (!waited) pdl_exit_idle();
+    if (!met) cluster_wait();  // a block must not leave while a peer may still be arriving at the start-up barrier
+    // a grid completes only after the grids before it: a block that found no work still waits
+    if (!waited) pdl_wait();
+}
+
+struct Plan {
+    SiteShape sh;
+    size_t smem;
+};
+
+// Shared-memory plan for `nsub` column groups
+Plan plan_for(int K, int parts, int max_rank, int total_rows, int nsub) {
+    Plan pl;
+    SiteShape& s = pl.sh;
+    s.kchunk = (((K + SITE_CLUSTER - 1) / SITE_CLUSTER) + 7) & ~7;
+    const int pieces = s.kchunk / 8;                          // 16-byte pieces per row
+    s.kb_pad = s.kchunk * 2 + ((pieces + 1) % 2 ? 16 : 32);   // an odd number of pieces between rows
+    s.rmax = parts * max_rank;
+    s.sp_pad = (s.rmax + 8) * 2;
+    s.g_rows = s.rmax < 64 ? s.rmax : 64;
+    const size_t a = (size_t)s.g_rows * s.kb_pad, wsum = (size_t)SITE_WARPS * PLORA_WORK_TOKENS * s.g_rows * 4;
+    s.g_stride = (int)(((a > wsum ? a : wsum) + 127) & ~(size_t)127);
+    s.aw_bytes = s.g_stride * ((s.rmax + 63) / 64);
+    s.x_bytes = (int)(((size_t)PLORA_WORK_TOKENS * s.kb_pad + 127) & ~(size_t)127);
+    const int share = ((total_rows + nsub * SITE_CLUSTER - 1) / (nsub * SITE_CLUSTER) + 1) & ~1;
+    // the tile loads of the last columns of a part may run up to 31 rows past the share
+    s.b_bytes = (int)((((size_t)share + 32 * parts) * max_rank * 2 + 127) & ~(size_t)127);
+    s.nsub = nsub;
+    pl.smem = (size_t)s.aw_bytes + s.x_bytes + s.b_bytes + (size_t)PLORA_WORK_TOKENS * s.rmax * 4 +
+              (size_t)4 * PLORA_WORK_TOKENS * s.sp_pad;
+    return pl;
 }
 
 }  // namespace
 
-// Shared-memory plan of the cluster kernel for one layer; returns 0 bytes when it does not fit.
-size_t plora_site_plan(int K, int parts, int max_rank, int total_rows, int* kchunk, int* rmax, int* a_bytes,
-                       int* x_bytes, int* b_bytes) {
-    const int kc = (((K + SITE_CLUSTER - 1) / SITE_CLUSTER) + 7) & ~7;
-    const int rm = parts * max_rank;
-    const int share = ((total_rows + SITE_CLUSTER - 1) / SITE_CLUSTER + 1) & ~1;
-    const size_t a = (size_t)rm * kc * 2, x = (size_t)PLORA_WORK_TOKENS * kc * 2;
-    const size_t b = ((size_t)share * max_rank * 2 + 127) & ~(size_t)127;
-    const size_t s = (size_t)2 * PLORA_WORK_TOKENS * rm * 4;
-    const size_t total = a + x + b + s;
-    if (total > 200 * 1024) return 0;
-    *kchunk = kc;
-    *rmax = rm;
-    *a_bytes = (int)a;
-    *x_bytes = (int)x;
-    *b_bytes = (int)b;
-    return total;
+// Plan of the cluster kernel for one layer: the fewest column groups (1, 2 or 4) with which two blocks share an
+// SM (one SM cannot take a whole cluster of 8, and a B200 has room for only 15 clusters of 8 at one block per
+// SM), else one block per SM with 4 groups. Returns the dynamic shared memory per block, 0 when nothing fits.
+size_t plora_site_plan(int K, int parts, int max_rank, int total_rows, int* nsub) {
+    if (parts * max_rank > 256) return 0;  // the shrink keeps at most 4 x 64 rows of A in flight per pass
+    for (int n = 1; n <= 4; n *= 2) {
+        const Plan pl = plan_for(K, parts, max_rank, total_rows, n);
+        if (pl.smem <= 111 * 1024) {
+            *nsub = n;
+            return pl.smem;
+        }
+    }
+    const Plan pl = plan_for(K, parts, max_rank, total_rows, 4);
+    if (pl.smem > 200 * 1024) return 0;
+    *nsub = 4;
+    return pl.smem;
 }
 
 cudaError_t plora_site_init() {
-    return cudaFuncSetAttribute(plora_site_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(plora_site_gather_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(plora_site_gather_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
 }
 
-cudaError_t plora_launch_site(const void* x, int ldx, int K, const int32_t* segs, SegLayout lay, const plora_desc* table,
-                              void* y, int ldy, int f32_out, int parts, int max_rank, int total_rows, int work_cap,
-                              int* status, bool pdl, cudaStream_t st) {
-    SiteShape sh;
-    const size_t smem = plora_site_plan(K, parts, max_rank, total_rows, &sh.kchunk, &sh.rmax, &sh.a_bytes, &sh.x_bytes,
-                                        &sh.b_bytes);
-    if (smem == 0) return cudaErrorInvalidValue;
+// How many clusters of the layer's plan the device runs at once (0 on failure)
+int plora_site_max_clusters(int K, int parts, int max_rank, int total_rows) {
+    int nsub = 1;
+    const size_t smem = plora_site_plan(K, parts, max_rank, total_rows, &nsub);
+    if (smem == 0) return 0;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(SITE_CLUSTER, 1, (unsigned)(work_cap < 128 ? work_cap : 128));
+    cfg.gridDim = dim3(SITE_CLUSTER, (unsigned)nsub, 16);
+    cfg.blockDim = dim3(SITE_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, plora_site_gather_kernel<false>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+cudaError_t plora_launch_site(const void* x, int ldx, int K, const PloraRec* recs, int rec_cap, const PloraRec* next_recs,
+                              void* y, int ldy, int f32_out, int parts, int max_rank, int total_rows, int work_cap,
+                              int max_clusters, bool early_x, int* status, bool pdl, cudaStream_t st) {
+    int nsub = 1;
+    const size_t smem = plora_site_plan(K, parts, max_rank, total_rows, &nsub);
+    if (smem == 0) return cudaErrorInvalidValue;
+    const Plan pl = plan_for(K, parts, max_rank, total_rows, nsub);
+    // one wave: work items beyond the clusters the device runs at once are walked in a loop, so that every block
+    // of the grid starts (and releases the next kernel) at once
+    int z = work_cap < PLORA_REC_TERM ? work_cap : PLORA_REC_TERM;
+    if (max_clusters >= nsub && z > max_clusters / nsub) z = max_clusters / nsub;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(SITE_CLUSTER, (unsigned)nsub, (unsigned)z);
     cfg.blockDim = dim3(SITE_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -339,6 +701,9 @@ cudaError_t plora_launch_site(const void* x, int ldx, int K, const int32_t* segs
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, plora_site_gather_kernel, reinterpret_cast<const bf16*>(x), ldx, K, segs, lay, table, y,
-                              ldy, f32_out, sh, status);
+    if (f32_out)
+        return cudaLaunchKernelEx(&cfg, plora_site_gather_kernel<true>, reinterpret_cast<const bf16*>(x), ldx, K, recs, rec_cap,
+                                  next_recs, y, ldy, pl.sh, early_x ? 1 : 0, status);
+    return cudaLaunchKernelEx(&cfg, plora_site_gather_kernel<false>, reinterpret_cast<const bf16*>(x), ldx, K, recs, rec_cap,
+                              next_recs, y, ldy, pl.sh, early_x ? 1 : 0, status);
 }

@@ -48,7 +48,7 @@ def to_dev_bf16(bits, device):
     return torch.from_numpy(bits.view(np.int16).copy()).to(f"cuda:{device}").view(torch.bfloat16)
 
 
-def run_gpu(pe, loras, wl, f32_out, meta="host", device=0, y_base=None, xs=None, fused=False):
+def run_gpu(pe, loras, wl, f32_out, meta="host", device=0, y_base=None, xs=None, fused=False, early_x=False):
     """All sites of the workload once; returns [y numpy per site] (f32 values; bf16 outputs widened)."""
     import torch
     torch.cuda.set_device(device)
@@ -61,8 +61,9 @@ def run_gpu(pe, loras, wl, f32_out, meta="host", device=0, y_base=None, xs=None,
         ss = torch.from_numpy(wl.row_slot.copy()).to(dev)
         loras.meta_build(cu.data_ptr(), ss.data_ptr(), wl.n_seqs, stream)
     step = loras.lora_step(loras.max_lora_tiles(), stream)
-    if fused:  # plora_apply: "early" = shrink/expand pair with early activation loads, "cluster" = one kernel per layer
+    if fused:  # plora_apply: "early" = the shrink / expand pair, "cluster" = one cluster kernel per layer
         loras.set_apply_mode(1 if fused == "cluster" else 0)
+        loras.set_early_x(early_x)  # the caller vouches for x (true here: x is a plain device copy made long before)
     outs = []
     for si in range(len(wl.sites)):
         xb = xs[si] if xs is not None else wl.x_bits(si)
@@ -132,13 +133,13 @@ def bf16_ulp_diff(a, b, pe, floor=2.0 ** -20):
     return d
 
 
-def run_and_check(pe, wl, device=0, f32_out=True, meta="host", run_min=None, fused=False):
+def run_and_check(pe, wl, device=0, f32_out=True, meta="host", run_min=None, fused=False, early_x=False):
     table, _ = oracle_registry(wl)
     loras = product_registry(pe, wl, device)
     if run_min is not None:
         loras.set_run_min(run_min)  # runs at least this long take the tensor-core tile kernels
     tiles = tiles_of(pe, wl)
-    ys = run_gpu(pe, loras, wl, f32_out, meta=meta, device=device, fused=fused)
+    ys = run_gpu(pe, loras, wl, f32_out, meta=meta, device=device, fused=fused, early_x=early_x)
     res = {}
     if f32_out:
         y64 = oracle_f64(wl, table, tiles)

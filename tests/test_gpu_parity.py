@@ -20,10 +20,11 @@ def test_plumbing_config_matches_the_oracle(pe, wls, meta, f32_out):
     harness.run_and_check(pe, wls.config1(), f32_out=f32_out, meta=meta)
 
 
-@pytest.mark.parametrize("fused", [False, "early", "cluster"], ids=["bracket", "apply-early", "apply-cluster"])
+@pytest.mark.parametrize("fused,early_x", [(False, False), ("early", False), ("cluster", False), ("early", True), ("cluster", True)],
+                         ids=["bracket", "apply-pair", "apply-cluster", "apply-pair-early-x", "apply-cluster-early-x"])
 @pytest.mark.parametrize("f32_out", [True, False])
-def test_decode_block_matches_the_oracle(pe, wls, f32_out, fused):
-    res = harness.run_and_check(pe, wls.config2(), f32_out=f32_out, meta="device", fused=fused)
+def test_decode_block_matches_the_oracle(pe, wls, f32_out, fused, early_x):
+    res = harness.run_and_check(pe, wls.config2(), f32_out=f32_out, meta="device", fused=fused, early_x=early_x)
     assert len(res) == 4
 
 
