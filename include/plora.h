@@ -234,6 +234,8 @@ int plora_meta_upload(plora_t* h, const int32_t* words, void* stream);
  * so the tensor-core tile kernels are neither fed nor launched. */
 int plora_step_begin(plora_t* h, int max_tiles, int decode, void* stream, plora_step* out);
 uint64_t plora_tiles_ptr(const plora_t* h);
+/* the step's launch records [sites][plora_max_lora_tiles-bounded] of 256 bytes each, for inspection */
+uint64_t plora_recs_ptr(const plora_t* h);
 
 /* ---- Linear::forward's bracket: src/linear.rs:428-443,844-921 ---- */
 
@@ -307,6 +309,10 @@ int plora_expand_reduced(plora_t* h, const plora_hook* hook, const plora_step* s
  * process). All ranks must then make the same sequence of plora_s_exchange calls on steps with identical
  * metadata; follow each with plora_expand_reduced. Graph-capturable: the call counter lives on the device. */
 int plora_exchange_create(plora_t* h, int world, int rank, int timeout_ms);
+/* Back to the state right after plora_exchange_create (flags and call counters zero, stream-ordered) after a
+ * wait ran out: the rank that timed out counted the call, the absent peer did not, so without this every later
+ * exchange would time out too. Every rank calls it; no rank starts its next plora_s_exchange before all have. */
+int plora_exchange_reset(plora_t* h, void* stream);
 int plora_exchange_export(plora_t* h, void* handle64);
 int plora_exchange_import(plora_t* h, int peer, const void* handle64);
 int plora_exchange_import_local(plora_t* h, int peer, plora_t* other);
@@ -333,17 +339,24 @@ int plora_set_tile_split(plora_t* h, int blocks);
 
 /* No counterpart in pocket-engine. One layer's adapter application (shrink, then expand, straight from the
  * engine's tile words and descriptor table) for callers that cannot allocate device memory: an engine whose
- * memory is fully claimed at start-up, code already inside a stream capture, a plugin host that forbids
- * allocation after initialisation. The f32 intermediate lives in a fixed 8 MiB device array inside the
+ * memory is fully claimed at start-up (a later cudaMalloc may fail), a plugin host that forbids allocation
+ * after initialisation. The f32 intermediate lives in a fixed 8 MiB device array inside the
  * library (held by every GPU that loads it, until exit), so this call allocates nothing. Calls with
  * nsplit * rows * lds * 4 bytes over plora_static_scratch_bytes() are rejected with PLORA_ERR_CAPACITY.
  * All calls on a device share that array: order them on the GPU, overlapping calls race. The first call on
- * a device resolves the array's address; make it outside any stream capture.
+ * a device resolves the array's address; make it before any stream capture begins.
  * x [rows, cols] bf16; tiles = [count,(start,len,slot) x count] i32; table = the layer's Desc table;
- * y [rows, ldy] bf16 or f32, updated in place. Error text: plora_static_error(). */
+ * y [rows, ldy] bf16 or f32, updated in place. Error text: plora_static_error().
+ * The tile words and descriptors are the caller's: every slot in the tile words must index `table`, and every
+ * part's width (Desc.rows) and offset (Desc.off) must be even, as the registry enforces for its own tables. The
+ * kernels check what they can see: a tile whose rows leave [0, rows), whose token count is not 1..16, whose slot
+ * is negative, or whose descriptor's ranks do not fit lds is skipped (y keeps its value for those tokens) and
+ * counted in plora_static_bad_tiles(). nsplit = plora_static_splits(cols). */
 int plora_site_apply_static(uint64_t x, int rows, int cols, uint64_t tiles, int max_tiles, uint64_t table, int parts,
                             int max_rows, int lds, uint64_t y, int ldy, int f32_out, void* stream);
 uint64_t plora_static_scratch_bytes(void);
+int plora_static_splits(int cols);
+long long plora_static_bad_tiles(void); /* refused tiles on the current device so far; waits for the device */
 const char* plora_static_error(void);
 
 /* Device status word: 0, or the PLORA_ERR_* a kernel recorded (bounded wait ran out, capacity).

@@ -146,6 +146,7 @@ SYMBOLS = {
     "plora_s_reduce": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _P]),
     "plora_expand_reduced": (_I, [_P, C.POINTER(Hook), C.POINTER(StepLora), _I, _U64, _I, _I, _P]),
     "plora_exchange_create": (_I, [_P, _I, _I, _I]),
+    "plora_exchange_reset": (_I, [_P, _P]),
     "plora_exchange_export": (_I, [_P, _P]),
     "plora_exchange_import": (_I, [_P, _I, _P]),
     "plora_exchange_import_local": (_I, [_P, _I, _P]),
@@ -159,6 +160,9 @@ SYMBOLS = {
     "plora_device_status": (_I, [_P]),
     "plora_site_apply_static": (_I, [_U64, _I, _I, _U64, _I, _U64, _I, _I, _I, _U64, _I, _I, _P]),
     "plora_static_scratch_bytes": (_U64, []),
+    "plora_static_splits": (_I, [_I]),
+    "plora_static_bad_tiles": (C.c_longlong, []),
+    "plora_recs_ptr": (_U64, [_P]),
     "plora_static_error": (C.c_char_p, []),
 }
 
@@ -592,6 +596,10 @@ class Loras:
     def exchange_create(self, world, rank, timeout_ms=2000):
         self._check(lib.plora_exchange_create(self._h, world, rank, timeout_ms))
 
+    def exchange_reset(self, stream=0):
+        """After a timed-out exchange: flags and call counters back to zero (every rank, then a barrier)."""
+        self._check(lib.plora_exchange_reset(self._h, _P(stream)))
+
     def exchange_export(self):
         """The 64-byte handle another process passes to exchange_import."""
         buf = C.create_string_buffer(64)
@@ -662,8 +670,8 @@ def s_exchange_all_ranks(ranks, hooks, steps, rows, stream=0):
 
 def site_apply_static(x, rows, cols, tiles, max_tiles, hook, lds, y, ldy, f32_out=False, stream=0):
     """One layer's shrink + expand for callers that cannot allocate device memory (an engine whose memory is
-    fully claimed at start-up, code inside a stream capture): the f32 intermediate sits in a fixed 8 MiB
-    array inside the library. Calls on one device must not overlap on the GPU; sizes over the array raise
+    fully claimed at start-up, a plugin host that forbids allocation): the f32 intermediate sits in a fixed
+    8 MiB array inside the library. Calls on one device must not overlap on the GPU; sizes over the array raise
     a capacity error. ``hook`` supplies the layer's descriptor table, part count and widest part."""
     rc = lib.plora_site_apply_static(x, rows, cols, tiles, max_tiles, hook.table, hook.parts, hook.max_rows, lds, y,
                                      ldy, int(f32_out), _P(stream))

@@ -1042,6 +1042,19 @@ int plora_exchange_create(plora_t* h, int world, int rank, int timeout_ms) {
     return PLORA_OK;
 }
 
+// After a wait ran out (a peer that never arrived), the ranks disagree on the call number: the rank that timed out
+// counted the call, the absent one did not. This puts one rank back to the state right after
+// plora_exchange_create: flags and call counters zero, stream-ordered. Every rank calls it, and no rank starts
+// its next plora_s_exchange before all have (a host-side barrier between the two): a peer's late store from
+// the failed call must not land after the reset.
+int plora_exchange_reset(plora_t* h, void* stream) {
+    if (!h) return PLORA_ERR_ARG;
+    if (!h->xchg) return fail(h, PLORA_ERR_ARG, "exchange not created");
+    CU(h, "reset exchange flags and counters",
+       cudaMemsetAsync(h->xchg + h->xchg_flags_off, 0, h->xchg_ctx_off - h->xchg_flags_off, as_stream(stream)));
+    return PLORA_OK;
+}
+
 int plora_exchange_export(plora_t* h, void* handle64) {
     if (!h || !handle64) return PLORA_ERR_ARG;
     if (!h->xchg) return fail(h, PLORA_ERR_ARG, "exchange not created");

@@ -196,6 +196,7 @@ __global__ void __launch_bounds__(1024) plora_meta_group_kernel(const int* __res
         int* mma = segs + lay.mma();
         for (int q = 0; q < nm; q++) {
             const int at = n_mma + excl + q;
+            if (at >= cap) break;  // tiles that overlap can add up to more rows than the step has: flagged below
             mma[3 * at] = start + q * PLORA_MMA_TOKENS;
             mma[3 * at + 1] = min(PLORA_MMA_TOKENS, len - q * PLORA_MMA_TOKENS);
             mma[3 * at + 2] = slot;
@@ -214,7 +215,11 @@ __global__ void __launch_bounds__(1024) plora_meta_group_kernel(const int* __res
         const int aidx = block_scan_excl(flag, n_act, sh);
         const int off = block_scan_excl(c, n_gather, sh);
         const int woff = block_scan_excl(nw, n_work, sh);
-        if (flag) {
+        // Tiles that overlap one another pass the per-tile checks but name more token rows than the step has: the
+        // regrouped rows would not fit their region. Such a list is refused as a whole.
+        if (n_gather > lay.max_tokens || n_work > cap || n_mma > cap) bad = true;
+        const bool over = n_gather > lay.max_tokens || n_work > cap || n_mma > cap;
+        if (flag && !over) {
             segs[lay.act() + aidx] = s;
             segs[lay.seg_off() + aidx] = off;
             seg_base[s] = off;
@@ -228,7 +233,8 @@ __global__ void __launch_bounds__(1024) plora_meta_group_kernel(const int* __res
             }
             cnt[s] = woff;  // from here on: the slot's first work item
         }
-        if (tid == 0) segs[lay.seg_off() + n_act] = n_gather;
+        if (tid == 0 && !over) segs[lay.seg_off() + n_act] = n_gather;
+        if (over) n_act = n_gather = n_work = n_mma = n_runs = 0;
     }
     __syncthreads();
 

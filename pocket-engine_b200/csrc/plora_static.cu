@@ -2,9 +2,8 @@
 // cannot allocate device memory.
 //
 // Who that is: a host that swaps this library's kernels into an engine whose memory is fully claimed at
-// start-up (pocket-engine sizes its pools once and never allocates inside Linear::forward), code that is
-// already inside a stream capture (cudaMalloc is illegal there), and plugin hosts that forbid their
-// plugins to allocate after initialisation. They still own x, y, the tile words and the descriptor table;
+// start-up (pocket-engine sizes its pools once and never allocates inside Linear::forward), so a later
+// cudaMalloc can simply fail, and plugin hosts that forbid their plugins to allocate after initialisation. They still own x, y, the tile words and the descriptor table;
 // what they lack is a place for the f32 intermediate S. Here that intermediate lives in a file-scope
 // device array of fixed size, so the entry point calls no cudaMalloc, cudaFree or any allocating routine.
 //
@@ -17,7 +16,7 @@
 //     slot's stacked A, each K-split) before the expand runs, so no clearing is done. Two calls whose
 //     kernels overlap on the GPU (different streams without ordering) race on it: order them.
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress) with that
-//     device current; make that first call outside any stream capture.
+//     device current; make that first call before any stream capture begins.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -33,6 +32,8 @@ typedef __nv_bfloat16 bf16;
 // In host code this name is only a stand-in for the symbol, never a device address: the address comes
 // from cudaGetSymbolAddress below.
 static __device__ __align__(256) float g_static_scratch[PLORA_STATIC_SCRATCH_BYTES / 4];
+// how many tiles the kernels refused since the library was loaded (see tile_ok); read by plora_static_bad_tiles
+static __device__ unsigned int g_static_bad_tiles = 0;
 
 namespace {
 
@@ -86,19 +87,42 @@ __device__ __forceinline__ float reduce16(float (&v)[16], int lane) {
     return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
 }
 
+// The tile words and the descriptor come from the caller, unchecked by any grouping kernel: a tile is used only
+// if its token rows lie inside [0, rows), it has 1..16 tokens, its slot is not negative and the slot's ranks fit
+// the intermediate's row (lds floats). A refused tile is skipped by both kernels (y keeps its value for those
+// tokens) and counted; nothing is read or written through its numbers.
+__device__ __forceinline__ bool tile_ok(int t0, int cnt, int slot, int rows) {
+    return t0 >= 0 && cnt >= 1 && cnt <= PLORA_TILE && t0 <= rows - cnt && slot >= 0;
+}
+__device__ __forceinline__ bool desc_ok(const plora_desc& d, int lds) {
+    if (d.rank < 0 || d.rank > lds) return false;
+#pragma unroll
+    for (int p = 0; p < PLORA_MAX_PARTS; p++)
+        if (d.r[p] < 0 || d.r_off[p] < 0 || d.r_off[p] + d.r[p] > d.rank || d.r[p] > lds / PLORA_MAX_PARTS || (d.r[p] & 7)) return false;
+    return true;
+}
+
 // Shrink straight from the engine's tile words: grid (tiles, K-splits), 128 threads. Writes
 // S[split][token][row] for every token of the tile and every row of the slot's stacked A.
 __global__ void __launch_bounds__(128) plora_static_shrink_kernel(const bf16* __restrict__ X, int ldx, int K,
                                                                    const int* __restrict__ tiles,
                                                                    const plora_desc* __restrict__ table,
                                                                    float* __restrict__ S, size_t s_stride, int lds,
-                                                                   int kchunk) {
+                                                                   int kchunk, int rows) {
     const int w = blockIdx.x;
     if (w >= tiles[0]) return;
     const int t0 = tiles[1 + 3 * w], cnt = tiles[2 + 3 * w], slot = tiles[3 + 3 * w];
+    if (!tile_ok(t0, cnt, slot, rows)) {
+        if (threadIdx.x == 0 && blockIdx.y == 0) atomicAdd(&g_static_bad_tiles, 1u);
+        return;
+    }
     const plora_desc& d = table[slot];
     const int rank = d.rank;
     if (rank == 0) return;
+    if (!desc_ok(d, lds)) {
+        if (threadIdx.x == 0 && blockIdx.y == 0) atomicAdd(&g_static_bad_tiles, 1u);
+        return;
+    }
     const bf16* A = reinterpret_cast<const bf16*>(d.a);
     const int k0 = blockIdx.y * kchunk, k1 = min(K, k0 + kchunk);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -142,16 +166,19 @@ __global__ void __launch_bounds__(128) plora_static_shrink_kernel(const bf16* __
 __global__ void __launch_bounds__(128) plora_static_expand_kernel(const float* __restrict__ S, size_t s_stride,
                                                                    int lds, int nsplit, const int* __restrict__ tiles,
                                                                    const plora_desc* __restrict__ table, void* Y,
-                                                                   int ldy, int f32_out) {
+                                                                   int ldy, int f32_out, int n_rows) {
     extern __shared__ float ss[];  // [16][r]
     const int w = blockIdx.x;
     if (w >= tiles[0]) return;
     const int t0 = tiles[1 + 3 * w], cnt = tiles[2 + 3 * w], slot = tiles[3 + 3 * w];
+    if (!tile_ok(t0, cnt, slot, n_rows)) return;  // counted by the shrink
     const plora_desc& d = table[slot];
+    if (d.rank == 0 || !desc_ok(d, lds)) return;
     const int p = blockIdx.z, r = d.r[p];
     if (r == 0) return;
-    const int rows = d.rows[p], c0 = blockIdx.y * 256;
-    if (c0 >= rows) return;
+    // two columns per thread: a part's width and offset must be even (the registry enforces it for its own tables)
+    const int rows = d.rows[p] & ~1, c0 = blockIdx.y * 256;
+    if (c0 >= rows || (d.off[p] & 1) || d.off[p] < 0 || d.off[p] + d.rows[p] > ldy) return;
     const int r_off = d.r_off[p];
     for (int i = threadIdx.x; i < cnt * r; i += 128) {
         const int t = i / r, j = i - t * r;
@@ -218,6 +245,23 @@ uint64_t plora_static_scratch_bytes(void) { return PLORA_STATIC_SCRATCH_BYTES; }
 
 const char* plora_static_error(void) { return g_static_err.c_str(); }
 
+// Tiles refused on the current device since the library was loaded (a bad row range, token count, slot or
+// descriptor). Waits for the device; allocates nothing. -1 on a CUDA error.
+long long plora_static_bad_tiles(void) {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_static_bad_tiles, sizeof(v)) != cudaSuccess) return -1;
+    return (long long)v;
+}
+
+// K-splits of the intermediate for a layer of `cols` inputs: a call needs splits * rows * lds * 4 bytes of scratch
+int plora_static_splits(int cols) {
+    if (cols <= 0) return 0;
+    const int few = cols + 511 < 512 * 16 ? (cols + 511) / 512 : 16;
+    const int want = (cols + 2047) / 2048 > few ? (cols + 2047) / 2048 : few;
+    const int kchunk = ((cols + want - 1) / want + 255) / 256 * 256;
+    return (cols + kchunk - 1) / kchunk;
+}
+
 int plora_site_apply_static(uint64_t x, int rows, int cols, uint64_t tiles, int max_tiles, uint64_t table, int parts,
                             int max_rows, int lds, uint64_t y, int ldy, int f32_out, void* stream) {
     if (!x || !tiles || !table || !y) return sfail(PLORA_ERR_ARG, "null device address");
@@ -245,13 +289,13 @@ int plora_site_apply_static(uint64_t x, int rows, int cols, uint64_t tiles, int 
     const size_t s_stride = (size_t)rows * (size_t)lds;
     plora_static_shrink_kernel<<<dim3((unsigned)ntiles, (unsigned)nsplit), 128, 0, st>>>(
         reinterpret_cast<const bf16*>(x), cols, cols, reinterpret_cast<const int*>(tiles),
-        reinterpret_cast<const plora_desc*>(table), S, s_stride, lds, kchunk);
+        reinterpret_cast<const plora_desc*>(table), S, s_stride, lds, kchunk, rows);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return sfail(PLORA_ERR_CUDA, std::string("shrink: ") + cudaGetErrorString(e));
     const size_t smem = (size_t)16 * (size_t)(lds / PLORA_MAX_PARTS) * 4;
     plora_static_expand_kernel<<<dim3((unsigned)ntiles, (unsigned)((max_rows + 255) / 256), (unsigned)parts), 128, smem, st>>>(
         S, s_stride, lds, nsplit, reinterpret_cast<const int*>(tiles), reinterpret_cast<const plora_desc*>(table),
-        reinterpret_cast<void*>(y), ldy, f32_out);
+        reinterpret_cast<void*>(y), ldy, f32_out, rows);
     e = cudaGetLastError();
     if (e != cudaSuccess) return sfail(PLORA_ERR_CUDA, std::string("expand: ") + cudaGetErrorString(e));
     return PLORA_OK;

@@ -336,6 +336,15 @@ def test_capacity_errors_are_reported_not_faulted(pe):
     with pytest.raises(pe.PloraError) as e:
         loras.device_status()
     assert e.value.code == pe.ERR_ARG
+    # tiles that overlap one another: each is fine by itself, together they name more rows than the step has
+    loras.meta_upload(np.array([8] + [0, 16, 1] * 4 + [16, 16, 2] * 4, np.int32))
+    loras.lora_step(8)
+    with pytest.raises(pe.PloraError) as e:
+        loras.device_status()
+    assert e.value.code == pe.ERR_ARG
+    loras.meta_upload(np.array([2, 0, 16, 1, 16, 16, 2], np.int32))  # the same rows once: accepted
+    loras.lora_step(8)
+    loras.device_status()
     loras.close()
 
 

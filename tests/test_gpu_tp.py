@@ -130,5 +130,24 @@ def test_exchange_wait_runs_out_and_reports(pe, wls):
     assert err.value.code == pe.ERR_TIMEOUT
     L.device_status()  # the word was cleared and the context still answers
     assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
+    # rank 0 counted the failed call, rank 1 did not: without a reset every later exchange would time out as well
+    for R in ranks:
+        R.exchange_reset(stream)
+    torch.cuda.synchronize()
+    steps, hooks, xs = [], [], []
+    for R, shd in zip(ranks, shards):
+        R.meta_upload(pe.fill_tiles(shd.row_n, shd.row_slot, R.max_lora_tiles()), stream)
+        steps.append(R.lora_step(R.max_lora_tiles(), stream))
+        hooks.append(R.hook(si))
+        xs.append(harness.to_dev_bf16(shd.x_bits(si), 0))
+        R.shrink(hooks[-1], steps[-1], xs[-1].data_ptr(), wl.tokens, stream)
+    pe.s_exchange_all_ranks(ranks, hooks, steps, wl.tokens, stream)
+    torch.cuda.synchronize()
+    for R in ranks:
+        R.device_status()
+    # both ranks now hold the same, complete sums: plane 0 of S, bit for bit
+    s0 = harness.dev_read(ranks[0].s, wl.tokens * ranks[0].lds * 4)
+    s1 = harness.dev_read(ranks[1].s, wl.tokens * ranks[1].lds * 4)
+    assert np.array_equal(s0, s1) and np.any(s0 != 0)
     for R in ranks:
         R.close()
