@@ -42,8 +42,9 @@ def peaks():
 PREFILL_SEQS = 8
 
 
-def make_workload(name, seed):
-    from pocket_engine_b200 import workloads
+def make_workload(name, seed, workloads=None):
+    if workloads is None:
+        from pocket_engine_b200 import workloads
     if name == "decode":
         return workloads.config2(seed=seed)
     if name == "prefill":
@@ -94,6 +95,17 @@ class ClockSampler:
         os.unlink(self.f.name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def shared_config(wl, work):
+    """What both arms print as `config`: the workload, and how each arm keeps its inputs out of the caches."""
+    return {"workload": wl.name, "tokens_per_step": wl.tokens, "lora_tokens": work["lora_tokens"], "adapters": wl.n_adapters,
+            "slots_present": work["slots_present"], "sites": len(wl.sites),
+            "partitioning": "adapter-affine, one batch per GPU, no collective",
+            "l2": "inputs larger than L2: the GPU arm rotates over copies of pool + x + y of >= 512 MiB in total (126 MB L2); "
+                  "the CPU arm streams its one copy (49 MB), larger than the host's L2",
+            "metadata": "the step's grouping and launch records (built once per step and shared by all layers of a model) "
+                        "run outside the device-timed `value` and inside `e2e`; their time is reported as meta_us"}
 
 
 # ------------------------------------------------------------------------------------- ours
@@ -214,7 +226,9 @@ def run_ours(args, rank, world, local_rank):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident timing: K graph replays
+    # ---- device-resident timing: K steps, each `inner` passes of the block (graph replays over the rotating copies),
+    # so that the timed region is long against launch and event jitter; reported per single pass
+    inner = max(1, args.inner_repeats) if decode else 1
     with torch.cuda.stream(main):
         for i in range(args.warmup):
             graphs[i % copies].replay()
@@ -222,11 +236,11 @@ def run_ours(args, rank, world, local_rank):
         sampler = ClockSampler(local_rank) if rank == 0 else None
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(main)
-        for i in range(args.steps):
+        for i in range(args.steps * inner):
             graphs[(args.warmup + i) % copies].replay()
         e1.record(main)
         barrier()
-        ms = e0.elapsed_time(e1)
+        ms = e0.elapsed_time(e1) / inner
     # keep the sampler alive a little longer for short runs so it sees load
     if sampler is not None and ms < 400:
         with torch.cuda.stream(main):
@@ -344,16 +358,14 @@ def run_ours(args, rank, world, local_rank):
         "metric": METRIC, "value": world * wl.tokens * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": wl.name, "tokens_per_step": wl.tokens, "lora_tokens": work["lora_tokens"],
-                   "adapters": wl.n_adapters, "slots_present": work["slots_present"], "sites": ns,
-                   "l2": f"inputs larger than L2: {copies} rotating copies of pool+x+y = "
-                         f"{copies * (pool_bytes + d2h + h2d // 2) / 2 ** 20:.0f} MiB",
-                   "partitioning": "adapter-affine, one batch per GPU, no collective",
-                   "graph": f"one CUDA graph per copy, {args.streams} stream(s)", "path": args.path,
-                   "early_x": bool(args.early_x)},
+        "config": shared_config(wl, work),
+        "run": {"copies": copies, "rotating_mib": round(copies * (pool_bytes + d2h + h2d // 2) / 2 ** 20),
+                "graph": f"one CUDA graph per copy, {args.streams} stream(s)", "path": args.path,
+                "early_x": bool(args.early_x), "inner_repeats": inner,
+                "timed_region": f"{args.steps} steps x {inner} passes of the block; value and ms_per_step are per pass"},
         "e2e": {"value": world * wl.tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps, "steps_in_flight": depth},
-        "gpu_launches": ((4 if args.path == "apply" else 8) if decode else 16) * args.steps,
+        "gpu_launches": ((4 if args.path == "apply" else 8) if decode else 16) * args.steps * inner,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                      "peak_kind": peak_kind, "traffic": NCU_TRAFFIC.get((wl.name, dom)), "us_per_launch": kern[dom]["us"],
                      "algorithmic_bytes_per_launch": kern[dom]["bytes"]},
@@ -591,11 +603,14 @@ def run_fused_bf16(args, rank, world, local_rank):
             "clocks": clocks}
 
 
-def run_tp(args, rank, world, local_rank):
+def tp_measure(args, rank, world, local_rank, exchanges, steps, warmup):
     """Tensor-parallel 27B-shaped layer set (q, o, gate/up, down; hidden 5120, intermediate 17408), 512 tokens,
-    32 rank-32 adapters: column-parallel q and gate/up, row-parallel o and down with an NCCL all-reduce of the
-    [512, 32] shrink partials. Strong scaling: the same batch over more GPUs."""
+    32 rank-32 adapters: column-parallel q and gate/up, row-parallel o and down whose [512, 32] shrink partials are
+    summed over the ranks, per `exchanges`: "nccl" = an NCCL all-reduce, "fused" = the library's one-kernel exchange
+    over peer memory. Strong scaling: the same batch over more GPUs. Returns {exchange: record}; every record carries
+    a parity check of sampled token rows against the unsharded fp64 oracle (rank 0, outside the timed region)."""
     import torch
+    import torch.distributed as dist
     pe = entry.load_package()
     from pocket_engine_b200 import tp, workloads
     torch.cuda.set_device(local_rank)
@@ -604,97 +619,156 @@ def run_tp(args, rank, world, local_rank):
     sh = tp.ShardedWorkload(wl, world, rank)
     ns = len(sh.sites)
     copies = args.copies or 4
+    facs = [sh.factors(i) for i in range(sh.n_adapters)]
+    x_h = [sh.x_bits(si) for si in range(ns)]
+    y_h = [sh.y_base(si) for si in range(ns)]
     sets = []
     for c in range(copies):
         L = pe.Loras(sh.sites, sh.n_adapters, sh.max_rank, sh.tokens, sh.n_seqs, device=local_rank)
         prep = L.prep()
         for i in range(sh.n_adapters):
-            L.upload(i + 1, L.insert(prep.prepare(f"a{i}", sh.factors(i))))
-        x = [torch.from_numpy(sh.x_bits(si).view(np.int16)).to(dev).view(torch.bfloat16) for si in range(ns)]
-        y = [torch.from_numpy(pe.bf16_bits(sh.y_base(si)).reshape(sh.tokens, -1).view(np.int16)).to(dev).view(torch.bfloat16)
+            L.upload(i + 1, L.insert(prep.prepare(f"a{i}", facs[i])))
+        x = [torch.from_numpy(x_h[si].view(np.int16)).to(dev).view(torch.bfloat16) for si in range(ns)]
+        y = [torch.from_numpy(pe.bf16_bits(y_h[si]).reshape(sh.tokens, -1).view(np.int16)).to(dev).view(torch.bfloat16)
              for si in range(ns)]
         L.meta_upload(pe.fill_tiles(sh.row_n, sh.row_slot, L.max_lora_tiles()))
         step = L.lora_step(L.max_lora_tiles())
-        if args.exchange == "fused":
+        if "fused" in exchanges:
             tp.connect_exchange(L, rank, world)
-        lins = [tp.TPLinear(L, si, sh.modes[si], exchange=args.exchange) for si in range(ns)]
-        sets.append({"L": L, "x": x, "y": y, "step": step, "lins": lins})
+        sets.append({"L": L, "x": x, "y": y, "step": step})
     torch.cuda.synchronize()
-    stream = torch.cuda.current_stream()
-
-    def block(i):
-        S = sets[i % copies]
-        for si in range(ns):
-            S["lins"][si].forward(S["x"][si].data_ptr(), sh.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1], False,
-                                  lora=S["step"], main=stream.cuda_stream)
 
     def barrier():
-        if world > 1:
-            torch.distributed.barrier()
+        dist.barrier()
         torch.cuda.synchronize()
 
-    # one CUDA graph per copy (kernels and the NCCL all-reduces), replayed; eager launches if capture is refused
-    mode = "cuda graph per copy"
-    cap = torch.cuda.Stream(device=dev)
-    graphs = []
-    try:
-        with torch.cuda.stream(cap):
-            for c in range(copies):
-                block(c)
-            torch.cuda.synchronize()
-            real = stream
-            stream = cap
-            for c in range(copies):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=cap):
-                    block(c)
-                graphs.append(g)
-            torch.cuda.synchronize()
-        run = lambda i: graphs[i % copies].replay()
-    except Exception as e:  # noqa: BLE001
-        mode = f"eager launches (graph capture refused: {type(e).__name__})"
+    # sampled rows for the parity check: the first and last rows of the prompt chunks, and decode rows
+    rng = np.random.default_rng(17)
+    cu = wl.cu()
+    rows = set(int(v) for v in rng.choice(wl.tokens, 56, replace=False))
+    for i, n in enumerate(wl.row_n):
+        if n > 1:
+            rows.update([int(cu[i]), int(cu[i + 1]) - 1, int(cu[i]) + 15, int(cu[i]) + 16])
+    rows = np.array(sorted(rows), np.int64)
+    y32 = [torch.from_numpy(y_h[si].copy()).to(dev) for si in range(ns)]
+    orc = entry.load_oracle() if rank == 0 else None  # the checker of the parity record, never the thing timed
+    full_adapters = [orc.OracleAdapter(wl.sites, wl.factors(i), wl.max_rank) for i in range(wl.n_adapters)] if rank == 0 else []
+    peak, kind, _ = peaks()
+    shw = workloads.Workload(sh.name, sh.sites, sh.ranks, sh.scale, sh.row_n, sh.row_slot, sh.seed).work()
+    out = {}
+    for exchange in exchanges:
+        for S in sets:
+            S["lins"] = [tp.TPLinear(S["L"], si, sh.modes[si], exchange=exchange) for si in range(ns)]
         stream = torch.cuda.current_stream()
+
+        def block(i, stream_handle=None):
+            S = sets[i % copies]
+            for si in range(ns):
+                S["lins"][si].forward(S["x"][si].data_ptr(), sh.tokens, S["y"][si].data_ptr(), S["y"][si].shape[1], False,
+                                      lora=S["step"], main=stream_handle if stream_handle is not None else stream.cuda_stream)
+
+        # one CUDA graph per copy (kernels and the collectives), replayed; eager launches if capture is refused
+        mode = "cuda graph per copy"
+        cap = torch.cuda.Stream(device=dev)
         graphs = []
-        run = block
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    ms = _event_time(torch, stream, run, args.steps, args.warmup, barrier)
-    # the collective alone: all-reduce of one [512, lds] plane
-    s0 = sets[0]["lins"][1]._s[:sh.tokens]
-    if world == 1:
-        ar = 0.0
-    elif args.exchange == "fused":  # the exchange kernel alone (partials left over from the last step)
-        L0, lin0 = sets[0]["L"], sets[0]["lins"][1]
-        ar = _event_time(torch, stream, lambda i: L0.s_exchange(lin0.lora, sets[0]["step"], sh.tokens, stream.cuda_stream),
-                         50, 5, barrier) / 50
-    else:
-        ar = _event_time(torch, stream, lambda i: torch.distributed.all_reduce(s0), 50, 5, barrier) / 50
-    clocks = sampler.stop() if sampler is not None else None
+        try:
+            with torch.cuda.stream(cap):
+                for c in range(copies):
+                    block(c, cap.cuda_stream)
+                torch.cuda.synchronize()
+                for c in range(copies):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=cap):
+                        block(c, cap.cuda_stream)
+                    graphs.append(g)
+                torch.cuda.synchronize()
+            stream = cap
+            run = lambda i: graphs[i % copies].replay()  # noqa: E731
+        except Exception as e:  # noqa: BLE001
+            mode = f"eager launches (graph capture refused: {type(e).__name__})"
+            stream = torch.cuda.current_stream()
+            graphs = []
+            run = block
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        ms = _event_time(torch, stream, run, steps, warmup, barrier)
+        # the collective alone: one [512, lds] plane
+        s0 = sets[0]["lins"][1]._s[:sh.tokens]
+        if world == 1:
+            ar = 0.0
+        elif exchange == "fused":  # the exchange kernel alone (partials left over from the last step)
+            L0, lin0 = sets[0]["L"], sets[0]["lins"][1]
+            ar = _event_time(torch, stream, lambda i: L0.s_exchange(lin0.lora, sets[0]["step"], sh.tokens, stream.cuda_stream),
+                             50, 5, barrier) / 50
+        else:
+            ar = _event_time(torch, stream, lambda i: dist.all_reduce(s0), 50, 5, barrier) / 50
+        clocks = sampler.stop() if sampler is not None else None
+        # parity: one pass in f32 on fresh outputs, sampled rows of every layer gathered on rank 0
+        S = sets[0]
+        worst = [0.0, 0.0]
+        cur = torch.cuda.current_stream()
+        for si in range(ns):
+            y = y32[si].clone()
+            S["lins"][si].forward(S["x"][si].data_ptr(), sh.tokens, y.data_ptr(), y.shape[1], True, lora=S["step"],
+                                  main=cur.cuda_stream)
+            torch.cuda.synchronize()
+            outs = [None] * world
+            dist.all_gather_object(outs, y[torch.from_numpy(rows).to(dev)].cpu().numpy())
+            if rank == 0:
+                got = sh.assemble(si, outs)
+                table = orc.OracleTable(wl.sites, wl.n_adapters)
+                for i, a in enumerate(full_adapters):
+                    table.upload(i + 1, a)
+                tslot = wl.token_slot()[rows]
+                words = [int((tslot > 0).sum())]
+                for i, sl in enumerate(tslot):
+                    if sl:
+                        words += [i, 1, int(sl)]
+                want = wl.y_base(si)[rows].astype(np.float64)
+                orc.site_f64(np.ascontiguousarray(wl.x_bits(si)[rows]), wl.sites[si].cols, np.array(words, np.int32),
+                             table.tables[si], want)
+                d = np.abs(got - want)
+                rms = float(np.sqrt(np.mean(want ** 2)))
+                worst = [max(worst[0], float(d.max()) / rms), max(worst[1], float(d.mean()) / rms)]
+        for S2 in sets:
+            S2["L"].device_status()
+        t = torch.tensor([ms, ar], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ar = float(t[0]), float(t[1])
+        us = 1e3 * ms / steps
+        out[exchange] = {
+            "ms_per_step": ms / steps, "tokens_per_s": sh.tokens * steps / (ms * 1e-3), "steps": steps, "warmup": warmup,
+            "collective_us": 1e3 * ar, "collective_bytes": int(sh.tokens * sets[0]["L"].lds * 4),
+            "collective": ("one exchange kernel per row-parallel layer: partials stored to every rank's staging memory over "
+                           "NVLink, flags, sum in rank order" if exchange == "fused" else
+                           "NCCL all-reduce(sum) of the f32 shrink partials") + ", 2 per step",
+            "step_roofline": {"algorithmic_bytes_per_step_per_gpu": shw["bytes"],
+                              "achieved_gbs_per_gpu": shw["bytes"] / (us * 1e-6) / 1e9,
+                              "frac": shw["bytes"] / (us * 1e-6) / 1e9 / peak, "us_per_step": us},
+            "parity": {"against": "unsharded fp64 oracle", "sampled_token_rows": int(len(rows)), "layers": ns,
+                       "max_over_rms": worst[0], "mean_over_rms": worst[1],
+                       "ok": bool(worst[0] <= 1e-2 and worst[1] <= 1e-3), "tolerance": "max 1e-2, mean 1e-3 of RMS(y)"},
+            "launch": mode, "clocks": clocks}
+        del graphs
+    info = {"workload": wl.name, "tokens_per_step": sh.tokens, "adapters": sh.n_adapters, "scaling": "strong",
+            "parallelism": f"tp{world}: column-parallel q, gate/up; row-parallel o, down", "l2": f"{copies} rotating copies"}
     for S in sets:
-        S["L"].device_status()
-    t = torch.tensor([ms, ar], device=dev, dtype=torch.float64)
-    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    ms, ar = float(t[0]), float(t[1])
+        S["L"].close()
+    return info, out
+
+
+def run_tp(args, rank, world, local_rank):
+    """--workload tp: the tensor-parallel layer set alone, with the chosen exchange."""
+    info, out = tp_measure(args, rank, world, local_rank, [args.exchange], args.steps, args.warmup)
     if rank != 0:
         return None
-    # per-GPU algorithmic bytes of the rank's shard
-    shw = workloads.Workload(sh.name, sh.sites, sh.ranks, sh.scale, sh.row_n, sh.row_slot, sh.seed).work()
-    peak, kind, _ = peaks()
-    us = 1e3 * ms / args.steps
-    return {"metric": METRIC, "value": sh.tokens * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl.name, "tokens_per_step": sh.tokens, "adapters": sh.n_adapters,
-                       "parallelism": f"tp{world}: column-parallel q, gate/up; row-parallel o, down",
-                       "collective": ("one exchange kernel per row-parallel layer: partials stored to every rank's staging "
-                                      "memory over NVLink, flags, sum in rank order" if args.exchange == "fused" else
-                                      "NCCL all-reduce(sum) of the f32 shrink partials") + ", 2 per step",
-                       "launch": mode,
-                       "l2": f"{copies} rotating copies"},
-            "gpu_launches": (2 * ns + 2) * 2 * args.steps,
-            "step_roofline": {"algorithmic_bytes_per_step_per_gpu": shw["bytes"], "achieved_gbs_per_gpu": shw["bytes"] / (us * 1e-6) / 1e9,
-                              "frac": shw["bytes"] / (us * 1e-6) / 1e9 / peak, "us_per_step": us},
-            "collective_us": 1e3 * ar, "collective_bytes": int(sh.tokens * sets[0]["L"].lds * 4),
-            "clocks": clocks}
+    r = out[args.exchange]
+    return {"metric": METRIC, "value": r["tokens_per_s"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(info, collective=r["collective"], launch=r["launch"]),
+            "gpu_launches": (2 * 4 + 2) * 2 * args.steps, "step_roofline": r["step_roofline"],
+            "collective_us": r["collective_us"], "collective_bytes": r["collective_bytes"], "parity": r["parity"],
+            "clocks": r["clocks"]}
 
 
 # -------------------------------------------------------------------------------- CPU port
@@ -704,18 +778,18 @@ def cpu_port(wl_name, seconds, seed=0, threads=0, steps=None, warmup=0):
     (tokens/s, cores, sample description, ms per step). The prefill workload is sampled: one of its eight
     sequences (same shapes, one adapter), tokens/s counted on the tokens actually processed."""
     orc = entry.load_oracle()
-    pe = entry.load_package()  # only the synthetic inputs and the tile rule (host arithmetic)
-    wl = make_workload(wl_name, seed)
+    workloads = entry.load_inputs()  # the synthetic inputs only: the product library is not loaded by this arm
+    bits = sys.modules["plora_inputs.sites"].bf16_bits
+    wl = make_workload(wl_name, seed, workloads)
     full_name = wl.name
     if wl_name == "prefill":
-        from pocket_engine_b200 import workloads
         wl = workloads.config3(seed=seed, seqs=1)
     table = orc.OracleTable(wl.sites, wl.n_adapters)
     for i in range(wl.n_adapters):
         table.upload(i + 1, orc.OracleAdapter(wl.sites, wl.factors(i), wl.max_rank))
     tiles = orc.fill_tiles(wl.row_n, wl.row_slot, wl.tokens // 16 + wl.n_seqs)
     xs = [wl.x_bits(si) for si in range(len(wl.sites))]
-    ys = [pe.bf16_bits(wl.y_base(si)).reshape(wl.tokens, -1) for si in range(len(wl.sites))]
+    ys = [bits(wl.y_base(si)).reshape(wl.tokens, -1) for si in range(len(wl.sites))]
     s = np.zeros((wl.tokens, 4 * ((wl.max_rank + 15) // 16 * 16)), np.float32)
     threads = threads or orc.hw_threads()
 
@@ -743,9 +817,10 @@ def run_reference(args, rank, world):
     if rank != 0:
         return None
     v, cores, sample, ms, wl = cpu_port(args.workload, 0, steps=args.steps, warmup=args.warmup)
+    wl = make_workload(args.workload, 0, entry.load_inputs())  # `config` names the whole workload (the sample says what ran)
     out = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": world, "steps": args.steps,
            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-           "dtype": "f32", "data": "synthetic", "config": {"workload": wl.name, "tokens_per_step": wl.tokens},
+           "dtype": "f32", "data": "synthetic", "config": shared_config(wl, wl.work()),
            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "note": "pocket-engine has no CPU path; this arm times the C port of its algorithm on the host cores"}
@@ -775,8 +850,9 @@ def reference_gpu(args, image=None):
     if not torch.cuda.is_available():
         return {"unavailable": "no GPU"}
     orc = entry.load_oracle()
-    pe = entry.load_package()  # synthetic inputs and bf16 helpers only
-    wl = make_workload(args.workload, 0)
+    workloads = entry.load_inputs()
+    bits = sys.modules["plora_inputs.sites"].bf16_bits
+    wl = make_workload(args.workload, 0, workloads)
     torch.cuda.set_device(0)
     ref = rk.RefKernels(image)
     max_rank = (wl.max_rank + 15) // 16 * 16
@@ -798,7 +874,7 @@ def reference_gpu(args, image=None):
         for i, a in enumerate(adapters):
             pool[i * slot_bytes:i * slot_bytes + a.len].copy_(torch.from_numpy(a.data[:a.len]))
         x = [torch.from_numpy(wl.x_bits(si).view(np.int16)).cuda() for si in range(len(wl.sites))]
-        y = [torch.from_numpy(pe.bf16_bits(wl.y_base(si)).reshape(wl.tokens, -1).view(np.int16)).cuda()
+        y = [torch.from_numpy(bits(wl.y_base(si)).reshape(wl.tokens, -1).view(np.int16)).cuda()
              for si in range(len(wl.sites))]
         sets.append({"pool": pool, "tabs": tabs, "x": x, "y": y, "tiles": torch.from_numpy(tiles_h.copy()).cuda(),
                      "s": torch.zeros(2, wl.tokens, lds, dtype=torch.float32, device="cuda")})
@@ -870,6 +946,9 @@ def main():
                          "expand-after bracket (plora_shrink, plora_expand)")
     ap.add_argument("--early-x", action="store_true",
                     help="plora_set_early_x(1): the caller vouches for x, which is then read ahead of the dependency wait")
+    ap.add_argument("--inner-repeats", type=int, default=50,
+                    help="decode workload: passes of the block per timed step (the result is reported per pass)")
+    ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel layer set that the default run appends")
     ap.add_argument("--streams", type=int, default=1, choices=[1, 2],
                     help="1: one stream, kernels chained by programmatic dependent launch; 2: the engine's "
                          "side-stream shrink with fork/join events")
@@ -891,7 +970,8 @@ def main():
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU fallback")
-    if world > 1 or args.workload == "tp":
+    with_tp = args.workload == "decode" and not args.no_tp  # the default run appends the tensor-parallel layer set
+    if world > 1 or args.workload == "tp" or with_tp:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29533")
         torch.distributed.init_process_group("nccl", rank=rank, world_size=world,
@@ -905,11 +985,36 @@ def main():
             torch.distributed.destroy_process_group()
         return
     out = run_ours(args, rank, world, local_rank)
+    if with_tp:
+        # configs[4] of the benchmark definition: NCCL all-reduce (the primary form) and, on more than one GPU, the
+        # library's own exchange kernel; strong scaling, so its numbers sit beside the headline, not in `value`
+        try:
+            info, tp_out = tp_measure(args, rank, world, local_rank, ["nccl", "fused"] if world > 1 else ["nccl"],
+                                      max(10, min(args.steps, 50)), 5)
+            if rank == 0:
+                out["tp"] = dict(info, **tp_out)
+        except Exception as e:  # noqa: BLE001  (the headline line must still be printed)
+            if rank == 0:
+                out["tp"] = {"failed": f"{type(e).__name__}: {e}"[:300]}
+    # The CPU baseline runs on rank 0 while the other ranks sleep on a store key (a collective barrier would have
+    # them spin on the cores the baseline is timed on).
+    store = None
+    if torch.distributed.is_initialized():
+        torch.cuda.synchronize()
+        try:
+            store = torch.distributed.distributed_c10d._get_default_store()
+        except Exception:  # noqa: BLE001
+            store = None
     if rank == 0:
         v, cores, sample, _, _ = cpu_port(args.workload, args.cpu_seconds)
         out["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        if store is not None:
+            store.set("plora_cpu_baseline_done", "1")
         print(json.dumps(out))
-    if world > 1:
+    elif store is not None:
+        import datetime
+        store.wait(["plora_cpu_baseline_done"], datetime.timedelta(seconds=900))
+    if torch.distributed.is_initialized():
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
 

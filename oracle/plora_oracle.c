@@ -426,25 +426,57 @@ void po_site_f32s(const uint16_t* X, int ldx, int K, const int32_t* tiles, const
     site_apply(X, ldx, K, tiles, table, Y, ldy, MODE_F32S, f32_out);
 }
 
-/* ---- multithreaded f32 implementation: the timed CPU baseline ---- */
+/* ---- multithreaded f32 implementation: the timed CPU baseline ----
+ * Same math as lora_shrink / lora_expand (src/kernels/lora.cuh:23-126) with f32 accumulation, laid out for a CPU:
+ * the tokens are grouped by slot first, so a row of A or of B is read once per slot and applied to all of the
+ * slot's tokens while it sits in the core's cache; the work units (slot x row of A for the shrink, slot x part x
+ * 64-column block for the expand) are dealt to a pool of threads that lives across calls; the two phases of a
+ * call are separated by a barrier. */
 
 typedef struct {
     const uint16_t* X;
     int ldx, K;
-    const int32_t* tiles;
     const po_desc* table;
     float* S;
     int lds;
     void* Y;
     int ldy, f32_out;
-    int tid, nthreads;
-    int phase;
-    /* flattened token list */
-    const int32_t* tok;
-    const int32_t* tok_slot;
-    int n_tok;
+    /* tokens grouped by slot: group g holds tok[goff[g] .. goff[g + 1]) of slot gslot[g] */
+    const int32_t *tok, *goff, *gslot;
+    int n_groups;
+    /* work units: prefix sums over the groups */
+    const int32_t *shrink_units, *expand_units;
 } mt_job;
 
+static struct {
+    pthread_t th[256];
+    int n; /* threads including the caller */
+    pthread_barrier_t go, phase, done;
+    const mt_job* job;
+    int quit;
+} g_pool;
+
+#if defined(__AVX2__) && defined(__FMA__)
+#include <immintrin.h>
+/* 8 bf16 -> 8 f32: a bf16 is the upper half of an f32 */
+static inline __m256 widen8(const uint16_t* p) {
+    return _mm256_castsi256_ps(_mm256_slli_epi32(_mm256_cvtepu16_epi32(_mm_loadu_si128((const __m128i*)p)), 16));
+}
+static float dot_bf16(const uint16_t* a, const uint16_t* b, int n) {
+    __m256 acc0 = _mm256_setzero_ps(), acc1 = _mm256_setzero_ps();
+    int k = 0;
+    for (; k + 16 <= n; k += 16) {
+        acc0 = _mm256_fmadd_ps(widen8(a + k), widen8(b + k), acc0);
+        acc1 = _mm256_fmadd_ps(widen8(a + k + 8), widen8(b + k + 8), acc1);
+    }
+    for (; k + 8 <= n; k += 8) acc0 = _mm256_fmadd_ps(widen8(a + k), widen8(b + k), acc0);
+    float v[8];
+    _mm256_storeu_ps(v, _mm256_add_ps(acc0, acc1));
+    float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+    for (; k < n; k++) s += po_bf16_to_f32(a[k]) * po_bf16_to_f32(b[k]);
+    return s;
+}
+#else
 static float dot_bf16(const uint16_t* a, const uint16_t* b, int n) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     int k = 0;
@@ -454,80 +486,168 @@ static float dot_bf16(const uint16_t* a, const uint16_t* b, int n) {
     for (; k < n; k++) s += po_bf16_to_f32(a[k]) * po_bf16_to_f32(b[k]);
     return s;
 }
+#endif
 
-static void* mt_run(void* arg) {
-    mt_job* j = (mt_job*)arg;
-    if (j->phase == 0) {
-        /* shrink: work unit = (token, S column); strided over threads by token-major index */
-        for (int i = 0; i < j->n_tok; i++) {
-            const po_desc* d = &j->table[j->tok_slot[i]];
-            if (d->rank == 0) continue;
-            const uint16_t* x = j->X + (size_t)j->tok[i] * (size_t)j->ldx;
-            const uint16_t* A = (const uint16_t*)(uintptr_t)d->a;
-            float* s = j->S + (size_t)j->tok[i] * (size_t)j->lds;
-            for (int n = j->tid; n < d->rank; n += j->nthreads) s[n] = dot_bf16(x, A + (size_t)n * (size_t)j->K, j->K);
+static int find_group(const int32_t* prefix, int n_groups, int unit) {
+    int lo = 0, hi = n_groups; /* last g with prefix[g] <= unit */
+    while (hi - lo > 1) {
+        int mid = (lo + hi) / 2;
+        if (prefix[mid] <= unit) lo = mid;
+        else hi = mid;
+    }
+    return lo;
+}
+
+static void mt_shrink(const mt_job* j, int tid, int nthreads) {
+    const int total = j->shrink_units[j->n_groups];
+    for (int u = tid; u < total; u += nthreads) {
+        const int g = find_group(j->shrink_units, j->n_groups, u), n = u - j->shrink_units[g];
+        const po_desc* d = &j->table[j->gslot[g]];
+        const uint16_t* arow = (const uint16_t*)(uintptr_t)d->a + (size_t)n * (size_t)j->K;
+        for (int i = j->goff[g]; i < j->goff[g + 1]; i++) {
+            const size_t t = (size_t)j->tok[i];
+            j->S[t * (size_t)j->lds + n] = dot_bf16(j->X + t * (size_t)j->ldx, arow, j->K);
         }
-    } else {
-        /* expand: output columns strided over threads in blocks of 64 */
-        for (int i = 0; i < j->n_tok; i++) {
-            const po_desc* d = &j->table[j->tok_slot[i]];
-            if (d->rank == 0) continue;
-            size_t t = (size_t)j->tok[i];
-            const float* s = j->S + t * (size_t)j->lds;
-            for (int p = 0; p < PO_MAX_PARTS; p++) {
-                int r = d->r[p];
-                if (r == 0) continue;
-                const uint16_t* B = (const uint16_t*)(uintptr_t)d->b[p];
-                const float* sp = s + d->r_off[p];
-                int nblk = (d->rows[p] + 63) / 64;
-                for (int blk = j->tid; blk < nblk; blk += j->nthreads) {
-                    int n1 = (blk + 1) * 64 < d->rows[p] ? (blk + 1) * 64 : d->rows[p];
-                    for (int n = blk * 64; n < n1; n++) {
-                        const uint16_t* bn = B + (size_t)n * (size_t)r;
-                        float acc = 0.f;
-                        for (int q = 0; q < r; q++) acc += sp[q] * po_bf16_to_f32(bn[q]);
-                        size_t at = t * (size_t)j->ldy + (size_t)d->off[p] + (size_t)n;
-                        if (j->f32_out) ((float*)j->Y)[at] += acc;
-                        else {
-                            uint16_t* y = (uint16_t*)j->Y;
-                            y[at] = po_bf16_from_f32(po_bf16_to_f32(y[at]) + acc);
-                        }
-                    }
+    }
+}
+
+static void mt_expand(const mt_job* j, int tid, int nthreads) {
+    const int total = j->expand_units[j->n_groups];
+    for (int u = tid; u < total; u += nthreads) {
+        const int g = find_group(j->expand_units, j->n_groups, u);
+        int blk = u - j->expand_units[g];
+        const po_desc* d = &j->table[j->gslot[g]];
+        int p = 0;
+        for (; p < PO_MAX_PARTS; p++) {
+            const int nb = d->r[p] ? (d->rows[p] + 63) / 64 : 0;
+            if (blk < nb) break;
+            blk -= nb;
+        }
+        if (p == PO_MAX_PARTS) continue;
+        const int r = d->r[p], n1 = (blk + 1) * 64 < d->rows[p] ? (blk + 1) * 64 : d->rows[p];
+        const uint16_t* B = (const uint16_t*)(uintptr_t)d->b[p];
+        for (int n = blk * 64; n < n1; n++) {
+            float bf[512]; /* one row of B, widened once for all of the slot's tokens */
+            const uint16_t* bn = B + (size_t)n * (size_t)r;
+            for (int q = 0; q < r; q++) bf[q] = po_bf16_to_f32(bn[q]);
+            for (int i = j->goff[g]; i < j->goff[g + 1]; i++) {
+                const size_t t = (size_t)j->tok[i];
+                const float* sp = j->S + t * (size_t)j->lds + d->r_off[p];
+                float acc = 0.f;
+                for (int q = 0; q < r; q++) acc += sp[q] * bf[q];
+                const size_t at = t * (size_t)j->ldy + (size_t)d->off[p] + (size_t)n;
+                if (j->f32_out) ((float*)j->Y)[at] += acc;
+                else {
+                    uint16_t* y = (uint16_t*)j->Y;
+                    y[at] = po_bf16_from_f32(po_bf16_to_f32(y[at]) + acc);
                 }
             }
         }
     }
-    return NULL;
+}
+
+static void mt_both(const mt_job* j, int tid, int nthreads) {
+    mt_shrink(j, tid, nthreads);
+    pthread_barrier_wait(&g_pool.phase);
+    mt_expand(j, tid, nthreads);
+}
+
+static void* pool_worker(void* arg) {
+    const int tid = (int)(intptr_t)arg;
+    for (;;) {
+        pthread_barrier_wait(&g_pool.go);
+        if (g_pool.quit) return NULL;
+        mt_both(g_pool.job, tid, g_pool.n);
+        pthread_barrier_wait(&g_pool.done);
+    }
+}
+
+static void pool_stop(void) {
+    if (g_pool.n <= 1) {
+        g_pool.n = 0;
+        return;
+    }
+    g_pool.quit = 1;
+    pthread_barrier_wait(&g_pool.go);
+    for (int i = 1; i < g_pool.n; i++) pthread_join(g_pool.th[i], NULL);
+    pthread_barrier_destroy(&g_pool.go);
+    pthread_barrier_destroy(&g_pool.phase);
+    pthread_barrier_destroy(&g_pool.done);
+    g_pool.n = 0;
+    g_pool.quit = 0;
+}
+
+static void pool_start(int n) {
+    if (g_pool.n == n) return;
+    pool_stop();
+    g_pool.n = n;
+    if (n <= 1) return;
+    pthread_barrier_init(&g_pool.go, NULL, (unsigned)n);
+    pthread_barrier_init(&g_pool.phase, NULL, (unsigned)n);
+    pthread_barrier_init(&g_pool.done, NULL, (unsigned)n);
+    for (int i = 1; i < n; i++) pthread_create(&g_pool.th[i], NULL, pool_worker, (void*)(intptr_t)i);
 }
 
 int po_site_mt(const uint16_t* X, int ldx, int K, const int32_t* tiles, const po_desc* table, float* S, int lds,
                void* Y, int ldy, int f32_out, int n_threads) {
     if (n_threads <= 0) n_threads = po_hw_threads();
     if (n_threads > 256) n_threads = 256;
-    int count = tiles[0], n_tok = 0;
-    for (int i = 0; i < count; i++) n_tok += tiles[2 + 3 * i];
-    int32_t* tok = (int32_t*)malloc(sizeof(int32_t) * (size_t)(n_tok + 1));
-    int32_t* tsl = (int32_t*)malloc(sizeof(int32_t) * (size_t)(n_tok + 1));
-    int at = 0;
-    for (int i = 0; i < count; i++)
-        for (int r = 0; r < tiles[2 + 3 * i]; r++) {
-            tok[at] = tiles[1 + 3 * i] + r;
-            tsl[at] = tiles[3 + 3 * i];
-            at++;
-        }
-    pthread_t th[256];
-    mt_job jobs[256];
-    for (int phase = 0; phase < 2; phase++) {
-        for (int i = 0; i < n_threads; i++) {
-            mt_job j = {X, ldx, K, tiles, table, S, lds, Y, ldy, f32_out, i, n_threads, phase, tok, tsl, n_tok};
-            jobs[i] = j;
-            if (i > 0) pthread_create(&th[i], NULL, mt_run, &jobs[i]);
-        }
-        mt_run(&jobs[0]);
-        for (int i = 1; i < n_threads; i++) pthread_join(th[i], NULL);
+    /* tokens of the step grouped by slot (stable): count, prefix, fill */
+    const int count = tiles[0];
+    int max_slot = 0, n_tok = 0;
+    for (int i = 0; i < count; i++) {
+        if (tiles[3 + 3 * i] > max_slot) max_slot = tiles[3 + 3 * i];
+        n_tok += tiles[2 + 3 * i];
     }
+    int32_t* per = (int32_t*)calloc((size_t)max_slot + 2, sizeof(int32_t));
+    for (int i = 0; i < count; i++) per[tiles[3 + 3 * i] + 1] += tiles[2 + 3 * i];
+    int32_t* tok = (int32_t*)malloc(sizeof(int32_t) * (size_t)(n_tok + 1));
+    int32_t* goff = (int32_t*)malloc(sizeof(int32_t) * (size_t)(max_slot + 2));
+    int32_t* gslot = (int32_t*)malloc(sizeof(int32_t) * (size_t)(max_slot + 2));
+    int32_t* su = (int32_t*)malloc(sizeof(int32_t) * (size_t)(max_slot + 2));
+    int32_t* eu = (int32_t*)malloc(sizeof(int32_t) * (size_t)(max_slot + 2));
+    int32_t* fill = (int32_t*)malloc(sizeof(int32_t) * (size_t)(max_slot + 2));
+    int ng = 0, at = 0;
+    su[0] = eu[0] = 0;
+    for (int s = 1; s <= max_slot; s++) {
+        fill[s] = -1;
+        if (per[s + 1] == 0 || table[s].rank == 0) continue;
+        const po_desc* d = &table[s];
+        int blocks = 0;
+        for (int p = 0; p < PO_MAX_PARTS; p++)
+            if (d->r[p]) blocks += (d->rows[p] + 63) / 64;
+        gslot[ng] = s;
+        goff[ng] = at;
+        fill[s] = at;
+        at += per[s + 1];
+        su[ng + 1] = su[ng] + d->rank;
+        eu[ng + 1] = eu[ng] + blocks;
+        ng++;
+    }
+    goff[ng] = at;
+    for (int i = 0; i < count; i++) {
+        const int s = tiles[3 + 3 * i];
+        if (s < 1 || fill[s] < 0) continue;
+        for (int r = 0; r < tiles[2 + 3 * i]; r++) tok[fill[s]++] = tiles[1 + 3 * i] + r;
+    }
+    mt_job job = {X, ldx, K, table, S, lds, Y, ldy, f32_out, tok, goff, gslot, ng, su, eu};
+    pool_start(n_threads);
+    if (n_threads <= 1) {
+        mt_shrink(&job, 0, 1);
+        mt_expand(&job, 0, 1);
+    } else {
+        g_pool.job = &job;
+        pthread_barrier_wait(&g_pool.go);
+        mt_both(&job, 0, n_threads);
+        pthread_barrier_wait(&g_pool.done);
+    }
+    free(per);
     free(tok);
-    free(tsl);
+    free(goff);
+    free(gslot);
+    free(su);
+    free(eu);
+    free(fill);
     return n_threads;
 }
 

@@ -186,83 +186,21 @@ if lib.plora_abi_version() != ABI_VERSION:
                       "rebuild it with `python pocket-engine_b200/build.py --force`")
 
 
-# ------------------------------------------------------------------------------------------ bf16
-
-def bf16_bits(x):
-    """f32 array -> bf16 bit patterns (uint16), round to nearest even."""
-    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
-    r = ((u >> 16) & 1) + np.uint32(0x7FFF)
-    return ((u + r) >> 16).astype(np.uint16)
+from .sites import Factors, Heads, Site, SitePart, bf16_bits, bf16_to_f32  # noqa: E402,F401
 
 
-def bf16_to_f32(bits):
-    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
-
-
-# ------------------------------------------------------------------------------------- sites
-
-class Heads:
-    """src/lora.rs:23-31; ``None`` in a field stands for Heads::None."""
-
-    def __init__(self, start, block):
-        self.start, self.block = start, block
-
-
-class SitePart:
-    """src/lora.rs:33-41"""
-
-    def __init__(self, module, rows, off, heads=None):
-        self.module, self.rows, self.off, self.heads = module, rows, off, heads
-
-
-class Site:
-    """src/lora.rs:43-50"""
-
-    def __init__(self, layer, cols, parts, col_heads=None):
-        self.layer, self.cols, self.parts, self.col_heads = layer, cols, list(parts), col_heads
-
-    @staticmethod
-    def fused(layer, cols, modules):
-        """A site whose parts are laid out back to back: ``modules`` is [(module path, rows), ...]."""
-        parts, off = [], 0
-        for m, rows in modules:
-            parts.append(SitePart(m, rows, off))
-            off += rows
-        return Site(layer, cols, parts)
-
-    def max_rows(self):  # src/lora.rs:52-56
-        return max((p.rows for p in self.parts), default=0)
-
-    def width(self):
-        return max(p.off + p.rows for p in self.parts)
-
-    def _c(self):
-        c = CSite()
-        c.layer, c.cols, c.n_parts = self.layer, self.cols, len(self.parts)
-        c.col_heads_start = self.col_heads.start if self.col_heads else -1
-        c.col_heads_block = self.col_heads.block if self.col_heads else 0
-        for i, p in enumerate(self.parts):
-            c.parts[i].module = p.module.encode()
-            c.parts[i].rows, c.parts[i].off = p.rows, p.off
-            c.parts[i].heads_start = p.heads.start if p.heads else -1
-            c.parts[i].heads_block = p.heads.block if p.heads else 0
-        return c
-
-
-class Factors:
-    """src/lora.rs:91-95: one module's A [r, cols] and B [rows, r] in f32, scale folded into B."""
-
-    def __init__(self, layer, module, a, b):
-        self.layer, self.module = layer, module
-        self.a = np.ascontiguousarray(a, dtype=np.float32)
-        self.b = np.ascontiguousarray(b, dtype=np.float32)
-        self.r = self.a.shape[0]
-
-    @staticmethod
-    def scaled(layer, module, a, b, scale):
-        """Folds ``scale`` into B in f32 as read_peft does (src/lora.rs:225-228)."""
-        b = np.asarray(b, dtype=np.float32) * np.float32(scale)
-        return Factors(layer, module, a, b)
+def _c_site(site):
+    """A Site as the C ABI's plora_site."""
+    c = CSite()
+    c.layer, c.cols, c.n_parts = site.layer, site.cols, len(site.parts)
+    c.col_heads_start = site.col_heads.start if site.col_heads else -1
+    c.col_heads_block = site.col_heads.block if site.col_heads else 0
+    for i, p in enumerate(site.parts):
+        c.parts[i].module = p.module.encode()
+        c.parts[i].rows, c.parts[i].off = p.rows, p.off
+        c.parts[i].heads_start = p.heads.start if p.heads else -1
+        c.parts[i].heads_block = p.heads.block if p.heads else 0
+    return c
 
 
 class Adapter:
@@ -411,7 +349,7 @@ class Loras:
         self.max_tokens = max_tokens
         self.max_seqs = max_seqs if max_seqs is not None else max_tokens
         self.device = device
-        csites = (CSite * len(self.sites))(*[s._c() for s in self.sites])
+        csites = (CSite * len(self.sites))(*[_c_site(s) for s in self.sites])
         h = _P()
         rc = lib.plora_create(csites, len(self.sites), int(base_gguf), heads[0], heads[1], max_slots, max_rank,
                               max_tokens, self.max_seqs, device, C.byref(h))

@@ -19,7 +19,7 @@ partial y.
 """
 import numpy as np
 
-from . import Factors, Site, SitePart
+from .sites import Factors, Site, SitePart
 
 COLUMN, ROW = "column", "row"
 
@@ -107,7 +107,7 @@ class ShardedWorkload:
         site = self.full.sites[si]
         if self.modes[si] == ROW:
             return np.sum(np.stack(outs, 0).astype(np.float64), 0)
-        full = np.zeros((self.tokens, site.width()), np.float64)
+        full = np.zeros((len(outs[0]), site.width()), np.float64)  # all rows, or the same sample of rows from every rank
         for r, y in enumerate(outs):
             at = 0
             for p in site.parts:

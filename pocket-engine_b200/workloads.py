@@ -7,7 +7,7 @@ slot i + 1; slot 0 is "no adapter".
 """
 import numpy as np
 
-from . import Factors, Site, bf16_bits
+from .sites import Factors, Site, bf16_bits
 
 
 def block_sites(hidden, inter, kv, layer=0):
