@@ -408,7 +408,7 @@ def run_fp8(args, rank, world, local_rank):
         wl = workloads.Workload(f"fp8-prefill-4096x12288-{seqs}x2048-r64", workloads.config4().sites, [64] * seqs, 1.0,
                                 [2048] * seqs, list(range(1, seqs + 1)), 1000 * rank, max_rank=128)
     else:
-        wl = workloads.config4(seed=1000 * rank)
+        wl = workloads.config4(seed=1000 * rank, two_part=args.two_part)  # --two-part: the engine's gate + up layer
     site = wl.sites[0]
     K, N, T = site.cols, site.width(), wl.tokens
     main = torch.cuda.Stream(device=dev)
@@ -463,6 +463,39 @@ def run_fp8(args, rank, world, local_rank):
         torch.cuda.synchronize()
     fused_us = 1e3 * float(np.mean([a.elapsed_time(b) for a, b in evs[2:]]))
     clocks = sampler.stop() if sampler is not None else None
+
+    # ---- comparison rows (library kernels; not part of the product path)
+    compare = {}
+    try:
+        # (a) what the engine does with an FP8 layer (src/gpu.rs:1183-1277, src/linear.rs:844-847): a library FP8 GEMM,
+        # then the adapter as a separate read-modify-write pass over y. torch._scaled_mm with one scale per token and
+        # per output channel is cuBLASLt's row-wise scaled FP8 GEMM.
+        f8 = torch.float8_e4m3fn
+        def library(S, m):
+            L = S["L"]
+            L.fp8_quant_rows(S["x"].data_ptr(), T, K, S["xq"].data_ptr(), S["st"].data_ptr(), m)
+            torch._scaled_mm(S["xq"].view(f8), S["wq"].view(f8).t(), scale_a=S["st"].view(T, 1), scale_b=S["sn"].view(1, N),
+                             out_dtype=torch.bfloat16, out=S["y"])
+            L.apply(S["hook"], S["step"], S["x"].data_ptr(), T, S["y"].data_ptr(), N, False, m)
+        t_lib = _event_time(torch, main, lambda i: library(sets[i % copies], main.cuda_stream), args.steps, args.warmup, barrier)
+        compare["library_fp8_gemm_then_apply_us"] = 1e3 * t_lib / args.steps
+    except Exception as e:  # noqa: BLE001
+        compare["library_fp8_gemm_then_apply_us"] = f"unavailable: {type(e).__name__}: {e}"[:160]
+    try:
+        # (b) a measured FP8 dense peak for the tensor-pipe fractions: the same library GEMM at 8192^3, per-tensor scales
+        n8 = 8192
+        a8 = torch.randn(n8, n8, device=dev).to(torch.float8_e4m3fn)
+        b8 = torch.randn(n8, n8, device=dev).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=dev)
+        o8 = torch.empty(n8, n8, dtype=torch.bfloat16, device=dev)
+        f = lambda i: torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16, out=o8)  # noqa: E731
+        best = min(_event_time(torch, main, f, 1, 3 if r == 0 else 0, barrier) for r in range(8))
+        t_sus = _event_time(torch, main, f, 200, 0, barrier) / 200
+        compare["fp8_dense_peak_tflops_burst"] = 2.0 * n8 ** 3 / (best * 1e-3) / 1e12
+        compare["fp8_dense_peak_tflops_sustained"] = 2.0 * n8 ** 3 / (t_sus * 1e-3) / 1e12
+        del a8, b8, o8
+    except Exception as e:  # noqa: BLE001
+        compare["fp8_dense_peak_tflops_burst"] = f"unavailable: {type(e).__name__}: {e}"[:160]
     # end to end with host buffers: x in, y out
     y_out = torch.empty(T, N, dtype=torch.int16).pin_memory()
 
@@ -500,6 +533,8 @@ def run_fp8(args, rank, world, local_rank):
     peak, kind, pk = peaks()
     fp8_peak = 2 * pk.get("bf16_tflops", 1590.0)
     us = 1e3 * ms / args.steps
+    meas = compare.get("fp8_dense_peak_tflops_burst")
+    meas_sus = compare.get("fp8_dense_peak_tflops_sustained")
     return {"metric": METRIC, "value": world * T * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp8 e4m3 base + bf16 adapters, f32 accumulate",
@@ -518,7 +553,12 @@ def run_fp8(args, rank, world, local_rank):
                          "tflops": flops / (fused_us * 1e-6) / 1e12,
                          "tensor_frac_of_2x_bf16_burst_peak": flops / (fused_us * 1e-6) / 1e12 / fp8_peak,
                          "tensor_frac_of_2x_bf16_sustained_peak": flops / (fused_us * 1e-6) / 1e12 /
-                         (2 * pk.get("bf16_tflops_sustained", 1400.0))},
+                         (2 * pk.get("bf16_tflops_sustained", 1400.0)),
+                         "tensor_frac_of_measured_fp8_burst_peak": flops / (fused_us * 1e-6) / 1e12 / meas
+                         if isinstance(meas, float) else None,
+                         "tensor_frac_of_measured_fp8_sustained_peak": flops / (fused_us * 1e-6) / 1e12 / meas_sus
+                         if isinstance(meas_sus, float) else None},
+            "compare": compare,
             "step_roofline": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (us * 1e-6) / 1e9,
                               "frac": step_bytes / (us * 1e-6) / 1e9 / peak, "us_per_step": us,
                               "tflops": flops / (us * 1e-6) / 1e12},
@@ -948,6 +988,7 @@ def main():
                     help="plora_set_early_x(1): the caller vouches for x, which is then read ahead of the dependency wait")
     ap.add_argument("--inner-repeats", type=int, default=50,
                     help="decode workload: passes of the block per timed step (the result is reported per pass)")
+    ap.add_argument("--two-part", action="store_true", help="fp8 workload: the engine's two-part gate + up layer (4096 -> 24576)")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel layer set that the default run appends")
     ap.add_argument("--streams", type=int, default=1, choices=[1, 2],
                     help="1: one stream, kernels chained by programmatic dependent launch; 2: the engine's "

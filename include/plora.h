@@ -359,6 +359,15 @@ int plora_static_splits(int cols);
 long long plora_static_bad_tiles(void); /* refused tiles on the current device so far; waits for the device */
 const char* plora_static_error(void);
 
+/* Where the time went (the engine's POCKET_PROFILE, src/gpu.rs:321-332, 809-822, 1741-1791). Between begin and end
+ * every kernel launch of this handle is bracketed by a pair of CUDA events on its stream (not while the stream is
+ * capturing; at most 65536 launches per profile). plora_profile_end waits for them and writes one line per kernel
+ * name, "name<TAB>launches<TAB>microseconds", into buf (truncated to cap); returns the number of names, or minus
+ * a PLORA_ERR_* code. Event pairs
+ * keep consecutive launches from overlapping, so the sum is an upper bound of the time inside a graph. */
+int plora_profile_begin(plora_t* h);
+int plora_profile_end(plora_t* h, char* buf, size_t cap);
+
 /* Device status word: 0, or the PLORA_ERR_* a kernel recorded (bounded wait ran out, capacity).
  * Synchronises the device. */
 int plora_device_status(plora_t* h);

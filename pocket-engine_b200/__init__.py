@@ -158,6 +158,8 @@ SYMBOLS = {
     "plora_set_run_min": (_I, [_P, _I]),
     "plora_set_tile_split": (_I, [_P, _I]),
     "plora_device_status": (_I, [_P]),
+    "plora_profile_begin": (_I, [_P]),
+    "plora_profile_end": (_I, [_P, C.c_char_p, C.c_size_t]),
     "plora_site_apply_static": (_I, [_U64, _I, _I, _U64, _I, _U64, _I, _I, _I, _U64, _I, _I, _P]),
     "plora_static_scratch_bytes": (_U64, []),
     "plora_static_splits": (_I, [_I]),
@@ -481,6 +483,22 @@ class Loras:
 
     def device_status(self):
         self._check(lib.plora_device_status(self._h))
+
+    def profile_begin(self):
+        """Starts timing every kernel launch of this registry (src/gpu.rs:1741-1791, POCKET_PROFILE)."""
+        self._check(lib.plora_profile_begin(self._h))
+
+    def profile_end(self):
+        """{kernel name: (launches, microseconds)} since profile_begin."""
+        buf = C.create_string_buffer(1 << 16)
+        n = lib.plora_profile_end(self._h, buf, len(buf))
+        if n < 0:
+            self._check(-n)
+        out = {}
+        for line in buf.value.decode().splitlines():
+            name, calls, us = line.split("\t")
+            out[name] = (int(calls), float(us))
+        return out
 
     # ---- Linear::forward's bracket ----
 

@@ -30,6 +30,39 @@ int cuda_fail(const plora_t* h, const char* what, cudaError_t e) {
         if (e_ != cudaSuccess) return cuda_fail(h, what, e_); \
     } while (0)
 
+// A kernel launch of the path. While a profile is being collected (plora_profile_begin) and the stream is not
+// capturing, the launch is bracketed by a pair of events on its stream (src/gpu.rs:321-332, 809-822 do the same
+// under POCKET_PROFILE); plora_profile_end sums the pairs per name.
+#define CUK(h, what, call)                                                        \
+    do {                                                                          \
+        cudaEvent_t pa_ = nullptr, pb_ = nullptr;                                 \
+        const bool prof_ = prof_open(h, as_stream(stream), &pa_, &pb_);           \
+        if (prof_) cudaEventRecord(pa_, as_stream(stream));                       \
+        cudaError_t e_ = (call);                                                  \
+        if (prof_) {                                                              \
+            cudaEventRecord(pb_, as_stream(stream));                              \
+            (h)->prof.push_back({what, pa_, pb_});                                \
+        }                                                                         \
+        if (e_ != cudaSuccess) return cuda_fail(h, what, e_);                     \
+    } while (0)
+
+// a pair of timing events for one launch, or false when no profile is open, the stream is capturing, or the
+// profile is full (it holds at most 65536 launches)
+bool prof_open(plora_t* h, cudaStream_t st, cudaEvent_t* a, cudaEvent_t* b) {
+    if (!h || !h->prof_on || h->prof.size() >= 65536) return false;
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return false;
+    }
+    if (cudaEventCreate(a) != cudaSuccess) return false;
+    if (cudaEventCreate(b) != cudaSuccess) {
+        cudaEventDestroy(*a);
+        return false;
+    }
+    return true;
+}
+
 int next_mult(int x, int m) { return (x + m - 1) / m * m; }
 
 // words the tile list [count, (start, len, slot) x cap_tiles] takes at the head of the step metadata, rounded up
@@ -281,6 +314,10 @@ void plora_destroy(plora_t* h) {
         for (int p = 0; p < PLORA_XCHG_MAX_WORLD; p++)
             if (h->xchg_ipc[p] && h->xchg_peer[p]) cudaIpcCloseMemHandle(h->xchg_peer[p]);
         if (h->xchg) cudaFree(h->xchg);
+        for (auto& e : h->prof) {
+            cudaEventDestroy(e.a);
+            cudaEventDestroy(e.b);
+        }
         if (h->fork_ev) cudaEventDestroy(h->fork_ev);
         if (h->join_ev) cudaEventDestroy(h->join_ev);
     } else {
@@ -679,7 +716,7 @@ int plora_meta_build(plora_t* h, uint64_t cu_dev, uint64_t seq_slot_dev, int n_s
     if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
     if (n_seqs < 0 || n_seqs > h->max_seqs) return fail(h, PLORA_ERR_CAPACITY, "more sequences than max_seqs");
     if (!cu_dev || !seq_slot_dev) return fail(h, PLORA_ERR_ARG, "null device pointer");
-    CU(h, "meta_tiles", plora_launch_meta_tiles((const int32_t*)(uintptr_t)cu_dev, (const int32_t*)(uintptr_t)seq_slot_dev,
+    CUK(h, "meta_tiles", plora_launch_meta_tiles((const int32_t*)(uintptr_t)cu_dev, (const int32_t*)(uintptr_t)seq_slot_dev,
                                                 n_seqs, h->meta, h->cap_tiles, h->status, as_stream(stream)));
     return PLORA_OK;
 }
@@ -702,8 +739,8 @@ int plora_step_begin(plora_t* h, int max_tiles, int decode, void* stream, plora_
     h->pdl_armed = false;
     SegLayout lay = h->seg;
     if (decode) lay.run_min = 1 << 30;
-    CU(h, "meta_group", plora_launch_meta_group(h->meta, segs, lay, h->status, as_stream(stream)));
-    CU(h, "meta_records", plora_launch_meta_records(segs, lay, h->tables, h->site_cols, (int)h->sites.size(), h->recs,
+    CUK(h, "meta_group", plora_launch_meta_group(h->meta, segs, lay, h->status, as_stream(stream)));
+    CUK(h, "meta_records", plora_launch_meta_records(segs, lay, h->tables, h->site_cols, (int)h->sites.size(), h->recs,
                                                     h->rec_cap, as_stream(stream)));
     out->run_min = lay.run_min;
     out->pad_ = 0;
@@ -752,12 +789,12 @@ static int shrink_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
     if (work_cap == 0) return PLORA_OK;
     const bool pdl = h->pdl && h->pdl_armed;
     h->pdl_armed = true;
-    CU(h, "shrink",
+    CUK(h, "shrink",
        plora_launch_shrink((const void*)(uintptr_t)x, site.cols, site.cols, recs_of(h, hook->site), h->rec_cap,
                            (float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.kchunk, site.nsplit,
                            work_cap, hook->parts * h->max_rank, h->status, pdl, early, early_x, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min)
-        CU(h, "shrink (tile path)",
+        CUK(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
                                    h->seg, (const plora_desc*)(uintptr_t)hook->table,
                                    h->amaps + (size_t)hook->site * (size_t)(h->max_slots + 1), (float*)(uintptr_t)step->s,
@@ -803,19 +840,19 @@ int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint
     h->pdl_armed = true;
     int total = 0;
     for (auto& p : site.parts) total += p.rows;
-    CU(h, "site kernel",
+    CUK(h, "site kernel",
        plora_launch_site((const void*)(uintptr_t)x, site.cols, site.cols, recs_of(h, hook->site), h->rec_cap,
                          h->prefetch_next && hook->site + 1 < (int)h->sites.size() ? recs_of(h, hook->site + 1) : nullptr,
                          (void*)(uintptr_t)y, ldy, f32_out, (int)site.parts.size(), h->max_rank, total, work_cap,
                          site.max_clusters, h->early_x, h->status, pdl, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min) {
-        CU(h, "shrink (tile path)",
+        CUK(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
                                    h->seg, (const plora_desc*)(uintptr_t)hook->table,
                                    h->amaps + (size_t)hook->site * (size_t)(h->max_slots + 1), (float*)(uintptr_t)step->s,
                                    (size_t)(step->s_stride / 4), step->lds, hook->parts * h->max_rank, std::max(1, rows / 64),
                                    tile_split(h, rows), h->status, h->pdl, false, as_stream(stream)));
-        CU(h, "expand (tile path)",
+        CUK(h, "expand (tile path)",
            plora_launch_expand_mma((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.cols,
                                    tile_split(h, rows), (const int32_t*)(uintptr_t)step->segs, h->seg,
                                    (const plora_desc*)(uintptr_t)hook->table, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
@@ -834,7 +871,7 @@ int plora_s_reduce(plora_t* h, const plora_hook* hook, const plora_step* step, i
     int work_cap = std::min(std::min(step->max_tiles, rows), h->max_slots + rows / PLORA_WORK_TOKENS);
     const bool pdl = h->pdl && h->pdl_armed;
     h->pdl_armed = true;
-    CU(h, "S reduce", plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
+    CUK(h, "S reduce", plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
                                             (const int32_t*)(uintptr_t)step->segs, h->seg,
                                             (const plora_desc*)(uintptr_t)hook->table, work_cap,
                                             h->mma_ok && rows >= step->run_min ? std::max(1, rows / 64) : 0,
@@ -855,13 +892,13 @@ static int expand_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
     if (work_cap == 0) return PLORA_OK;
     const bool pdl = h->pdl && h->pdl_armed;
     h->pdl_armed = true;
-    CU(h, "expand",
+    CUK(h, "expand",
        plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds,
                            reduced ? 1 : site.nsplit, recs_of(h, hook->site), h->rec_cap,
                            (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap, h->status, pdl,
                            early, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min)
-        CU(h, "expand (tile path)",
+        CUK(h, "expand (tile path)",
            plora_launch_expand_mma((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.cols,
                                    reduced ? 1 : tile_split(h, rows), (const int32_t*)(uintptr_t)step->segs, h->seg,
                                    (const plora_desc*)(uintptr_t)hook->table, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
@@ -875,7 +912,7 @@ int plora_fp8_quant_rows(plora_t* h, uint64_t x, int rows, int cols, uint64_t xq
     if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
     if (!x || !xq || !st || (x & 15) || (xq & 7) || cols <= 0 || (cols & 7) || rows < 0)
         return fail(h, PLORA_ERR_ARG, "x, xq, st must be aligned device addresses and cols a multiple of 8");
-    CU(h, "fp8 quantise", plora_launch_fp8_quant((const void*)(uintptr_t)x, rows, cols, cols, (void*)(uintptr_t)xq,
+    CUK(h, "fp8 quantise", plora_launch_fp8_quant((const void*)(uintptr_t)x, rows, cols, cols, (void*)(uintptr_t)xq,
                                                  (float*)(uintptr_t)st, as_stream(stream)));
     h->pdl_armed = false;
     return PLORA_OK;
@@ -891,19 +928,19 @@ static int gemm_layer(plora_t* h, const plora_hook* hook, const plora_step* step
     h->pdl_armed = true;
     // the kernel reads the long runs' S from plane 0: fold the tile path's planes (the gather tokens' K-split
     // planes are added by the gather expand itself)
-    CU(h, "S reduce (tiles)",
+    CUK(h, "S reduce (tiles)",
        plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, 1,
                              (const int32_t*)(uintptr_t)step->segs, h->seg, (const plora_desc*)(uintptr_t)hook->table, 0,
                              h->mma_ok && rows >= step->run_min ? std::max(1, rows / 64) : 0, tile_split(h, rows),
                              site.cols, pdl, as_stream(stream)));
-    CU(h, "fused layer (tensor-core adapter term)",
+    CUK(h, "fused layer (tensor-core adapter term)",
        plora_launch_gemm_fused(kind, (const void*)(uintptr_t)x, (const float*)(uintptr_t)st, (const void*)(uintptr_t)w,
                                (const float*)(uintptr_t)sn, rows, width, site.cols, (const int32_t*)(uintptr_t)step->segs,
                                h->seg, (const plora_desc*)(uintptr_t)hook->table, (int)site.parts.size(), site.part_off,
                                site.part_rows, (const float*)(uintptr_t)step->s, step->lds, (void*)(uintptr_t)y, ldy, f32_out,
                                h->status, h->pdl, as_stream(stream)));
     if (work_cap > 0)
-        CU(h, "expand (tokens outside long runs)",
+        CUK(h, "expand (tokens outside long runs)",
            plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
                                recs_of(h, hook->site), h->rec_cap, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
                                hook->max_rows, work_cap, h->status, h->pdl, false, as_stream(stream)));
@@ -963,12 +1000,12 @@ int plora_linear_fp8_fused(plora_t* h, const plora_hook* hook, const plora_step*
         return gemm_layer(h, hook, step, 0, xq, st, wq, sn, rows, width, y, ldy, f32_out, work_cap, stream);
     const bool pdl = h->pdl && h->pdl_armed;
     h->pdl_armed = true;
-    CU(h, "S reduce", plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
+    CUK(h, "S reduce", plora_launch_s_reduce((float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
                                             (const int32_t*)(uintptr_t)step->segs, h->seg,
                                             (const plora_desc*)(uintptr_t)hook->table, work_cap,
                                             h->mma_ok && rows >= step->run_min ? std::max(1, rows / 64) : 0,
                                             tile_split(h, rows), site.cols, pdl, as_stream(stream)));
-    CU(h, "fused fp8 layer",
+    CUK(h, "fused fp8 layer",
        plora_launch_fp8_fused((const void*)(uintptr_t)xq, (const float*)(uintptr_t)st, (const void*)(uintptr_t)wq,
                               (const float*)(uintptr_t)sn, rows, width, site.cols, (const int32_t*)(uintptr_t)step->segs,
                               h->seg, (const plora_desc*)(uintptr_t)hook->table, (int)site.parts.size(), off, prow,
@@ -993,6 +1030,54 @@ int plora_join(plora_t* h, void* main_stream, void* side_stream) {
     CU(h, "join record", cudaEventRecord(h->join_ev, as_stream(side_stream)));
     CU(h, "join wait", cudaStreamWaitEvent(as_stream(main_stream), h->join_ev, 0));
     return PLORA_OK;
+}
+
+// ---- where the time went: src/gpu.rs:1741-1791 (POCKET_PROFILE) ----
+
+int plora_profile_begin(plora_t* h) {
+    if (!h) return PLORA_ERR_ARG;
+    if (h->device < 0) return fail(h, PLORA_ERR_CUDA, "layout-only handle: no device");
+    for (auto& e : h->prof) {
+        cudaEventDestroy(e.a);
+        cudaEventDestroy(e.b);
+    }
+    h->prof.clear();
+    h->prof_on = true;
+    return PLORA_OK;
+}
+
+int plora_profile_end(plora_t* h, char* buf, size_t cap) {
+    if (!h) return -PLORA_ERR_ARG;
+    h->prof_on = false;
+    std::map<std::string, std::pair<int, double>> sum;  // name -> launches, microseconds
+    cudaError_t bad = cudaSuccess;
+    for (auto& e : h->prof) {
+        float ms = 0.f;
+        cudaError_t r = cudaEventSynchronize(e.b);
+        if (r == cudaSuccess) r = cudaEventElapsedTime(&ms, e.a, e.b);
+        if (r != cudaSuccess) bad = r;
+        else {
+            auto& s = sum[e.what];
+            s.first += 1;
+            s.second += 1e3 * ms;
+        }
+        cudaEventDestroy(e.a);
+        cudaEventDestroy(e.b);
+    }
+    h->prof.clear();
+    if (bad != cudaSuccess) return -cuda_fail(h, "profile events", bad);  // negative: a count is expected
+    std::string out;
+    for (auto& kv : sum) {
+        char line[160];
+        snprintf(line, sizeof line, "%s\t%d\t%.3f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+        out += line;
+    }
+    if (buf && cap) {
+        const size_t n = out.size() < cap - 1 ? out.size() : cap - 1;
+        memcpy(buf, out.data(), n);
+        buf[n] = 0;
+    }
+    return (int)sum.size();
 }
 
 int plora_set_apply_mode(plora_t* h, int mode) {
@@ -1140,7 +1225,7 @@ int plora_s_exchange(plora_t* h, const plora_hook* hook, const plora_step* step,
     if (rc != PLORA_OK) return rc;
     const bool pdl = h->pdl && h->pdl_armed;
     h->pdl_armed = true;
-    CU(h, "S exchange", plora_launch_xchg(c, nblocks, pdl, as_stream(stream)));
+    CUK(h, "S exchange", plora_launch_xchg(c, nblocks, pdl, as_stream(stream)));
     return PLORA_OK;
 }
 

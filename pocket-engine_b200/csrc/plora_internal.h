@@ -151,6 +151,13 @@ struct plora {
     bool tile_late = true;    // the tile shrink runs beside the gather shrink launched right before it (PLORA_TILE_LATE=0: behind it)
     bool mma_ok = false;    // the tensor-core tile kernels can run (max_rank <= 128 and the driver entry point exists)
     bool pdl_armed = false;  // false right after the step's grouping kernel: the next launch is a plain one
+    // plora_profile_begin / _end: one pair of events per kernel launch while a profile is open
+    struct ProfEntry {
+        const char* what;
+        cudaEvent_t a, b;
+    };
+    bool prof_on = false;
+    std::vector<ProfEntry> prof;
 };
 
 size_t plora_meta_group_smem(const SegLayout& lay);

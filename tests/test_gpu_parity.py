@@ -348,6 +348,24 @@ def test_capacity_errors_are_reported_not_faulted(pe):
     loras.close()
 
 
+def test_kernel_profile_names_the_launches(pe, wls):
+    """plora_profile_begin / _end (the engine's POCKET_PROFILE, src/gpu.rs:1741-1791): launches counted per kernel."""
+    import torch
+    wl = wls.config2(tokens=32, adapters=4)
+    loras = harness.product_registry(pe, wl)
+    loras.profile_begin()
+    harness.run_gpu(pe, loras, wl, False, meta="device", fused="cluster")
+    harness.run_gpu(pe, loras, wl, False, meta="device")
+    prof = loras.profile_end()
+    assert prof["site kernel"][0] == 4 and prof["shrink"][0] == 4 and prof["expand"][0] == 4
+    assert prof["meta_group"][0] == 2 and prof["meta_records"][0] == 2 and prof["meta_tiles"][0] == 2
+    assert all(us > 0 for _, us in prof.values())
+    assert loras.profile_end() == {}  # closed: nothing is collected any more
+    harness.run_gpu(pe, loras, wl, False)
+    assert loras.profile_end() == {}
+    loras.close()
+
+
 def test_random_steps_match_the_oracle(pe, wls):
     """Seeded random steps: run lengths on both sides of the tile threshold and of the 128-token tile size, base-only
     sequences, ranks from 8 to 64, one to three parts, input widths that are and are not multiples of
