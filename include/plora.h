@@ -31,6 +31,12 @@ extern "C" {
  * plora_abi_version() of the library it loaded before making any other call. */
 #define PLORA_ABI_VERSION 2
 int plora_abi_version(void);
+/* 1 when the library was built with -DPLORA_BOUNDS (libplora_bounds.so): its few-token kernels check every launch
+ * record against the launch's arguments (token rows inside [0, rows), slabs inside the slot pool, ranks inside the
+ * intermediate's row, output columns inside y's pitch) and skip what does not fit, recording PLORA_ERR_ARG in the
+ * device status word instead of reading or writing through it. The stand-in, on this path, for running the suite
+ * under a memory checker. 0 in the ordinary build. */
+int plora_bounds_build(void);
 
 #define PLORA_MAX_PARTS 4  /* src/lora.rs:14 */
 #define PLORA_RANK_STEP 16 /* src/lora.rs:16 */

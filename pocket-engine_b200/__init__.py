@@ -114,6 +114,7 @@ SYMBOLS = {
     "plora_free": (_I, [_P, C.c_uint32]),
     "plora_id": (_I, [_P, C.c_char_p, _U32P]),
     "plora_abi_version": (_I, []),
+    "plora_bounds_build": (_I, []),
     "plora_names": (_I, [_P, C.c_char_p, C.c_size_t]),
     "plora_adapter_of": (_P, [_P, C.c_uint32]),
     "plora_upload": (_I, [_P, _I, C.c_uint32, _P]),

@@ -9,6 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libplora.so")
+LIB_BOUNDS = os.path.join(HERE, "libplora_bounds.so")  # the range-checked build (-DPLORA_BOUNDS), used by tests
 SOURCES = ["plora_host.cpp", "plora_read.cpp", "plora_manager.cpp", "plora_kernels.cu", "plora_mma.cu", "plora_fp8.cu", "plora_site.cu", "plora_static.cu", "plora_xchg.cu", "plora_gemm.cu"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -16,10 +17,10 @@ FLAGS = [
 ]
 
 
-def stale():
-    if not os.path.exists(LIB):
+def stale(lib=LIB):
+    if not os.path.exists(lib):
         return True
-    t = os.path.getmtime(LIB)
+    t = os.path.getmtime(lib)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f != "plora_compat.cu"] + \
         [os.path.join(HERE, "..", "include", "plora.h")]
     return any(os.path.getmtime(d) > t for d in deps)
@@ -41,17 +42,22 @@ def build_compat(force=False):
     return COMPAT
 
 
-def build(force=False, verbose=False):
-    build_compat(force)
-    if not force and not stale():
-        return LIB
-    cmd = ["nvcc"] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
-        [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB]
+def _nvcc(lib, extra, verbose):
+    cmd = ["nvcc"] + FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + \
+        [os.path.join(CSRC, s) for s in SOURCES] + ["-o", lib]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
     if r.returncode != 0:
-        raise RuntimeError("nvcc failed building libplora.so")
+        raise RuntimeError("nvcc failed building " + os.path.basename(lib))
+
+
+def build(force=False, verbose=False, bounds=True):
+    build_compat(force)
+    if force or stale(LIB):
+        _nvcc(LIB, [], verbose)
+    if bounds and (force or stale(LIB_BOUNDS)):
+        _nvcc(LIB_BOUNDS, ["-DPLORA_BOUNDS"], False)
     return LIB
 
 

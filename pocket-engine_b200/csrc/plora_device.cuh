@@ -5,8 +5,40 @@
 #include <stdint.h>
 
 #include "../../include/plora.h"
+#include "plora_internal.h"
+
+// Kernel parameter and launch argument that exist in the range-checked build only
+#ifdef PLORA_BOUNDS
+#define PLORA_BOUNDS_PARAM , PloraBounds bnd
+#define PLORA_BOUNDS_ARG(b) , b
+#else
+#define PLORA_BOUNDS_PARAM
+#define PLORA_BOUNDS_ARG(b)
+#endif
 
 namespace {
+
+#ifdef PLORA_BOUNDS
+// Everything a few-token kernel will index with comes from `rec` (and K, the layer's input width): true when all of
+// it stays inside what the launch may touch.
+__device__ __forceinline__ bool rec_in_bounds(const PloraRec& rec, const PloraBounds& b, int K) {
+    if (rec.cnt < 0 || rec.cnt > PLORA_WORK_TOKENS) return false;
+    if (rec.cnt == 0 || rec.rank == 0) return true;  // nothing will be touched
+    if (rec.rank < 0 || rec.rank > b.rmax || (rec.rank & 15)) return false;
+    for (int t = 0; t < rec.cnt; t++)
+        if (rec.tok[t] < 0 || rec.tok[t] >= b.rows) return false;
+    if (rec.a < b.pool_lo || rec.a + (unsigned long long)rec.rank * (unsigned long long)K * 2ull > b.pool_hi || (rec.a & 15)) return false;
+    for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+        const int r = rec.r[p];
+        if (r == 0) continue;
+        if (r < 0 || r > b.max_rank || (r & 15) || rec.r_off[p] < 0 || rec.r_off[p] + r > rec.rank) return false;
+        if (rec.rows[p] <= 0 || (rec.rows[p] & 1) || rec.off[p] < 0 || (rec.off[p] & 1)) return false;
+        if (b.ldy > 0 && rec.off[p] + rec.rows[p] > b.ldy) return false;
+        if (rec.b[p] < b.pool_lo || rec.b[p] + (unsigned long long)rec.rows[p] * (unsigned long long)r * 2ull > b.pool_hi || (rec.b[p] & 15)) return false;
+    }
+    return true;
+}
+#endif
 
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
     // a bf16 is the upper half of an f32

@@ -328,6 +328,15 @@ void plora_destroy(plora_t* h) {
 
 int plora_abi_version(void) { return PLORA_ABI_VERSION; }
 
+// 1 in the range-checked build (-DPLORA_BOUNDS), else 0
+int plora_bounds_build(void) {
+#ifdef PLORA_BOUNDS
+    return 1;
+#else
+    return 0;
+#endif
+}
+
 const char* plora_last_error(const plora_t* h) { return h ? h->err.c_str() : g_create_err.c_str(); }
 
 uint64_t plora_bytes(const plora_t* h) {  // src/lora.rs:526-528
@@ -772,6 +781,18 @@ int plora_shrink(plora_t* h, const plora_hook* hook, const plora_step* step, uin
     return shrink_impl(h, hook, step, x, rows, false, false, stream);
 }
 
+// what a launch over `rows` token rows may touch (checked by the kernels of the -DPLORA_BOUNDS build only)
+static PloraBounds bounds_of(const plora_t* h, const plora_hook* hook, int rows, int ldy) {
+    PloraBounds b;
+    b.pool_lo = (unsigned long long)(uintptr_t)h->pool;
+    b.pool_hi = b.pool_lo + (unsigned long long)h->slot_bytes * (unsigned long long)h->max_slots;
+    b.rows = rows;
+    b.ldy = ldy;
+    b.rmax = hook->parts * h->max_rank;
+    b.max_rank = h->max_rank;
+    return b;
+}
+
 // the launch records of a layer for this step
 static const PloraRec* recs_of(const plora_t* h, int site) { return h->recs + (size_t)site * (size_t)h->rec_cap; }
 
@@ -792,7 +813,8 @@ static int shrink_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
     CUK(h, "shrink",
        plora_launch_shrink((const void*)(uintptr_t)x, site.cols, site.cols, recs_of(h, hook->site), h->rec_cap,
                            (float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.kchunk, site.nsplit,
-                           work_cap, hook->parts * h->max_rank, h->status, pdl, early, early_x, as_stream(stream)));
+                           work_cap, hook->parts * h->max_rank, bounds_of(h, hook, rows, 0), h->status, pdl, early, early_x,
+                           as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min)
         CUK(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
@@ -844,7 +866,7 @@ int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint
        plora_launch_site((const void*)(uintptr_t)x, site.cols, site.cols, recs_of(h, hook->site), h->rec_cap,
                          h->prefetch_next && hook->site + 1 < (int)h->sites.size() ? recs_of(h, hook->site + 1) : nullptr,
                          (void*)(uintptr_t)y, ldy, f32_out, (int)site.parts.size(), h->max_rank, total, work_cap,
-                         site.max_clusters, h->early_x, h->status, pdl, as_stream(stream)));
+                         site.max_clusters, h->early_x, bounds_of(h, hook, rows, ldy), h->status, pdl, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min) {
         CUK(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,
@@ -895,8 +917,8 @@ static int expand_impl(plora_t* h, const plora_hook* hook, const plora_step* ste
     CUK(h, "expand",
        plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds,
                            reduced ? 1 : site.nsplit, recs_of(h, hook->site), h->rec_cap,
-                           (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap, h->status, pdl,
-                           early, as_stream(stream)));
+                           (void*)(uintptr_t)y, ldy, f32_out, hook->parts, hook->max_rows, work_cap,
+                           bounds_of(h, hook, rows, ldy), h->status, pdl, early, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min)
         CUK(h, "expand (tile path)",
            plora_launch_expand_mma((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.cols,
@@ -943,7 +965,8 @@ static int gemm_layer(plora_t* h, const plora_hook* hook, const plora_step* step
         CUK(h, "expand (tokens outside long runs)",
            plora_launch_expand((const float*)(uintptr_t)step->s, (size_t)(step->s_stride / 4), step->lds, site.nsplit,
                                recs_of(h, hook->site), h->rec_cap, (void*)(uintptr_t)y, ldy, f32_out, hook->parts,
-                               hook->max_rows, work_cap, h->status, h->pdl, false, as_stream(stream)));
+                               hook->max_rows, work_cap, bounds_of(h, hook, rows, ldy), h->status, h->pdl, false,
+                               as_stream(stream)));
     return PLORA_OK;
 }
 

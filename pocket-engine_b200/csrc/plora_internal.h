@@ -61,6 +61,20 @@ struct alignas(256) PloraRec {
 };
 static_assert(sizeof(PloraRec) == 256, "one record is two 128-byte lines");
 
+// Range-checked build (-DPLORA_BOUNDS, libplora_bounds.so): what a launch may touch. The few-token kernels take
+// every index they use from a launch record and from these launch arguments, so they check each record against
+// this before using it: a record that names a token row outside [0, rows), a slab outside the slot pool, ranks
+// that do not fit the intermediate's row, or output columns past the pitch of y is skipped by every block that
+// sees it and PLORA_ERR_ARG is recorded in the status word; nothing is read or written through its numbers and
+// nothing traps. In the ordinary build the struct is passed along and ignored.
+struct PloraBounds {
+    unsigned long long pool_lo, pool_hi;  // the slot pool [lo, hi)
+    int rows;                             // token rows of x and y the caller named
+    int ldy;                              // pitch of y in elements (0: the launch does not touch y)
+    int rmax;                             // parts * max_rank: the longest stacked A, the live part of an S row
+    int max_rank;
+};
+
 struct alignas(64) PloraTmap {  // a CUtensorMap, opaque to the host registry
     unsigned char b[128];
 };
@@ -210,7 +224,7 @@ size_t plora_site_plan(int K, int parts, int max_rank, int total_rows, int* nsub
 int plora_site_max_clusters(int K, int parts, int max_rank, int total_rows);
 cudaError_t plora_launch_site(const void* x, int ldx, int K, const PloraRec* recs, int rec_cap, const PloraRec* next_recs,
                               void* y, int ldy, int f32_out, int parts, int max_rank, int total_rows, int work_cap,
-                              int max_clusters, bool early_x, int* status, bool pdl, cudaStream_t st);
+                              int max_clusters, bool early_x, const PloraBounds& bnd, int* status, bool pdl, cudaStream_t st);
 cudaError_t plora_mma_init();
 cudaError_t plora_fp8_init(int max_rank);
 cudaError_t plora_launch_fp8_quant(const void* x, int rows, int ldx, int K, void* xq, float* st, cudaStream_t stream);
@@ -241,7 +255,7 @@ cudaError_t plora_launch_expand_mma(const float* S, size_t s_stride_elems, int l
 // plora_apply, whose kernels follow one another); early_x: x too may be read ahead of the wait
 cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const PloraRec* recs, int rec_cap, float* S,
                                 size_t s_stride_elems, int lds, int kchunk, int nsplit, int work_cap, int max_rank_total,
-                                int* status, bool pdl, bool early, bool early_x, cudaStream_t st);
+                                const PloraBounds& bnd, int* status, bool pdl, bool early, bool early_x, cudaStream_t st);
 cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, int nsplit, const PloraRec* recs,
                                 int rec_cap, void* y, int ldy, int f32_out, int parts, int max_rows, int work_cap,
-                                int* status, bool pdl, bool early, cudaStream_t st);
+                                const PloraBounds& bnd, int* status, bool pdl, bool early, cudaStream_t st);

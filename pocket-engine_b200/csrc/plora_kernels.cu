@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
                                                                    const PloraRec* __restrict__ recs, int rec_cap,
                                                                    float* __restrict__ S, size_t s_stride, int lds,
                                                                    int kchunk, int rps, int rt_max, int early, int early_x,
-                                                                   int* __restrict__ status) {
+                                                                   int* __restrict__ status PLORA_BOUNDS_PARAM) {
     // early != 0: dependents are released at kernel start (every store of the path comes after a wait).
     // early_x != 0: the caller vouches that x is older than every kernel still in flight, so x is fetched and
     // the partial sums computed before the dependency wait; only the stores into S (which the expand before may
@@ -393,6 +393,13 @@ __global__ void __launch_bounds__(128) plora_shrink_gather_kernel(const bf16* __
     __syncthreads();
     const int cnt = srec.cnt, rank = srec.rank;
     if (cnt == 0) break;
+#ifdef PLORA_BOUNDS
+    if (!rec_in_bounds(srec, bnd, K)) {
+        if (threadIdx.x == 0) atomicMax(status, PLORA_ERR_ARG);
+        __syncthreads();
+        continue;
+    }
+#endif
     if (row0 >= rank) {
         __syncthreads();
         continue;
@@ -487,7 +494,7 @@ __global__ void __launch_bounds__(256 / NH, 4 * NH) plora_expand_gather_kernel(c
                                                                       int lds, int nsplit,
                                                                       const PloraRec* __restrict__ recs, int rec_cap,
                                                                       void* Y, int ldy, int f32_out, int nc, int bs_bytes,
-                                                                      int early, int* __restrict__ status) {
+                                                                      int early, int* __restrict__ status PLORA_BOUNDS_PARAM) {
     // early != 0: dependents are released at kernel start. No value of y is bound before the dependency wait
     // (the kernel before, the layer's matrix multiply, may still be writing it): only L2 prefetch hints.
     extern __shared__ __align__(128) unsigned char dsm[];
@@ -507,6 +514,13 @@ __global__ void __launch_bounds__(256 / NH, 4 * NH) plora_expand_gather_kernel(c
     __syncthreads();
     const int cnt = srec.cnt;
     if (cnt == 0) break;
+#ifdef PLORA_BOUNDS
+    if (!rec_in_bounds(srec, bnd, srec.cols)) {
+        if (threadIdx.x == 0) atomicMax(status, PLORA_ERR_ARG);
+        __syncthreads();
+        continue;
+    }
+#endif
     const int p = blockIdx.y, r = srec.r[p];
     const int rows = srec.rows[p], c0 = blockIdx.x * nc;
     if (r == 0 || c0 >= rows) {
@@ -725,13 +739,14 @@ int plora_shrink_rps(int kchunk) {
 
 cudaError_t plora_launch_shrink(const void* x, int ldx, int K, const PloraRec* recs, int rec_cap, float* S,
                                 size_t s_stride_elems, int lds, int kchunk, int nsplit, int work_cap, int max_rank_total,
-                                int* status, bool pdl, bool early, bool early_x, cudaStream_t st) {
+                                const PloraBounds& bnd, int* status, bool pdl, bool early, bool early_x, cudaStream_t st) {
+    (void)bnd;
     const int rps = plora_shrink_rps(kchunk);
     const int rt_max = (max_rank_total + rps - 1) / rps;
     dim3 grid((unsigned)(nsplit * rt_max), 1, (unsigned)(work_cap < PLORA_GRID_Z_CAP ? work_cap : PLORA_GRID_Z_CAP));
     const size_t smem = (size_t)(rps + PLORA_WORK_TOKENS) * (size_t)kchunk * 2;
     return launch_pdl(plora_shrink_gather_kernel, grid, dim3(128), smem, st, pdl, reinterpret_cast<const bf16*>(x), ldx,
-                      K, recs, rec_cap, S, s_stride_elems, lds, kchunk, rps, rt_max, early ? 1 : 0, early_x ? 1 : 0, status);
+                      K, recs, rec_cap, S, s_stride_elems, lds, kchunk, rps, rt_max, early ? 1 : 0, early_x ? 1 : 0, status PLORA_BOUNDS_ARG(bnd));
 }
 
 // output columns per block (two per thread): 512 for wide layers so the grid stays near one wave, 256
@@ -744,7 +759,8 @@ int plora_expand_nc(int max_rank, int max_rows) {
 
 cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, int nsplit, const PloraRec* recs,
                                 int rec_cap, void* y, int ldy, int f32_out, int parts, int max_rows, int work_cap,
-                                int* status, bool pdl, bool early, cudaStream_t st) {
+                                const PloraBounds& bnd, int* status, bool pdl, bool early, cudaStream_t st) {
+    (void)bnd;
     const int max_rank = lds / PLORA_MAX_PARTS;
     const int nc = plora_expand_nc(max_rank, max_rows);
     // tile buffer: all of a block's columns at the maximum rank, up to 32 KB; blocks of higher-rank slots take
@@ -762,7 +778,7 @@ cudaError_t plora_launch_expand(const float* S, size_t s_stride_elems, int lds, 
     if (per_sm > 8) per_sm = 8;
     const int nh = nc >= 512 && (long long)grid.x * grid.y * grid.z <= (long long)per_sm * g_sms ? 2 : 1;
     const dim3 block((unsigned)(nc / (2 * nh)));
-#define PLORA_EXPAND_ARGS S, s_stride_elems, lds, nsplit, recs, rec_cap, y, ldy, f32_out, nc, bs_bytes, early ? 1 : 0, status
+#define PLORA_EXPAND_ARGS S, s_stride_elems, lds, nsplit, recs, rec_cap, y, ldy, f32_out, nc, bs_bytes, early ? 1 : 0, status PLORA_BOUNDS_ARG(bnd)
     if (nh == 2)
         return passes ? launch_pdl(plora_expand_gather_kernel<true, 2>, grid, block, smem, st, pdl, PLORA_EXPAND_ARGS)
                       : launch_pdl(plora_expand_gather_kernel<false, 2>, grid, block, smem, st, pdl, PLORA_EXPAND_ARGS);

@@ -332,7 +332,7 @@ template <bool F32>
 __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THREADS, 2)
     plora_site_gather_kernel(const bf16* __restrict__ X, int ldx, int K, const PloraRec* __restrict__ recs, int rec_cap,
                              const PloraRec* __restrict__ next_recs, void* Y, int ldy, SiteShape sh, int early_x,
-                             int* __restrict__ status) {
+                             int* __restrict__ status PLORA_BOUNDS_PARAM) {
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ __align__(8) uint64_t bars[4];  // A rows, x chunks, B rows, the cluster's partials
     __shared__ PloraRec srec;
@@ -385,6 +385,13 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
         __syncthreads();
         const int cnt = srec.cnt, R = srec.rank;
         if (cnt == 0) break;  // end of the list: the same decision in every block of the cluster
+#ifdef PLORA_BOUNDS
+        if (!rec_in_bounds(srec, bnd, K) || srec.cols != K) {  // the same decision in every block that reads this record
+            if (tid == 0) atomicMax(status, PLORA_ERR_ARG);
+            __syncthreads();
+            continue;
+        }
+#endif
         if (R == 0) {         // the slot's adapter skips this layer
             __syncthreads();
             continue;
@@ -682,7 +689,8 @@ int plora_site_max_clusters(int K, int parts, int max_rank, int total_rows) {
 
 cudaError_t plora_launch_site(const void* x, int ldx, int K, const PloraRec* recs, int rec_cap, const PloraRec* next_recs,
                               void* y, int ldy, int f32_out, int parts, int max_rank, int total_rows, int work_cap,
-                              int max_clusters, bool early_x, int* status, bool pdl, cudaStream_t st) {
+                              int max_clusters, bool early_x, const PloraBounds& bnd, int* status, bool pdl, cudaStream_t st) {
+    (void)bnd;
     int nsub = 1;
     const size_t smem = plora_site_plan(K, parts, max_rank, total_rows, &nsub);
     if (smem == 0) return cudaErrorInvalidValue;
@@ -703,7 +711,7 @@ cudaError_t plora_launch_site(const void* x, int ldx, int K, const PloraRec* rec
     cfg.numAttrs = pdl ? 1 : 0;
     if (f32_out)
         return cudaLaunchKernelEx(&cfg, plora_site_gather_kernel<true>, reinterpret_cast<const bf16*>(x), ldx, K, recs, rec_cap,
-                                  next_recs, y, ldy, pl.sh, early_x ? 1 : 0, status);
+                                  next_recs, y, ldy, pl.sh, early_x ? 1 : 0, status PLORA_BOUNDS_ARG(bnd));
     return cudaLaunchKernelEx(&cfg, plora_site_gather_kernel<false>, reinterpret_cast<const bf16*>(x), ldx, K, recs, rec_cap,
-                              next_recs, y, ldy, pl.sh, early_x ? 1 : 0, status);
+                              next_recs, y, ldy, pl.sh, early_x ? 1 : 0, status PLORA_BOUNDS_ARG(bnd));
 }
