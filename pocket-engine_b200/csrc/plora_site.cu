@@ -41,7 +41,6 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // a float at the same shared-memory offset in block `rank` of the cluster
 __device__ __forceinline__ float ld_peer_f32(const float* p, uint32_t rank) {
@@ -361,7 +360,7 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
         mbar_init(&bars[3], SITE_CLUSTER);  // one arrival per block of the cluster
         mbar_fence_init();
     }
-    cluster_arrive();  // the barriers exist; met (cluster_wait) before the first remote arrival
+    cluster_arrive_relaxed();  // the barriers exist (published by the init fence); met before the first remote arrival
     bool met = false, waited = false;
     uint32_t ph_ax = 0, ph_b = 0, ph_s = 0;  // barrier phases (each flips only when its barrier was used)
     bool alive = true;                       // false once a bounded wait ran out: keep meeting the cluster, do no more work
@@ -396,8 +395,28 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
             __syncthreads();
             continue;
         }
-        if (warp == 1 && lane < PLORA_MAX_PARTS) column_share(srec, (int)blockIdx.y * SITE_CLUSTER + (int)crank, lane, sshare);
-        // ---- slab requests (before the dependency wait)
+        // warp 1: the block's share of the output columns (lane p takes part p), then the copies of its rows of B
+        if (warp == 1) {
+            if (lane < PLORA_MAX_PARTS) column_share(srec, (int)blockIdx.y * SITE_CLUSTER + (int)crank, lane, sshare);
+            __syncwarp();
+            if (lane == 0) {
+                uint32_t total = 0;
+#pragma unroll
+                for (int p = 0; p < PLORA_MAX_PARTS; p++)
+                    total += (uint32_t)(sshare.hi[p] - sshare.lo[p]) * (uint32_t)srec.r[p] * 2u;
+                if (total > 0) {
+                    mbar_expect_tx(&bars[2], total);
+#pragma unroll
+                    for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+                        const uint32_t bytes = (uint32_t)(sshare.hi[p] - sshare.lo[p]) * (uint32_t)srec.r[p] * 2u;
+                        if (bytes > 0)
+                            bulk_g2s(Bs + sshare.boff[p],
+                                     reinterpret_cast<const bf16*>(srec.b[p]) + (size_t)sshare.lo[p] * srec.r[p], bytes, &bars[2]);
+                    }
+                }
+            }
+        }
+        // ---- slab requests (before the dependency wait): warp 0 asks for the block's rows of A
         if (warp == 0 && klen > 0) {
             const bf16* A = reinterpret_cast<const bf16*>(srec.a) + k0;
             if (lane == 0) mbar_expect_tx(&bars[0], (uint32_t)R * kbytes);
@@ -410,23 +429,7 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
             for (int r = tid; r < R + PLORA_WORK_TOKENS; r += SITE_THREADS)
                 *reinterpret_cast<uint4*>((r < R ? As + (size_t)(r >> 6) * sh.g_stride + (size_t)(r & 63) * sh.kb_pad
                                                  : Xs + (size_t)(r - R) * sh.kb_pad) + kbytes) = make_uint4(0u, 0u, 0u, 0u);
-        __syncthreads();  // the share is known
-        if (tid == 0) {
-            uint32_t total = 0;
-#pragma unroll
-            for (int p = 0; p < PLORA_MAX_PARTS; p++)
-                total += (uint32_t)(sshare.hi[p] - sshare.lo[p]) * (uint32_t)srec.r[p] * 2u;
-            if (total > 0) {
-                mbar_expect_tx(&bars[2], total);
-#pragma unroll
-                for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-                    const uint32_t bytes = (uint32_t)(sshare.hi[p] - sshare.lo[p]) * (uint32_t)srec.r[p] * 2u;
-                    if (bytes > 0)
-                        bulk_g2s(Bs + sshare.boff[p],
-                                 reinterpret_cast<const bf16*>(srec.b[p]) + (size_t)sshare.lo[p] * srec.r[p], bytes, &bars[2]);
-                }
-            }
-        }
+        __syncthreads();  // the share is known to every warp
         // ---- hints: the x and y lines this block will touch, and the next layer's slabs of this work item
         if (!waited && warp >= 2) {
             const int t1 = tid - 64, n1 = SITE_THREADS - 64;
