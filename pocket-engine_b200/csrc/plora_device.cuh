@@ -96,6 +96,20 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  : "memory");
 }
 
+// ---- barrier arrival, proxy fence and the bulk-group calls that tensor stores are tracked with ----
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// makes this thread's ordinary shared-memory writes visible to the bulk-copy engine (which reads shared memory
+// through the async proxy); to be followed by a barrier before another thread issues the copy
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all of this thread's groups have read their shared-memory source (it may be overwritten)
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... and have been written to global memory
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // Programmatic dependent launch. Every kernel of the path waits for the kernels before it and only then
 // lets the next one start its prologue, so a prologue may read anything written two or more kernels back
 // (slabs, descriptors, the step's grouping) but nothing the kernel right before it writes.

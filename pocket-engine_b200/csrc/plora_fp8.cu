@@ -20,65 +20,17 @@
 
 #include "plora_internal.h"
 #include "plora_device.cuh"
+#include "plora_tc.cuh"
 
 typedef __nv_bfloat16 bf16;
 
-
 namespace {
 
-__device__ __forceinline__ bool elect_one() {
-    uint32_t p;
-    asm volatile("{\n.reg .pred e;\nelect.sync _|e, 0xffffffff;\nselp.u32 %0, 1, 0, e;\n}\n" : "=r"(p));
-    return p != 0;
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// D (tensor memory) (+)= A (shared) . B (shared), 8-bit float inputs, f32 accumulate
-__device__ __forceinline__ void umma_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(d),
-        "l"(a), "l"(b), "r"(idesc), "r"(acc)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-        "%29,%30,%31}, [%32];\n"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 // K-major operand in 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
     return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
            (2ull << 61);
 }
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-            smem_u32(dst)),
-        "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
-        : "memory");
-}
-// barrier among the 128 threads of the four adapter/epilogue warps only
-__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------------------------------
 // Per-token dynamic quantisation: s_t = amax / 448 (1 for an all-zero row), xq = e4m3_satfinite(x / s_t).
@@ -196,10 +148,6 @@ struct Fp8Parts {
 
 #define F8_NQ 8  // adapter work units in flight per block
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
 // Warps: 0 = TMA producer of the GEMM ring, 1 = MMA issuer, 2..5 = adapter term + epilogue (128 threads, one
 // output column each in two halves of 64), 6 = producer of the adapter ring (bulk copies of each unit's rows of
 // B and S into a byte ring, first in first out).
@@ -280,7 +228,7 @@ __global__ void __launch_bounds__(224) plora_fp8_fused_kernel(const __grid_const
                 const uint32_t ws = xs + F8_BM * F8_BK;
 #pragma unroll
                 for (int kk = 0; kk < F8_BK / 32; kk++)
-                    umma_f8(tmem, umma_desc_sw128(xs + kk * 32), umma_desc_sw128(ws + kk * 32), idesc, (ks | kk) != 0);
+                    umma<0>(tmem, umma_desc_sw128(xs + kk * 32), umma_desc_sw128(ws + kk * 32), idesc, (ks | kk) != 0);
                 umma_commit(&empty[stg]);
             }
             umma_commit(&acc_bar);

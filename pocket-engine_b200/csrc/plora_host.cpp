@@ -748,9 +748,8 @@ int plora_step_begin(plora_t* h, int max_tiles, int decode, void* stream, plora_
     h->pdl_armed = false;
     SegLayout lay = h->seg;
     if (decode) lay.run_min = 1 << 30;
-    CUK(h, "meta_group", plora_launch_meta_group(h->meta, segs, lay, h->status, as_stream(stream)));
-    CUK(h, "meta_records", plora_launch_meta_records(segs, lay, h->tables, h->site_cols, (int)h->sites.size(), h->recs,
-                                                    h->rec_cap, as_stream(stream)));
+    CUK(h, "meta_group", plora_launch_meta_group(h->meta, segs, lay, h->status, h->tables, h->site_cols, (int)h->sites.size(),
+                                                 h->recs, h->rec_cap, as_stream(stream)));
     out->run_min = lay.run_min;
     out->pad_ = 0;
     out->tiles = (uint64_t)(uintptr_t)h->meta;

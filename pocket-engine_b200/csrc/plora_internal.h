@@ -47,7 +47,7 @@ struct SegLayout {
 // kernel right after the grouping. A record carries everything a block of the few-token kernels needs about
 // its work item (the slot's resolved descriptor and the token rows), so the block makes one metadata fetch
 // and then issues its slab copies, instead of walking header -> work item -> descriptor table -> slab.
-// Record w of a layer is valid while cnt > 0; the records kernel ends the list with cnt == 0.
+// Record w of a layer is valid while cnt > 0; the grouping kernel ends the list with cnt == 0.
 #define PLORA_REC_TERM 128  // cleared records after the last valid one (>= the z extent of every grid that walks them)
 struct alignas(256) PloraRec {
     int32_t cnt, slot, rank, cols;  // tokens (1..16), slot, stacked rows of A, the layer's input width
@@ -213,11 +213,10 @@ __host__ __device__ inline int plora_tile_chunks(int K, int R) {
 // ---- kernel launchers (plora_kernels.cu); each returns a cudaError_t from the launch ----
 cudaError_t plora_launch_meta_tiles(const int32_t* cu, const int32_t* seq_slot, int n_seqs, int32_t* tiles,
                                     int cap_tiles, int* status, cudaStream_t st);
-cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status,
-                                    cudaStream_t st);
+// Groups the step's tiles by slot and writes the launch records of every layer (recs may be null: grouping only).
 // site_info: per layer {input width, blocks that share a work item's output columns in the cluster kernel (0: none)}
-cudaError_t plora_launch_meta_records(const int32_t* segs, SegLayout lay, const plora_desc* tables, const int32_t* site_info,
-                                      int n_sites, PloraRec* recs, int rec_cap, cudaStream_t st);
+cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status, const plora_desc* tables,
+                                    const int32_t* site_info, int n_sites, PloraRec* recs, int rec_cap, cudaStream_t st);
 cudaError_t plora_kernels_init(const SegLayout& lay);
 cudaError_t plora_site_init();
 size_t plora_site_plan(int K, int parts, int max_rank, int total_rows, int* nsub);

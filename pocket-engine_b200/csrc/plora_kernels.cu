@@ -103,11 +103,55 @@ __global__ void __launch_bounds__(1024) plora_meta_tiles_kernel(const int* __res
 }
 
 // ---------------------------------------------------------------------------------------------
+// One launch record: gather work item w resolved against one layer's descriptor table, so that the kernels of
+// that layer make one metadata fetch per block. `o` is the record's 16 uint4.
+__device__ __forceinline__ void write_record(uint4* o, const int* segs, const SegLayout& lay, const plora_desc* table, int w,
+                                             int cols, int pieces) {
+    const uint4* work = reinterpret_cast<const uint4*>(segs + lay.work() + PLORA_WORK_WORDS * w);
+    const uint4 head = work[0];  // slot, perm start, count, 0
+    const int slot = (int)head.x;
+    const uint4* d = reinterpret_cast<const uint4*>(table + slot);  // 112 bytes: a, b[4], rank, r, r_off, off, rows
+    uint4 dv[7];
+#pragma unroll
+    for (int i = 0; i < 7; i++) dv[i] = d[i];
+    // Desc: a | b0 b1 | b2 b3 | rank r0 r1 r2 | r3 ro0 ro1 ro2 | ro3 o0 o1 o2 | o3 rows0 rows1 rows2 | rows3 pad
+    const uint32_t* dw = reinterpret_cast<const uint32_t*>(dv);
+    o[0] = make_uint4(head.z, head.x, dw[10], (uint32_t)cols);  // cnt, slot, rank, cols
+    o[1] = make_uint4(dw[0], dw[1], dw[2], dw[3]);              // a, b[0]
+    o[2] = make_uint4(dw[4], dw[5], dw[6], dw[7]);              // b[1], b[2]
+    o[3] = make_uint4(dw[8], dw[9], dw[11], dw[12]);            // b[3], r[0], r[1]
+    o[4] = make_uint4(dw[13], dw[14], dw[15], dw[16]);          // r[2], r[3], r_off[0], r_off[1]
+    o[5] = make_uint4(dw[17], dw[18], dw[19], dw[20]);          // r_off[2], r_off[3], off[0], off[1]
+    o[6] = make_uint4(dw[21], dw[22], dw[23], dw[24]);          // off[2], off[3], rows[0], rows[1]
+    // the slot's output columns over its targeted parts laid end to end, and the even share of them that
+    // one block of the layer's cluster kernel expands
+    uint32_t cat[PLORA_MAX_PARTS], ntot = 0;
+#pragma unroll
+    for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+        cat[p] = ntot;
+        if ((int)dw[11 + p] > 0) ntot += dw[23 + p];
+    }
+    const uint32_t share = pieces > 0 ? (((ntot + pieces - 1) / pieces + 1) & ~1u) : 0u;
+    o[7] = make_uint4(dw[25], dw[26], ntot, share);             // rows[2], rows[3], ntot, share
+    o[8] = work[1];                                             // the token rows
+    o[9] = work[2];
+    o[10] = work[3];
+    o[11] = work[4];
+    o[12] = make_uint4(cat[0], cat[1], cat[2], cat[3]);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Regroup the tile words by slot. Runs = maximal ranges of contiguous tokens of one slot. Runs of at
 // least lay.run_min tokens become tensor-core tiles; the rest are gathered by slot: perm lists their
 // token rows ordered by (slot, position in the tile list), cut into work items of <= 16 tokens.
+//
+// The same block then writes the step's launch records: every gather work item resolved against every layer's
+// descriptor table. The list of a layer ends with records whose cnt is 0.
 __global__ void __launch_bounds__(1024) plora_meta_group_kernel(const int* __restrict__ tiles, int* __restrict__ segs,
-                                                                 SegLayout lay, int* __restrict__ status) {
+                                                                 SegLayout lay, int* __restrict__ status,
+                                                                 const plora_desc* __restrict__ tables,
+                                                                 const int* __restrict__ site_cols, int n_sites,
+                                                                 PloraRec* __restrict__ recs, int rec_cap) {
     extern __shared__ int sm[];
     __shared__ int sh[33];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -299,60 +343,16 @@ __global__ void __launch_bounds__(1024) plora_meta_group_kernel(const int* __res
         segs[SEG_N_TILES] = n_tiles;
         segs[SEG_STATUS] = any_bad ? PLORA_ERR_ARG : 0;
     }
-}
-
-// ---------------------------------------------------------------------------------------------
-// Launch records of the step: block `site` resolves every gather work item against that layer's descriptor
-// table, once, so that the kernels of the layers make one metadata fetch per block. The list of a layer ends
-// with records whose cnt is 0.
-__global__ void __launch_bounds__(256) plora_meta_records_kernel(const int* __restrict__ segs, SegLayout lay,
-                                                                  const plora_desc* __restrict__ tables,
-                                                                  const int* __restrict__ site_cols, PloraRec* __restrict__ recs,
-                                                                  int rec_cap) {
-    const int site = blockIdx.x;
-    pdl_wait();  // the grouping kernel's output
-    const int n_work = min(segs[SEG_N_WORK], rec_cap - 1);
-    const plora_desc* table = tables + (size_t)site * (size_t)(lay.max_slots + 1);
-    PloraRec* out = recs + (size_t)site * (size_t)rec_cap;
-    const int cols = site_cols[2 * site], pieces = site_cols[2 * site + 1];
-    const int end = min(rec_cap, n_work + PLORA_REC_TERM);
-    for (int w = threadIdx.x; w < end; w += blockDim.x) {
-        uint4* o = reinterpret_cast<uint4*>(out + w);
-        if (w >= n_work) {
-            o[0] = make_uint4(0u, 0u, 0u, (uint32_t)cols);
-            continue;
+    // launch records (the barrier above made the work items, written by other threads of this block, visible)
+    if (recs != nullptr) {
+        const int nw = min(n_work, rec_cap - 1), end = min(rec_cap, nw + PLORA_REC_TERM);
+        for (int i = tid; i < n_sites * end; i += 1024) {
+            const int site = i / end, w = i - site * end;
+            uint4* o = reinterpret_cast<uint4*>(recs + (size_t)site * (size_t)rec_cap + w);
+            const int cols = site_cols[2 * site];
+            if (w >= nw) o[0] = make_uint4(0u, 0u, 0u, (uint32_t)cols);
+            else write_record(o, segs, lay, tables + (size_t)site * (size_t)(lay.max_slots + 1), w, cols, site_cols[2 * site + 1]);
         }
-        const uint4* work = reinterpret_cast<const uint4*>(segs + lay.work() + PLORA_WORK_WORDS * w);
-        const uint4 head = work[0];  // slot, perm start, count, 0
-        const int slot = (int)head.x;
-        const uint4* d = reinterpret_cast<const uint4*>(table + slot);  // 112 bytes: a, b[4], rank, r, r_off, off, rows
-        uint4 dv[7];
-#pragma unroll
-        for (int i = 0; i < 7; i++) dv[i] = d[i];
-        // Desc: a | b0 b1 | b2 b3 | rank r0 r1 r2 | r3 ro0 ro1 ro2 | ro3 o0 o1 o2 | o3 rows0 rows1 rows2 | rows3 pad
-        const uint32_t* dw = reinterpret_cast<const uint32_t*>(dv);
-        o[0] = make_uint4(head.z, head.x, dw[10], (uint32_t)cols);  // cnt, slot, rank, cols
-        o[1] = make_uint4(dw[0], dw[1], dw[2], dw[3]);              // a, b[0]
-        o[2] = make_uint4(dw[4], dw[5], dw[6], dw[7]);              // b[1], b[2]
-        o[3] = make_uint4(dw[8], dw[9], dw[11], dw[12]);            // b[3], r[0], r[1]
-        o[4] = make_uint4(dw[13], dw[14], dw[15], dw[16]);          // r[2], r[3], r_off[0], r_off[1]
-        o[5] = make_uint4(dw[17], dw[18], dw[19], dw[20]);          // r_off[2], r_off[3], off[0], off[1]
-        o[6] = make_uint4(dw[21], dw[22], dw[23], dw[24]);          // off[2], off[3], rows[0], rows[1]
-        // the slot's output columns over its targeted parts laid end to end, and the even share of them that
-        // one block of the layer's cluster kernel expands
-        uint32_t cat[PLORA_MAX_PARTS], ntot = 0;
-#pragma unroll
-        for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-            cat[p] = ntot;
-            if ((int)dw[11 + p] > 0) ntot += dw[23 + p];
-        }
-        const uint32_t share = pieces > 0 ? (((ntot + pieces - 1) / pieces + 1) & ~1u) : 0u;
-        o[7] = make_uint4(dw[25], dw[26], ntot, share);             // rows[2], rows[3], ntot, share
-        o[8] = work[1];                                             // the token rows
-        o[9] = work[2];
-        o[10] = work[3];
-        o[11] = work[4];
-        o[12] = make_uint4(cat[0], cat[1], cat[2], cat[3]);
     }
 }
 
@@ -698,9 +698,10 @@ cudaError_t plora_kernels_init(const SegLayout& lay) {
     return cudaFuncSetAttribute(plora_expand_gather_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
 }
 
-cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status,
-                                    cudaStream_t st) {
-    plora_meta_group_kernel<<<1, 1024, plora_meta_group_smem(lay), st>>>(tiles, segs, lay, status);
+cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status, const plora_desc* tables,
+                                    const int32_t* site_cols, int n_sites, PloraRec* recs, int rec_cap, cudaStream_t st) {
+    plora_meta_group_kernel<<<1, 1024, plora_meta_group_smem(lay), st>>>(tiles, segs, lay, status, tables, site_cols, n_sites, recs,
+                                                                         rec_cap);
     return cudaGetLastError();
 }
 
@@ -721,12 +722,6 @@ cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t 
     return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
 }
 }  // namespace
-
-cudaError_t plora_launch_meta_records(const int32_t* segs, SegLayout lay, const plora_desc* tables, const int32_t* site_cols,
-                                      int n_sites, PloraRec* recs, int rec_cap, cudaStream_t st) {
-    return launch_pdl(plora_meta_records_kernel, dim3((unsigned)n_sites), dim3(256), 0, st, true, segs, lay, tables, site_cols,
-                      recs, rec_cap);
-}
 
 #define PLORA_GRID_Z_CAP 64  // blocks along the work-item axis; more work items are walked in a loop
 

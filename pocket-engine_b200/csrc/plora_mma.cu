@@ -15,61 +15,13 @@
 
 #include "plora_internal.h"
 #include "plora_device.cuh"
+#include "plora_tc.cuh"
 
 typedef __nv_bfloat16 bf16;
-
 
 namespace {
 
 // ---- tcgen05 ----
-
-__device__ __forceinline__ bool elect_one() {
-    uint32_t p;
-    asm volatile("{\n.reg .pred e;\nelect.sync _|e, 0xffffffff;\nselp.u32 %0, 1, 0, e;\n}\n" : "=r"(p));
-    return p != 0;
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// D (tensor memory) (+)= A (shared) . B (shared), bf16 inputs, f32 accumulate
-__device__ __forceinline__ void umma_bf16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d),
-        "l"(a), "l"(b), "r"(idesc), "r"(acc)
-        : "memory");
-}
-
-// arrives on `bar` once this thread's earlier MMAs are complete
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-
-// 32 consecutive columns of this warp's 32 lanes: v[j] = column (col + j) of lane (32 * (warp % 4) + lane)
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-        "%29,%30,%31}, [%32];\n"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 // 8 consecutive columns, without the wait (several loads, then one tmem_ld_wait)
 __device__ __forceinline__ void tmem_ld8_nowait(uint32_t taddr, float* v) {
@@ -80,7 +32,6 @@ __device__ __forceinline__ void tmem_ld8_nowait(uint32_t taddr, float* v) {
 #pragma unroll
     for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // v[0] = balanced binary tree sum of v[0..n), n a power of two <= 8 (W values per item)
 template <int W>
@@ -94,19 +45,10 @@ __device__ __forceinline__ void tree_sum(float (&v)[PLORA_TILE_SPLIT_MAX][W], in
                 for (int q = 0; q < W; q++) v[a][q] += v[a + stride][q];
 }
 
-// Shared-memory matrix descriptor: start address, leading (K direction) and stride (8-row group) byte
-// offsets, descriptor version 1, swizzle mode in bits 61-63 (0 none, 2 = 128 bytes).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo, uint32_t swizzle) {
-    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
-           ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46) | ((uint64_t)swizzle << 61);
-}
-
 // Instruction descriptor, kind::f16: f32 accumulator, bf16 A and B, both K-major, M rows by N columns.
 __device__ __forceinline__ uint32_t umma_idesc_bf16(int M, int N) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
-
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
     const uint32_t n = valid ? 16u : 0u;  // a zero source size fills the 16 bytes with zeros
@@ -118,34 +60,10 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// 2-D tiled TMA load (no cluster-wide delivery: this block's shared memory only)
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-            smem_u32(dst)),
-        "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
-        : "memory");
-}
-
 // Makes a tensor map that sits in global memory (written by a copy earlier in the stream) visible to this
 // thread's tensor copies.
 __device__ __forceinline__ void tmap_acquire(const CUtensorMap* map) {
     asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(map) : "memory");
-}
-
-// A wait that may span a block's whole main loop: the same bounded try-wait, with a pause between tries
-// (about a second in all before it gives up).
-__device__ __forceinline__ bool mbar_wait_long(uint64_t* bar, uint32_t parity, int* status) {
-    for (int i = 0; i < (1 << 22); i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 64) __nanosleep(200);
-    }
-    atomicMax(status, PLORA_ERR_TIMEOUT);
-    return false;
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 #define MMA_M 128
@@ -283,8 +201,8 @@ __global__ void __launch_bounds__(128) plora_shrink_mma_kernel(const __grid_cons
                     const uint64_t da = da0 + st16 + (uint32_t)u * abox16;
 #pragma unroll
                     for (int kk = 0; kk < SHR_KSTEP / 16; kk++) {
-                        umma_bf16(dacc, dx + 2 * kk, da + 2 * kk, idesc_lo, (first | kk) != 0);
-                        if (R > 256) umma_bf16(dacc + 256, dx + 2 * kk, da + (256 * 128 >> 4) + 2 * kk, idesc_hi, (first | kk) != 0);
+                        umma<1>(dacc, dx + 2 * kk, da + 2 * kk, idesc_lo, (first | kk) != 0);
+                        if (R > 256) umma<1>(dacc + 256, dx + 2 * kk, da + (256 * 128 >> 4) + 2 * kk, idesc_hi, (first | kk) != 0);
                     }
                     if (++first == spc) {  // the next step starts the next chunk's accumulator
                         first = 0;
@@ -477,10 +395,10 @@ __global__ void __launch_bounds__(128) plora_expand_mma_kernel(const float* __re
                 tc_fence_after();
                 const uint32_t a_hi = smem_u32(Ahi), a_lo = smem_u32(Alo), b = smem_u32(Bs[nb & 1]);
                 for (int kk = 0; kk < r / 16; kk++)
-                    umma_bf16(tmem, umma_desc(a_hi + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc,
+                    umma<1>(tmem, umma_desc(a_hi + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc,
                               kk != 0);
                 for (int kk = 0; kk < r / 16; kk++)
-                    umma_bf16(tmem, umma_desc(a_lo + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, 1);
+                    umma<1>(tmem, umma_desc(a_lo + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, 1);
                 umma_commit(&done);
             }
             __syncwarp();
@@ -573,15 +491,7 @@ struct ExpandYMaps {
 #define EXP_RING_MAX 8
 #define EXP_SLOT_BYTES 4096
 
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, const void* src) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0), "r"(c1),
-                 "r"(smem_u32(src))
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 template <bool F32, int WPQ>  // WPQ: warps per 32 rows (2 or 4)
 __global__ void __launch_bounds__(32 * (4 * WPQ + 1)) plora_expand_tma_kernel(const float* __restrict__ S, size_t s_stride, int lds, int K,
@@ -674,9 +584,9 @@ __global__ void __launch_bounds__(32 * (4 * WPQ + 1)) plora_expand_tma_kernel(co
                 const uint32_t a_hi = smem_u32(Ahi), a_lo = smem_u32(Alo), b = smem_u32(Bs[nb & 1]);
                 const uint32_t acc = tmem + (uint32_t)(nb & 1) * 128u;
                 for (int kk = 0; kk < r / 16; kk++)
-                    umma_bf16(acc, umma_desc(a_hi + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, kk != 0);
+                    umma<1>(acc, umma_desc(a_hi + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, kk != 0);
                 for (int kk = 0; kk < r / 16; kk++)
-                    umma_bf16(acc, umma_desc(a_lo + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, 1);
+                    umma<1>(acc, umma_desc(a_lo + kk * 256, 128, sbo, 0), umma_desc(b + kk * 256, 128, sbo, 0), idesc, 1);
                 umma_commit(&done[nb & 1]);
             }
             __syncwarp();
@@ -844,7 +754,7 @@ __global__ void __launch_bounds__(32 * (4 * WPQ + 1)) plora_expand_tma_kernel(co
                     tma_store_2d(ymap, ycol0 + q * CW, start + wrow0, sl);
                     bulk_commit();
                     if (nst == 1) {  // one slot: wait for this store to have read it, then refill it
-                        bulk_wait_read_0();
+                        bulk_wait_read();
                         if (i + 1 < my_n) load_y(i + 1);
                     } else {  // the store before this one has read its slot: refill that slot
                         bulk_wait_read_1();

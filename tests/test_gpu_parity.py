@@ -358,7 +358,7 @@ def test_kernel_profile_names_the_launches(pe, wls):
     harness.run_gpu(pe, loras, wl, False, meta="device")
     prof = loras.profile_end()
     assert prof["site kernel"][0] == 4 and prof["shrink"][0] == 4 and prof["expand"][0] == 4
-    assert prof["meta_group"][0] == 2 and prof["meta_records"][0] == 2 and prof["meta_tiles"][0] == 2
+    assert prof["meta_group"][0] == 2 and prof["meta_tiles"][0] == 2
     assert all(us > 0 for _, us in prof.values())
     assert loras.profile_end() == {}  # closed: nothing is collected any more
     harness.run_gpu(pe, loras, wl, False)
