@@ -110,6 +110,12 @@ __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.w
 // ... and have been written to global memory
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+    return v;
+}
+
 // Programmatic dependent launch. Every kernel of the path waits for the kernels before it and only then
 // lets the next one start its prologue, so a prologue may read anything written two or more kernels back
 // (slabs, descriptors, the step's grouping) but nothing the kernel right before it writes.

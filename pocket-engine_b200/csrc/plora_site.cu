@@ -668,9 +668,18 @@ size_t plora_site_plan(int K, int parts, int max_rank, int total_rows, int* nsub
 }
 
 cudaError_t plora_site_init() {
-    cudaError_t e = cudaFuncSetAttribute(plora_site_gather_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(plora_site_gather_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    // The split of an SM's memory between L1 and shared memory is fixed while any block runs on it. Layers of
+    // different widths ask for different amounts of shared memory per block; left to itself the driver would pick
+    // a split per launch, and a block of the next layer would then find no room beside the blocks still running
+    // under a smaller split. Every launch of this kernel asks for the largest split.
+    cudaError_t e = cudaSuccess;
+    for (int f32 = 0; f32 < 2 && e == cudaSuccess; f32++) {
+        const void* fn = f32 ? reinterpret_cast<const void*>(plora_site_gather_kernel<true>)
+                             : reinterpret_cast<const void*>(plora_site_gather_kernel<false>);
+        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    }
+    return e;
 }
 
 // How many clusters of the layer's plan the device runs at once (0 on failure)
