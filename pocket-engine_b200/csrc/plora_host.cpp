@@ -273,6 +273,7 @@ int plora_create(const plora_site* sites, int n_sites, int base_gguf, int key_he
             if (const char* e = getenv("PLORA_FUSED_TILE_ROWS")) h->fused_tile_rows = std::max(1, atoi(e));
             if (const char* e = getenv("PLORA_TILE_LATE")) h->tile_late = e[0] != '0';
             if (const char* e = getenv("PLORA_PREFETCH_NEXT")) h->prefetch_next = e[0] != '0';
+            if (const char* e = getenv("PLORA_SITE_RELEASE")) h->site_release = atoi(e);
             if (rc == PLORA_OK) {
                 memset(h->host_tables, 0, h->table_bytes);
                 check("zero tables", cudaMemset(h->tables, 0, h->table_bytes));  // src/lora.rs:494
@@ -865,7 +866,8 @@ int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint
        plora_launch_site((const void*)(uintptr_t)x, site.cols, site.cols, recs_of(h, hook->site), h->rec_cap,
                          h->prefetch_next && hook->site + 1 < (int)h->sites.size() ? recs_of(h, hook->site + 1) : nullptr,
                          (void*)(uintptr_t)y, ldy, f32_out, (int)site.parts.size(), h->max_rank, total, work_cap,
-                         site.max_clusters, h->early_x, bounds_of(h, hook, rows, ldy), h->status, pdl, as_stream(stream)));
+                         site.max_clusters, (h->early_x ? 1 : 0) | ((h->site_release >= 0 && h->site_release <= 4 ? h->site_release : (h->early_x ? 0 : 1)) << 1),
+                         bounds_of(h, hook, rows, ldy), h->status, pdl, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min) {
         CUK(h, "shrink (tile path)",
            plora_launch_shrink_mma((const void*)(uintptr_t)x, rows, site.cols, site.cols, (const int32_t*)(uintptr_t)step->segs,

@@ -157,6 +157,7 @@ struct plora {
     int tile_split_force = 0;  // plora_set_tile_split: 0 = chosen per launch
     int apply_mode = 1;     // plora_apply: 0 = shrink / expand pair, 1 = one cluster kernel per layer where it fits
     bool early_x = false;   // plora_set_early_x: plora_apply may read x ahead of its dependency wait
+    int site_release = -1;  // when the cluster kernel releases the next kernel (-1: chosen by mode)
     bool prefetch_next = true;  // the cluster kernel asks L2 for the next layer's slabs of its work item (PLORA_PREFETCH_NEXT=0: off)
     bool site_ok = false;   // the cluster kernel's attributes were set
     bool fp8_ok = false;    // the fused FP8 layer can run
@@ -223,7 +224,7 @@ size_t plora_site_plan(int K, int parts, int max_rank, int total_rows, int* nsub
 int plora_site_max_clusters(int K, int parts, int max_rank, int total_rows);
 cudaError_t plora_launch_site(const void* x, int ldx, int K, const PloraRec* recs, int rec_cap, const PloraRec* next_recs,
                               void* y, int ldy, int f32_out, int parts, int max_rank, int total_rows, int work_cap,
-                              int max_clusters, bool early_x, const PloraBounds& bnd, int* status, bool pdl, cudaStream_t st);
+                              int max_clusters, int mode, const PloraBounds& bnd, int* status, bool pdl, cudaStream_t st);
 cudaError_t plora_mma_init();
 cudaError_t plora_fp8_init(int max_rank);
 cudaError_t plora_launch_fp8_quant(const void* x, int rows, int ldx, int K, void* xq, float* st, cudaStream_t stream);

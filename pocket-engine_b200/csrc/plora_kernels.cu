@@ -687,15 +687,19 @@ cudaError_t plora_kernels_init(const SegLayout& lay) {
                                          (int)plora_meta_group_smem(lay) > 48 * 1024 ? (int)plora_meta_group_smem(lay)
                                                                                        : 48 * 1024);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(plora_shrink_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 136 * 1024);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(plora_expand_gather_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(plora_expand_gather_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(plora_expand_gather_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(plora_expand_gather_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    // The few-token kernels overlap with their neighbours in the stream (programmatic dependent launch), and an SM's
+    // split between L1 and shared memory is fixed while any block runs on it: all of them ask for the largest
+    // split, so that a block of the next kernel finds room beside the blocks of this one.
+    const void* fns[5] = {reinterpret_cast<const void*>(plora_shrink_gather_kernel),
+                          reinterpret_cast<const void*>(plora_expand_gather_kernel<false, 1>),
+                          reinterpret_cast<const void*>(plora_expand_gather_kernel<true, 1>),
+                          reinterpret_cast<const void*>(plora_expand_gather_kernel<false, 2>),
+                          reinterpret_cast<const void*>(plora_expand_gather_kernel<true, 2>)};
+    for (int i = 0; i < 5 && e == cudaSuccess; i++) {
+        e = cudaFuncSetAttribute(fns[i], cudaFuncAttributeMaxDynamicSharedMemorySize, i == 0 ? 136 * 1024 : 112 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fns[i], cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    }
+    return e;
 }
 
 cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status, const plora_desc* tables,

@@ -6,13 +6,16 @@
 // the layer's own matrix multiply).
 //
 // Order of events in a block, chosen so that nothing that can be known early waits for anything:
-//   1. dependents are released at once (their prologues touch only slabs and launch records);
+//   1. (when the caller vouched for x) the next kernel of the stream is released at once;
 //   2. one fetch of the work item's launch record (descriptor and token rows, written once per step);
 //   3. bulk async copies of the block's rows of A and of its share of B into shared memory, L2 prefetch hints
 //      for the x and y lines it will touch, and an L2 prefetch of the same work item's slabs of the next layer;
 //   4. the dependency wait (the kernel before, typically the layer's matrix multiply, wrote y);
-//   5. x into shared memory, shrink, exchange, expand, y read-modify-write.
-// Nothing before step 4 binds a value of x or y, unless the caller vouched for x (early_x).
+//   5. x into shared memory, shrink, release of the next kernel of the stream (its prologue, steps 2 and 3, then
+//      overlaps this kernel's exchange and expand), exchange, expand, y read-modify-write.
+// Nothing before step 4 binds a value of x or y, unless the caller vouched for x (early_x). The release point was
+// measured: released at kernel start, the next layer's blocks take the places that this layer's own late clusters
+// need (a B200 holds about 33 clusters of this kernel, two neighbouring layers can need 48) and sit in their wait.
 //
 // Arithmetic: 16-token tiles on the warp-level tensor-core instruction (m16n8k16, bf16 in, f32 accumulate), the
 // shape the engine's own kernels use for their 16-token tiles. On the CUDA cores the step is bound by
@@ -330,7 +333,7 @@ __device__ __forceinline__ void expand_fast(uint32_t s3_part, uint32_t sp_pad, u
 template <bool F32>
 __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THREADS, 2)
     plora_site_gather_kernel(const bf16* __restrict__ X, int ldx, int K, const PloraRec* __restrict__ recs, int rec_cap,
-                             const PloraRec* __restrict__ next_recs, void* Y, int ldy, SiteShape sh, int early_x,
+                             const PloraRec* __restrict__ next_recs, void* Y, int ldy, SiteShape sh, int mode,
                              int* __restrict__ status PLORA_BOUNDS_PARAM) {
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ __align__(8) uint64_t bars[4];  // A rows, x chunks, B rows, the cluster's partials
@@ -352,7 +355,11 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
     // The kernels after this one may start their prologues now: before their own waits they touch slabs and
     // launch records only (and x, where their caller vouched for it); every store of the path comes after a
     // wait, and every grid waits for its predecessor before it completes.
-    pdl_trigger();
+    // mode: bit 0 = the caller vouched for x; bits 1-2 = when the next kernel of the stream is released (0: at
+    // once, 1: after the shrink, 2: after the exchange)
+    const int early_x = mode & 1, release_at = mode >> 1;  // (3, 4: after the wait, after A and x landed)
+    bool triggered = release_at == 0;
+    if (triggered) pdl_trigger();
     if (tid == 0) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
@@ -473,6 +480,10 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
             pdl_wait();
             waited = true;
         }
+        if (!triggered && release_at == 3) {
+            pdl_trigger();
+            triggered = true;
+        }
         // y of this lane's first expand step (first part of the share), on its way while the shrink and the exchange run
         uint4 pre0 = make_uint4(0u, 0u, 0u, 0u), pre1 = pre0;
         int pre_part = -1;
@@ -503,6 +514,10 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
             }
             if (alive) alive = mbar_wait(&bars[0], ph_ax, status) && mbar_wait(&bars[1], ph_ax, status);
             ph_ax ^= 1;
+        }
+        if (!triggered && release_at == 4) {
+            pdl_trigger();
+            triggered = true;
         }
         // rows of A in groups of 64 (8 tiles of 8): 32 accumulators per lane
         for (int j0 = 0; j0 < R; j0 += 64) {
@@ -540,6 +555,10 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
                 Sp[t * sh.rmax + j] = acc;
             }
         }
+        if (!triggered && release_at == 1) {
+            pdl_trigger();
+            triggered = true;
+        }
         // ---- the eight partials meet: every block tells every block that its Sp is written, then reads all
         // eight and adds them in block order
         __syncthreads();
@@ -571,6 +590,10 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
             }
         }
         cluster_arrive_relaxed();  // my reads of the others' partials are done
+        if (!triggered) {
+            pdl_trigger();
+            triggered = true;
+        }
         if (!waited) {             // early_x: everything so far ran ahead of the kernel before; y must not
             pdl_wait();
             waited = true;
@@ -701,7 +724,7 @@ int plora_site_max_clusters(int K, int parts, int max_rank, int total_rows) {
 
 cudaError_t plora_launch_site(const void* x, int ldx, int K, const PloraRec* recs, int rec_cap, const PloraRec* next_recs,
                               void* y, int ldy, int f32_out, int parts, int max_rank, int total_rows, int work_cap,
-                              int max_clusters, bool early_x, const PloraBounds& bnd, int* status, bool pdl, cudaStream_t st) {
+                              int max_clusters, int mode, const PloraBounds& bnd, int* status, bool pdl, cudaStream_t st) {
     (void)bnd;
     int nsub = 1;
     const size_t smem = plora_site_plan(K, parts, max_rank, total_rows, &nsub);
@@ -723,7 +746,7 @@ cudaError_t plora_launch_site(const void* x, int ldx, int K, const PloraRec* rec
     cfg.numAttrs = pdl ? 1 : 0;
     if (f32_out)
         return cudaLaunchKernelEx(&cfg, plora_site_gather_kernel<true>, reinterpret_cast<const bf16*>(x), ldx, K, recs, rec_cap,
-                                  next_recs, y, ldy, pl.sh, early_x ? 1 : 0, status PLORA_BOUNDS_ARG(bnd));
+                                  next_recs, y, ldy, pl.sh, mode, status PLORA_BOUNDS_ARG(bnd));
     return cudaLaunchKernelEx(&cfg, plora_site_gather_kernel<false>, reinterpret_cast<const bf16*>(x), ldx, K, recs, rec_cap,
-                              next_recs, y, ldy, pl.sh, early_x ? 1 : 0, status PLORA_BOUNDS_ARG(bnd));
+                              next_recs, y, ldy, pl.sh, mode, status PLORA_BOUNDS_ARG(bnd));
 }
