@@ -423,12 +423,14 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
                 }
             }
         }
-        // ---- slab requests (before the dependency wait): warp 0 asks for the block's rows of A
-        if (warp == 0 && klen > 0) {
+        // ---- slab requests (before the dependency wait): the block's rows of A, one bulk copy per row. The copies
+        // of the lanes of one warp are issued one after another, so the rows go round the warps: row r is lane
+        // r / 8 of warp r % 8. (The barrier's one arrival carries the whole byte count; copies that land before it
+        // only run the count down early.)
+        if (klen > 0) {
             const bf16* A = reinterpret_cast<const bf16*>(srec.a) + k0;
-            if (lane == 0) mbar_expect_tx(&bars[0], (uint32_t)R * kbytes);
-            __syncwarp();
-            for (int r = lane; r < R; r += 32)
+            if (tid == 0) mbar_expect_tx(&bars[0], (uint32_t)R * kbytes);
+            for (int r = warp + SITE_WARPS * lane; r < R; r += SITE_THREADS)
                 bulk_g2s(As + (size_t)(r >> 6) * sh.g_stride + (size_t)(r & 63) * sh.kb_pad, A + (size_t)r * K, kbytes, &bars[0]);
         }
         // a half step at the end of the rows multiplies zeros
@@ -638,8 +640,10 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
         __syncthreads();  // shared memory is reused by the next work item
     }
     if (!met) cluster_wait();  // a block must not leave while a peer may still be arriving at the start-up barrier
-    // a grid completes only after the grids before it: a block that found no work still waits
-    if (!waited) pdl_wait();
+    // A grid completes only after the grids before it. Blocks with work have waited; of the blocks that found none,
+    // one waits for all (a grid is complete only when every block has left), so that the others give their places
+    // on the SMs back at once instead of holding them until the kernel before has finished.
+    if (!waited && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) pdl_wait();
 }
 
 struct Plan {
