@@ -507,9 +507,13 @@ cudaError_t plora_fp8_init(int max_rank) {
     if ((size_t)F8_BN * max_rank * 2 + (size_t)4 * PLORA_MAX_PARTS * max_rank * 4 > (size_t)fused_ring_bytes() / 2)
         return cudaErrorInvalidValue;
     const int smem = (int)fused_smem();
-    cudaError_t e = cudaFuncSetAttribute(plora_fp8_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    // the two small kernels that run right before the layer kernel ask for the same split of the SM
+    cudaError_t e0 = plora_kernel_shared(reinterpret_cast<const void*>(plora_fp8_quant_rows_kernel), 0);
+    if (e0 == cudaSuccess) e0 = plora_kernel_shared(reinterpret_cast<const void*>(plora_s_reduce_kernel), 0);
+    if (e0 != cudaSuccess) return e0;
+    cudaError_t e = plora_kernel_shared(reinterpret_cast<const void*>(plora_fp8_fused_kernel<false>), smem);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(plora_fp8_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    return plora_kernel_shared(reinterpret_cast<const void*>(plora_fp8_fused_kernel<true>), smem);
 }
 
 cudaError_t plora_launch_fp8_quant(const void* x, int rows, int ldx, int K, void* xq, float* st, cudaStream_t stream) {

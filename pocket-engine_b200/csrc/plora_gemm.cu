@@ -345,10 +345,10 @@ cudaError_t plora_gemm_init() {
     }
     cudaError_t e;
     const int smem = (int)gemm_smem();
-    if ((e = cudaFuncSetAttribute(plora_gemm_fused_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return e;
-    if ((e = cudaFuncSetAttribute(plora_gemm_fused_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return e;
-    if ((e = cudaFuncSetAttribute(plora_gemm_fused_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return e;
-    return cudaFuncSetAttribute(plora_gemm_fused_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if ((e = plora_kernel_shared(reinterpret_cast<const void*>(plora_gemm_fused_kernel<0, false>), smem))) return e;
+    if ((e = plora_kernel_shared(reinterpret_cast<const void*>(plora_gemm_fused_kernel<0, true>), smem))) return e;
+    if ((e = plora_kernel_shared(reinterpret_cast<const void*>(plora_gemm_fused_kernel<1, false>), smem))) return e;
+    return plora_kernel_shared(reinterpret_cast<const void*>(plora_gemm_fused_kernel<1, true>), smem);
 }
 
 // Whether a layer's shapes fit the kernel: parts starting at multiples of 256 columns (so does every block),

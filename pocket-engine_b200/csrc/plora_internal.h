@@ -218,6 +218,16 @@ cudaError_t plora_launch_meta_tiles(const int32_t* cu, const int32_t* seq_slot, 
 // site_info: per layer {input width, blocks that share a work item's output columns in the cluster kernel (0: none)}
 cudaError_t plora_launch_meta_group(const int32_t* tiles, int32_t* segs, SegLayout lay, int* status, const plora_desc* tables,
                                     const int32_t* site_info, int n_sites, PloraRec* recs, int rec_cap, cudaStream_t st);
+// Dynamic shared-memory limit of a kernel together with a request for the largest shared-memory split of the SM.
+// Kernels of this library overlap with their neighbours in the stream (programmatic dependent launch); an SM's
+// split between L1 and shared memory is fixed while any block runs on it, so kernels that each let the driver
+// pick their own split would keep each other's blocks off the SMs.
+inline cudaError_t plora_kernel_shared(const void* fn, int max_dynamic_bytes) {
+    cudaError_t e = cudaSuccess;
+    if (max_dynamic_bytes > 0) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dynamic_bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    return e;
+}
 cudaError_t plora_kernels_init(const SegLayout& lay);
 cudaError_t plora_site_init();
 size_t plora_site_plan(int K, int parts, int max_rank, int total_rows, int* nsub);

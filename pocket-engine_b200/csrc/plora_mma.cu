@@ -793,16 +793,16 @@ cudaError_t plora_mma_init() {
         if (!fn || q != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
         g_encode = reinterpret_cast<encode_tiled_fn>(fn);
     }
-    cudaError_t e = cudaFuncSetAttribute(plora_shrink_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = plora_kernel_shared(reinterpret_cast<const void*>(plora_shrink_mma_kernel), 200 * 1024);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(plora_expand_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 172 * 1024);
+    e = plora_kernel_shared(reinterpret_cast<const void*>(plora_expand_mma_kernel<false>), 172 * 1024);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(plora_expand_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 172 * 1024);
+    e = plora_kernel_shared(reinterpret_cast<const void*>(plora_expand_mma_kernel<true>), 172 * 1024);
     if (e != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(plora_expand_tma_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024))) return e;
-    if ((e = cudaFuncSetAttribute(plora_expand_tma_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024))) return e;
-    if ((e = cudaFuncSetAttribute(plora_expand_tma_kernel<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024))) return e;
-    return cudaFuncSetAttribute(plora_expand_tma_kernel<true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if ((e = plora_kernel_shared(reinterpret_cast<const void*>(plora_expand_tma_kernel<false, 2>), 220 * 1024))) return e;
+    if ((e = plora_kernel_shared(reinterpret_cast<const void*>(plora_expand_tma_kernel<true, 2>), 220 * 1024))) return e;
+    if ((e = plora_kernel_shared(reinterpret_cast<const void*>(plora_expand_tma_kernel<false, 4>), 220 * 1024))) return e;
+    return plora_kernel_shared(reinterpret_cast<const void*>(plora_expand_tma_kernel<true, 4>), 220 * 1024);
 }
 
 namespace {
