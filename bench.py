@@ -309,11 +309,32 @@ def run_ours(args, rank, world, local_rank):
                                       False, lora=st, main=m, side=side_h if depth == 1 else None, fused=fused)
             y_out[lane].copy_(S["yreg"], non_blocking=True)
 
+    # One CUDA graph per (copy, lane) holds the whole step as issued above (the two host-to-device copies, the metadata
+    # kernels, the layers, the device-to-host copy), so that a step costs the host one replay instead of a dozen calls
+    # through the binding: at 190 us per step the Python side of those calls was what bounded the rate, not PCIe.
+    e2e_graphs = {}
+    if not args.no_e2e_graph:
+        torch.cuda.synchronize()
+        for k in range(len(e2e_sets)):
+            for lane in range(depth):
+                if len(e2e_sets) % depth == 0 and k % depth != lane:
+                    continue  # with an even number of copies a copy always meets the same lane
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=lanes[lane]):
+                    e2e_issue(e2e_sets[k], lane)
+                e2e_graphs[(k, lane)] = g
+        torch.cuda.synchronize()
+
     def e2e_run(first, count):
         for i in range(count):
-            e2e_issue(e2e_sets[(first + i) % len(e2e_sets)], i % depth)
+            k, lane = (first + i) % len(e2e_sets), (first + i) % depth
+            if (k, lane) in e2e_graphs:
+                with torch.cuda.stream(lanes[lane]):
+                    e2e_graphs[(k, lane)].replay()
+            else:
+                e2e_issue(e2e_sets[k], lane)
             if depth == 2 and i >= 1:
-                lanes[(i - 1) % depth].synchronize()
+                lanes[(first + i - 1) % depth].synchronize()
             elif depth == 1:
                 lanes[0].synchronize()
         for s in lanes:
@@ -405,7 +426,8 @@ def run_ours(args, rank, world, local_rank):
                 "early_x": bool(args.early_x), "inner_repeats": inner,
                 "timed_region": f"{args.steps} steps x {inner} passes of the block; value and ms_per_step are per pass"},
         "e2e": {"value": world * wl.tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps, "steps_in_flight": depth},
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps, "steps_in_flight": depth,
+                "launch": "one CUDA graph per copy and lane (copies, metadata kernels, layers)" if e2e_graphs else "individual calls"},
         "gpu_launches": ((4 if args.path == "apply" else 8) if decode else 16) * args.steps * inner,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                      "peak_kind": peak_kind, "traffic": NCU_TRAFFIC.get((wl.name, dom)), "us_per_launch": kern[dom]["us"],
@@ -1037,6 +1059,7 @@ def main():
     ap.add_argument("--inner-repeats", type=int, default=50,
                     help="decode workload: passes of the block per timed step (the result is reported per pass)")
     ap.add_argument("--two-part", action="store_true", help="fp8 workload: the engine's two-part gate + up layer (4096 -> 24576)")
+    ap.add_argument("--no-e2e-graph", action="store_true", help="end-to-end steps as individual calls instead of one CUDA graph per copy")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel layer set that the default run appends")
     ap.add_argument("--streams", type=int, default=1, choices=[1, 2],
                     help="1: one stream, kernels chained by programmatic dependent launch; 2: the engine's "
