@@ -112,12 +112,11 @@ def shared_config(wl, work):
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels that dominate the two block
 # workloads, from the ncu captures summarised under profiles/ (decode_block_cluster_kernel_launch_records.md: the
-# gate/up layer's cluster kernel at full size; its reads include the 8.4 MB of the NEXT layer's slabs that the kernel
-# asks L2 for, which are that layer's algorithmic bytes, and its y writes stay in L2.
+# gate/up layer's cluster kernel at full size: its slabs, x and y are read once, and its y writes stay in L2.
 # prefill_block_tile_kernels_tma_pipelines.md: the gate/up expand captured on 2 of the 8 sequences, traffic scaled by
 # 4 since it grows with the token count).
 NCU_TRAFFIC = {
-    ("decode-4096x12288-64tok-16xr16", "site[2]"): 27.99e6,
+    ("decode-4096x12288-64tok-16xr16", "site[2]"): 19.60e6,
     ("decode-4096x12288-64tok-16xr16", "expand[2]"): 15.02e6,
     ("prefill-4096x12288-8x2048-r64", "expand[2]"): 4 * (214.6e6 + 148.2e6),
 }

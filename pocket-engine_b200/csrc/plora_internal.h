@@ -158,7 +158,7 @@ struct plora {
     int apply_mode = 1;     // plora_apply: 0 = shrink / expand pair, 1 = one cluster kernel per layer where it fits
     bool early_x = false;   // plora_set_early_x: plora_apply may read x ahead of its dependency wait
     int site_release = -1;  // when the cluster kernel releases the next kernel (-1: chosen by mode)
-    bool prefetch_next = true;  // the cluster kernel asks L2 for the next layer's slabs of its work item (PLORA_PREFETCH_NEXT=0: off)
+    bool prefetch_next = false;  // the cluster kernel asks L2 for the next layer's slabs of its work item (PLORA_PREFETCH_NEXT=1: on)
     bool site_ok = false;   // the cluster kernel's attributes were set
     bool fp8_ok = false;    // the fused FP8 layer can run
     bool gemm_ok = false;   // the one-kernel layer for prefill-sized steps can run

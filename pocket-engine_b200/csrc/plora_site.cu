@@ -9,7 +9,8 @@
 //   1. (when the caller vouched for x) the next kernel of the stream is released at once;
 //   2. one fetch of the work item's launch record (descriptor and token rows, written once per step);
 //   3. bulk async copies of the block's rows of A and of its share of B into shared memory, L2 prefetch hints
-//      for the x and y lines it will touch, and an L2 prefetch of the same work item's slabs of the next layer;
+//      for the x and y lines it will touch (and, when asked for, an L2 prefetch of the same work item's slabs of
+//      the next layer);
 //   4. the dependency wait (the kernel before, typically the layer's matrix multiply, wrote y);
 //   5. x into shared memory, shrink, release of the next kernel of the stream (its prologue, steps 2 and 3, then
 //      overlaps this kernel's exchange and expand), exchange, expand, y read-modify-write.
