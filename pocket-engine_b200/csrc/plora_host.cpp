@@ -864,9 +864,10 @@ int plora_apply(plora_t* h, const plora_hook* hook, const plora_step* step, uint
     for (auto& p : site.parts) total += p.rows;
     CUK(h, "site kernel",
        plora_launch_site((const void*)(uintptr_t)x, site.cols, site.cols, recs_of(h, hook->site), h->rec_cap,
-                         h->prefetch_next && hook->site + 1 < (int)h->sites.size() ? recs_of(h, hook->site + 1) : nullptr,
+                         hook->site + 1 < (int)h->sites.size() ? recs_of(h, hook->site + 1) : nullptr,
                          (void*)(uintptr_t)y, ldy, f32_out, (int)site.parts.size(), h->max_rank, total, work_cap,
-                         site.max_clusters, (h->early_x ? 1 : 0) | ((h->site_release >= 0 && h->site_release <= 4 ? h->site_release : (h->early_x ? 0 : 1)) << 1),
+                         site.max_clusters, (h->early_x ? 1 : 0) | ((h->site_release >= 0 && h->site_release <= 4 ? h->site_release : (h->early_x ? 0 : 1)) << 1) |
+                             (h->prefetch_next ? 16 : 0),
                          bounds_of(h, hook, rows, ldy), h->status, pdl, as_stream(stream)));
     if (h->mma_ok && rows >= step->run_min) {
         CUK(h, "shrink (tile path)",

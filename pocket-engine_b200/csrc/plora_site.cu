@@ -171,9 +171,9 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
     // The kernels after this one may start their prologues now: before their own waits they touch slabs and
     // launch records only (and x, where their caller vouched for it); every store of the path comes after a
     // wait, and every grid waits for its predecessor before it completes.
-    // mode: bit 0 = the caller vouched for x; bits 1-2 = when the next kernel of the stream is released (0: at
-    // once, 1: after the shrink, 2: after the exchange)
-    const int early_x = mode & 1, release_at = mode >> 1;  // (3, 4: after the wait, after A and x landed)
+    // mode: bit 0 = the caller vouched for x; bits 1-3 = when the next kernel of the stream is released (0: at
+    // once, 1: after the shrink, 2: after the exchange); bit 4 = ask L2 for the next layer's slabs too
+    const int early_x = mode & 1, release_at = (mode >> 1) & 7;  // (3, 4: after the wait, after A and x landed)
     bool triggered = release_at == 0;
     if (triggered) pdl_trigger();
     if (tid == 0) {
@@ -280,17 +280,19 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
             }
         }
         if (next_recs != nullptr && warp == 1 && blockIdx.y == 0) {
-            // an eighth of every slab of this work item at the next layer (same slot; the records are written
-            // for all layers at once)
+            // the same work item's launch record at the next layer (the records are written for all layers at
+            // once) is asked into L2, and, when the caller wants it, an eighth of each of its slabs
             const PloraRec* nr = next_recs + w;
-            if (crank == 0 && lane == 0) prefetch_l2(reinterpret_cast<const unsigned char*>(nr) + 128);  // the record's second line
-            const int4 head = __ldg(reinterpret_cast<const int4*>(nr));  // cnt, slot, rank, cols
-            if (head.x > 0 && head.z > 0) {
-                prefetch_eighth(__ldg(&nr->a), (uint64_t)head.z * (uint64_t)head.w * 2u, crank, lane);
+            if (crank == 0 && lane < 2) prefetch_l2(reinterpret_cast<const unsigned char*>(nr) + 128 * lane);
+            if (mode & 16) {
+                const int4 head = __ldg(reinterpret_cast<const int4*>(nr));  // cnt, slot, rank, cols
+                if (head.x > 0 && head.z > 0) {
+                    prefetch_eighth(__ldg(&nr->a), (uint64_t)head.z * (uint64_t)head.w * 2u, crank, lane);
 #pragma unroll 1
-                for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-                    const int rp = __ldg(&nr->r[p]);
-                    if (rp > 0) prefetch_eighth(__ldg(&nr->b[p]), (uint64_t)__ldg(&nr->rows[p]) * (uint64_t)rp * 2u, crank, lane);
+                    for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+                        const int rp = __ldg(&nr->r[p]);
+                        if (rp > 0) prefetch_eighth(__ldg(&nr->b[p]), (uint64_t)__ldg(&nr->rows[p]) * (uint64_t)rp * 2u, crank, lane);
+                    }
                 }
             }
         }
