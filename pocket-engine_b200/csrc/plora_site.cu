@@ -36,6 +36,7 @@
 #define SITE_CLUSTER 8
 #define SITE_THREADS 256
 #define SITE_WARPS PLORA_TILE_WARPS
+#define SITE_TOK 8  // tokens per pass over a work item
 
 namespace {
 
@@ -160,7 +161,7 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
     // A rows in groups of g_rows: group q at q * g_stride, its rows kb_pad apart. Once a group's rows are used up,
     // the warps' partial sums of those rows [warp][16][g_rows] take their place.
     unsigned char* As = dsm;
-    unsigned char* Xs = As + sh.aw_bytes;                   // x chunks [16][kb_pad]
+    unsigned char* Xs = As + sh.aw_bytes;                   // x chunks [8][kb_pad]
     unsigned char* Bs = Xs + sh.x_bytes;                    // this block's rows of B, part after part
     float* Sp = reinterpret_cast<float*>(Bs + sh.b_bytes);  // this block's partial S [16][rmax]
     // the summed S as three bf16 planes [16][sp_pad] (high, middle, low term) and a fourth plane that stays zero
@@ -198,7 +199,8 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
     // 8-row tiles x 16 inputs)
     const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_piece = lane >> 4;
     const int b_row = (lane & 7) + (lane >> 4) * 8, b_piece = (lane >> 3) & 1;
-    const uint32_t xs_lane = smem_u32(Xs) + (uint32_t)a_row * (uint32_t)sh.kb_pad + (uint32_t)a_piece * 16u;
+    // (the x tile has 8 rows: rows 8-15 of the multiply's token tile repeat them and their results are dropped)
+    const uint32_t xs_lane = smem_u32(Xs) + (uint32_t)(a_row & 7) * (uint32_t)sh.kb_pad + (uint32_t)a_piece * 16u;
     const uint32_t as_lane = smem_u32(As) + (uint32_t)b_row * (uint32_t)sh.kb_pad + (uint32_t)b_piece * 16u;
     const uint32_t s3_lane = smem_u32(S3) + (uint32_t)a_row * (uint32_t)sh.sp_pad + (uint32_t)a_piece * 16u;
     for (int w = blockIdx.z; w < rec_cap; w += gridDim.z) {
@@ -218,244 +220,249 @@ __global__ void __cluster_dims__(SITE_CLUSTER, 1, 1) __launch_bounds__(SITE_THRE
             __syncthreads();
             continue;
         }
-        // warp 1: the block's share of the output columns (lane p takes part p), then the copies of its rows of B
-        if (warp == 1) {
-            if (lane < PLORA_MAX_PARTS) column_share(srec, (int)blockIdx.y * SITE_CLUSTER + (int)crank, lane, sshare);
-            __syncwarp();
-            if (lane == 0) {
-                uint32_t total = 0;
-#pragma unroll
-                for (int p = 0; p < PLORA_MAX_PARTS; p++)
-                    total += (uint32_t)(sshare.hi[p] - sshare.lo[p]) * (uint32_t)srec.r[p] * 2u;
-                if (total > 0) {
-                    mbar_expect_tx(&bars[2], total);
-#pragma unroll
-                    for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-                        const uint32_t bytes = (uint32_t)(sshare.hi[p] - sshare.lo[p]) * (uint32_t)srec.r[p] * 2u;
-                        if (bytes > 0)
-                            bulk_g2s(Bs + sshare.boff[p],
-                                     reinterpret_cast<const bf16*>(srec.b[p]) + (size_t)sshare.lo[p] * srec.r[p], bytes, &bars[2]);
-                    }
-                }
-            }
-        }
-        // ---- slab requests (before the dependency wait): the block's rows of A, one bulk copy per row. The copies
-        // of the lanes of one warp are issued one after another, so the rows go round the warps: row r is lane
-        // r / 8 of warp r % 8. (The barrier's one arrival carries the whole byte count; copies that land before it
-        // only run the count down early.)
-        if (klen > 0) {
-            const bf16* A = reinterpret_cast<const bf16*>(srec.a) + k0;
-            if (tid == 0) mbar_expect_tx(&bars[0], (uint32_t)R * kbytes);
-            for (int r = warp + SITE_WARPS * lane; r < R; r += SITE_THREADS)
-                bulk_g2s(As + (size_t)(r >> 6) * sh.g_stride + (size_t)(r & 63) * sh.kb_pad, A + (size_t)r * K, kbytes, &bars[0]);
-        }
-        // a half step at the end of the rows multiplies zeros
-        if ((klen & 15) != 0)
-            for (int r = tid; r < R + PLORA_WORK_TOKENS; r += SITE_THREADS)
-                *reinterpret_cast<uint4*>((r < R ? As + (size_t)(r >> 6) * sh.g_stride + (size_t)(r & 63) * sh.kb_pad
-                                                 : Xs + (size_t)(r - R) * sh.kb_pad) + kbytes) = make_uint4(0u, 0u, 0u, 0u);
-        __syncthreads();  // the share is known to every warp
-        // ---- hints: the x and y lines this block will touch, and the next layer's slabs of this work item
-        if (!waited && warp >= 2) {
-            const int t1 = tid - 64, n1 = SITE_THREADS - 64;
-            if (klen > 0 && !early_x) {
-                const int lines = (int)((kbytes + 127) / 128);
-                for (int i = t1; i < cnt * lines; i += n1) {
-                    const int t = i / lines, l = i - t * lines;
-                    prefetch_l2(reinterpret_cast<const unsigned char*>(X + (size_t)srec.tok[t] * ldx + k0) + (size_t)l * 128);
-                }
-            }
-#pragma unroll 1
-            for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-                const int ncol = sshare.hi[p] - sshare.lo[p];
-                if (ncol <= 0) continue;
-                const size_t len = (size_t)ncol * esize;
-                const int lines = (int)((len + 127) / 128) + 1;
-                for (int i = t1; i < cnt * lines; i += n1) {
-                    const int t = i / lines, l = i - t * lines;
-                    const size_t start = ((size_t)srec.tok[t] * ldy + srec.off[p] + sshare.lo[p]) * esize;
-                    const size_t at = (start & ~(size_t)127) + (size_t)l * 128;
-                    if (at < start + len) prefetch_l2(reinterpret_cast<const unsigned char*>(Y) + at);
-                }
-            }
-        }
-        if (next_recs != nullptr && warp == 1 && blockIdx.y == 0) {
-            // the same work item's launch record at the next layer (the records are written for all layers at
-            // once) is asked into L2, and, when the caller wants it, an eighth of each of its slabs
-            const PloraRec* nr = next_recs + w;
-            if (crank == 0 && lane < 2) prefetch_l2(reinterpret_cast<const unsigned char*>(nr) + 128 * lane);
-            if (mode & 16) {
-                const int4 head = __ldg(reinterpret_cast<const int4*>(nr));  // cnt, slot, rank, cols
-                if (head.x > 0 && head.z > 0) {
-                    prefetch_eighth(__ldg(&nr->a), (uint64_t)head.z * (uint64_t)head.w * 2u, crank, lane);
-#pragma unroll 1
-                    for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-                        const int rp = __ldg(&nr->r[p]);
-                        if (rp > 0) prefetch_eighth(__ldg(&nr->b[p]), (uint64_t)__ldg(&nr->rows[p]) * (uint64_t)rp * 2u, crank, lane);
-                    }
-                }
-            }
-        }
-        if (!waited && !early_x) {
-            pdl_wait();
-            waited = true;
-        }
-        if (!triggered && release_at == 3) {
-            pdl_trigger();
-            triggered = true;
-        }
-        // y of this lane's first expand step (first part of the share), on its way while the shrink and the exchange run
-        uint4 pre0 = make_uint4(0u, 0u, 0u, 0u), pre1 = pre0;
-        int pre_part = -1;
-        if (waited) {
-#pragma unroll
-            for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-                if (pre_part < 0 && srec.r[p] > 0 && sshare.hi[p] > sshare.lo[p]) {
-                    pre_part = p;
-                    const size_t ybase = (size_t)srec.off[p] + sshare.lo[p];
-                    const int ncols = sshare.hi[p] - sshare.lo[p];
-                    const bool fast = cnt <= 8 && (ncols & 7) == 0 &&
-                                      ((reinterpret_cast<uintptr_t>(Y) | ((size_t)ldy * esize) | (ybase * esize)) & 15) == 0;
-                    const int c = warp * 32 + 8 * (lane & 3);
-                    if (fast && g < cnt && c < ncols) {
-                        const unsigned char* yp = reinterpret_cast<const unsigned char*>(Y) + ((size_t)srec.tok[g] * ldy + ybase + c) * esize;
-                        pre0 = __ldcg(reinterpret_cast<const uint4*>(yp));
-                        if (F32) pre1 = __ldcg(reinterpret_cast<const uint4*>(yp) + 1);
-                    }
-                }
-            }
-        }
-        // ---- shrink over this block's eighth of the inputs: warp q takes the 16-wide steps q, q + 8, ...
-        if (klen > 0) {
-            if (warp == 0) {
-                if (lane == 0) mbar_expect_tx(&bars[1], (uint32_t)cnt * kbytes);
+        // the work item's tokens, 8 at a time (a decoding batch rarely has more of one slot): the x tile has 8 rows,
+        // which is what lets the layers with the longest inputs keep their whole share of B in one block
+        for (int t0 = 0; t0 < cnt; t0 += SITE_TOK) {
+            const int cn = min(SITE_TOK, cnt - t0);
+            const int* tok = srec.tok + t0;
+            // warp 1: the block's share of the output columns (lane p takes part p), then the copies of its rows of B
+            if (warp == 1 && t0 == 0) {
+                if (lane < PLORA_MAX_PARTS) column_share(srec, (int)blockIdx.y * SITE_CLUSTER + (int)crank, lane, sshare);
                 __syncwarp();
-                if (lane < cnt) bulk_g2s(Xs + (size_t)lane * sh.kb_pad, X + (size_t)srec.tok[lane] * ldx + k0, kbytes, &bars[1]);
-            }
-            if (alive) alive = mbar_wait(&bars[0], ph_ax, status) && mbar_wait(&bars[1], ph_ax, status);
-            ph_ax ^= 1;
-        }
-        if (!triggered && release_at == 4) {
-            pdl_trigger();
-            triggered = true;
-        }
-        // rows of A in groups of 64 (8 tiles of 8): 32 accumulators per lane
-        for (int j0 = 0; j0 < R; j0 += 64) {
-            float acc[8][4];
-#pragma unroll
-            for (int i = 0; i < 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-            const int pairs = min(4, (R - j0) >> 4);  // 16-row pairs of tiles in this group
-            const uint32_t grp = (uint32_t)(j0 >> 6) * (uint32_t)sh.g_stride;
-            if (alive && klen > 0) {
-                const uint32_t xs_w = xs_lane + (uint32_t)warp * 32u, as_w = as_lane + grp + (uint32_t)warp * 32u;
-                const int n = (nks - warp + SITE_WARPS - 1) / SITE_WARPS;  // this warp's steps
-                if (pairs == 1) shrink_steps<1>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
-                else if (pairs == 2) shrink_steps<2>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
-                else if (pairs == 3) shrink_steps<3>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
-                else shrink_steps<4>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
-            }
-            __syncthreads();  // every warp is through with this group's rows of A: their place takes the partials
-            float* wp = reinterpret_cast<float*>(As + grp) + (size_t)warp * PLORA_WORK_TOKENS * sh.g_rows + t2;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                if (i < 2 * pairs) {
-                    if (g < cnt) *reinterpret_cast<float2*>(wp + g * sh.g_rows + i * 8) = make_float2(acc[i][0], acc[i][1]);
-                    if (g + 8 < cnt) *reinterpret_cast<float2*>(wp + (g + 8) * sh.g_rows + i * 8) = make_float2(acc[i][2], acc[i][3]);
+                if (lane == 0) {
+                    uint32_t total = 0;
+    #pragma unroll
+                    for (int p = 0; p < PLORA_MAX_PARTS; p++)
+                        total += (uint32_t)(sshare.hi[p] - sshare.lo[p]) * (uint32_t)srec.r[p] * 2u;
+                    if (total > 0) {
+                        mbar_expect_tx(&bars[2], total);
+    #pragma unroll
+                        for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+                            const uint32_t bytes = (uint32_t)(sshare.hi[p] - sshare.lo[p]) * (uint32_t)srec.r[p] * 2u;
+                            if (bytes > 0)
+                                bulk_g2s(Bs + sshare.boff[p],
+                                         reinterpret_cast<const bf16*>(srec.b[p]) + (size_t)sshare.lo[p] * srec.r[p], bytes, &bars[2]);
+                        }
+                    }
                 }
             }
-        }
-        __syncthreads();
-        // the eight warps' partials, added in warp order: warp q takes the token rows q, q + 8
-        for (int t = warp; t < cnt; t += SITE_WARPS) {
-            for (int j = lane; j < R; j += 32) {
-                const float* p = reinterpret_cast<const float*>(As + (size_t)(j >> 6) * sh.g_stride) + t * sh.g_rows + (j & 63);
-                float acc = p[0];
-#pragma unroll
-                for (int q = 1; q < SITE_WARPS; q++) acc += p[(size_t)q * PLORA_WORK_TOKENS * sh.g_rows];
-                Sp[t * sh.rmax + j] = acc;
+            // ---- slab requests (before the dependency wait): the block's rows of A, one bulk copy per row. The copies
+            // of the lanes of one warp are issued one after another, so the rows go round the warps: row r is lane
+            // r / 8 of warp r % 8. (The barrier's one arrival carries the whole byte count; copies that land before it
+            // only run the count down early.)
+            if (klen > 0) {
+                const bf16* A = reinterpret_cast<const bf16*>(srec.a) + k0;
+                if (tid == 0) mbar_expect_tx(&bars[0], (uint32_t)R * kbytes);
+                for (int r = warp + SITE_WARPS * lane; r < R; r += SITE_THREADS)
+                    bulk_g2s(As + (size_t)(r >> 6) * sh.g_stride + (size_t)(r & 63) * sh.kb_pad, A + (size_t)r * K, kbytes, &bars[0]);
             }
-        }
-        if (!triggered && release_at == 1) {
-            pdl_trigger();
-            triggered = true;
-        }
-        // ---- the eight partials meet: every block tells every block that its Sp is written, then reads all
-        // eight and adds them in block order
-        __syncthreads();
-        if (!met) {
-            cluster_wait();  // everybody's barriers exist
-            met = true;
-        }
-        if (tid < SITE_CLUSTER) mbar_arrive_peer(&bars[3], (uint32_t)tid);
-        if (alive) alive = mbar_wait_cluster(&bars[3], ph_s, status);
-        ph_s ^= 1;
-        for (int t = warp; t < cnt; t += SITE_WARPS) {
-            for (int j = lane; j < R; j += 32) {
-                const float* p = Sp + t * sh.rmax + j;
-                float v[SITE_CLUSTER];
-#pragma unroll
-                for (int q = 0; q < SITE_CLUSTER; q++) v[q] = ld_peer_f32(p, q);
-                float acc = v[0];
-#pragma unroll
-                for (int q = 1; q < SITE_CLUSTER; q++) acc += v[q];
-                // three bf16 terms whose sum is the f32 value
-                const bf16 hi = __float2bfloat16_rn(acc);
-                const float r1 = acc - __bfloat162float(hi);
-                const bf16 mid = __float2bfloat16_rn(r1);
-                const bf16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
-                unsigned char* s3 = S3 + (size_t)t * sh.sp_pad + (size_t)j * 2;
-                *reinterpret_cast<bf16*>(s3) = hi;
-                *reinterpret_cast<bf16*>(s3 + plane_bytes) = mid;
-                *reinterpret_cast<bf16*>(s3 + 2 * plane_bytes) = lo;
+            // a half step at the end of the rows multiplies zeros
+            if ((klen & 15) != 0)
+                for (int r = tid; r < R + SITE_TOK; r += SITE_THREADS)
+                    *reinterpret_cast<uint4*>((r < R ? As + (size_t)(r >> 6) * sh.g_stride + (size_t)(r & 63) * sh.kb_pad
+                                                     : Xs + (size_t)(r - R) * sh.kb_pad) + kbytes) = make_uint4(0u, 0u, 0u, 0u);
+            __syncthreads();  // the share is known to every warp
+            // ---- hints: the x and y lines this block will touch, and the next layer's slabs of this work item
+            if (!waited && warp >= 2) {
+                const int t1 = tid - 64, n1 = SITE_THREADS - 64;
+                if (klen > 0 && !early_x) {
+                    const int lines = (int)((kbytes + 127) / 128);
+                    for (int i = t1; i < cn * lines; i += n1) {
+                        const int t = i / lines, l = i - t * lines;
+                        prefetch_l2(reinterpret_cast<const unsigned char*>(X + (size_t)tok[t] * ldx + k0) + (size_t)l * 128);
+                    }
+                }
+    #pragma unroll 1
+                for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+                    const int ncol = sshare.hi[p] - sshare.lo[p];
+                    if (ncol <= 0) continue;
+                    const size_t len = (size_t)ncol * esize;
+                    const int lines = (int)((len + 127) / 128) + 1;
+                    for (int i = t1; i < cn * lines; i += n1) {
+                        const int t = i / lines, l = i - t * lines;
+                        const size_t start = ((size_t)tok[t] * ldy + srec.off[p] + sshare.lo[p]) * esize;
+                        const size_t at = (start & ~(size_t)127) + (size_t)l * 128;
+                        if (at < start + len) prefetch_l2(reinterpret_cast<const unsigned char*>(Y) + at);
+                    }
+                }
             }
-        }
-        cluster_arrive_relaxed();  // my reads of the others' partials are done
-        if (!triggered) {
-            pdl_trigger();
-            triggered = true;
-        }
-        if (!waited) {             // early_x: everything so far ran ahead of the kernel before; y must not
-            pdl_wait();
-            waited = true;
-        }
-        __syncthreads();
-        // ---- expand over this block's share of the output columns
-        bool okb = true;
-        {
-            int total = 0;
-#pragma unroll
-            for (int p = 0; p < PLORA_MAX_PARTS; p++) total += sshare.hi[p] - sshare.lo[p];
-            if (total > 0) {
-                if (alive) okb = mbar_wait(&bars[2], ph_b, status);
-                ph_b ^= 1;
+            if (next_recs != nullptr && warp == 1 && blockIdx.y == 0 && t0 == 0) {
+                // the same work item's launch record at the next layer (the records are written for all layers at
+                // once) is asked into L2, and, when the caller wants it, an eighth of each of its slabs
+                const PloraRec* nr = next_recs + w;
+                if (crank == 0 && lane < 2) prefetch_l2(reinterpret_cast<const unsigned char*>(nr) + 128 * lane);
+                if (mode & 16) {
+                    const int4 head = __ldg(reinterpret_cast<const int4*>(nr));  // cn, slot, rank, cols
+                    if (head.x > 0 && head.z > 0) {
+                        prefetch_eighth(__ldg(&nr->a), (uint64_t)head.z * (uint64_t)head.w * 2u, crank, lane);
+    #pragma unroll 1
+                        for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+                            const int rp = __ldg(&nr->r[p]);
+                            if (rp > 0) prefetch_eighth(__ldg(&nr->b[p]), (uint64_t)__ldg(&nr->rows[p]) * (uint64_t)rp * 2u, crank, lane);
+                        }
+                    }
+                }
             }
-        }
-        if (!okb) alive = false;
-        if (alive) {
-            const int tok0 = g < cnt ? srec.tok[g] : -1, tok1 = g + 8 < cnt ? srec.tok[g + 8] : -1;
-#pragma unroll 1
-            for (int p = 0; p < PLORA_MAX_PARTS; p++) {
-                const int r = srec.r[p];
-                const int lo = sshare.lo[p], hi = sshare.hi[p];
-                if (r == 0 || hi <= lo) continue;
-                const uint32_t s3_part = s3_lane + (uint32_t)srec.r_off[p] * 2u;
-                const uint32_t bs_lane = smem_u32(Bs) + (uint32_t)sshare.boff[p] + (uint32_t)b_row * (uint32_t)r * 2u + (uint32_t)b_piece * 16u;
-                const size_t ybase = (size_t)srec.off[p] + lo;
-                // fast form: at most 8 tokens, and y rows that move in 16-byte pieces
-                const bool fast = cnt <= 8 && ((hi - lo) & 7) == 0 && ((reinterpret_cast<uintptr_t>(Y) | ((size_t)ldy * esize) | (ybase * esize)) & 15) == 0;
-                if (fast) {
-                    const int tok = g < cnt ? srec.tok[g] : -1;
-                    const uint32_t s3p = smem_u32(S3) + (uint32_t)srec.r_off[p] * 2u, bsp = smem_u32(Bs) + (uint32_t)sshare.boff[p];
-                    const bool pre = p == pre_part;
-                    if (r == 16) expand_fast<1, F32>(s3p, (uint32_t)sh.sp_pad, plane_bytes, bsp, r, hi - lo, Y, ldy, ybase, tok, warp, lane, pre, pre0, pre1);
-                    else if (r == 32) expand_fast<2, F32>(s3p, (uint32_t)sh.sp_pad, plane_bytes, bsp, r, hi - lo, Y, ldy, ybase, tok, warp, lane, pre, pre0, pre1);
-                    else expand_fast<0, F32>(s3p, (uint32_t)sh.sp_pad, plane_bytes, bsp, r, hi - lo, Y, ldy, ybase, tok, warp, lane, pre, pre0, pre1);
-                } else if (r == 16) expand_part<1, F32>(s3_part, plane_bytes, bs_lane, r, hi - lo, Y, ldy, ybase, tok0, tok1, warp, t2);
-                else expand_part<0, F32>(s3_part, plane_bytes, bs_lane, r, hi - lo, Y, ldy, ybase, tok0, tok1, warp, t2);
+            if (!waited && !early_x) {
+                pdl_wait();
+                waited = true;
             }
+            if (!triggered && release_at == 3) {
+                pdl_trigger();
+                triggered = true;
+            }
+            // y of this lane's first expand step (first part of the share), on its way while the shrink and the exchange run
+            uint4 pre0 = make_uint4(0u, 0u, 0u, 0u), pre1 = pre0;
+            int pre_part = -1;
+            if (waited) {
+    #pragma unroll
+                for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+                    if (pre_part < 0 && srec.r[p] > 0 && sshare.hi[p] > sshare.lo[p]) {
+                        pre_part = p;
+                        const size_t ybase = (size_t)srec.off[p] + sshare.lo[p];
+                        const int ncols = sshare.hi[p] - sshare.lo[p];
+                        const bool fast = cn <= 8 && (ncols & 7) == 0 &&
+                                          ((reinterpret_cast<uintptr_t>(Y) | ((size_t)ldy * esize) | (ybase * esize)) & 15) == 0;
+                        const int c = warp * 32 + 8 * (lane & 3);
+                        if (fast && g < cn && c < ncols) {
+                            const unsigned char* yp = reinterpret_cast<const unsigned char*>(Y) + ((size_t)tok[g] * ldy + ybase + c) * esize;
+                            pre0 = __ldcg(reinterpret_cast<const uint4*>(yp));
+                            if (F32) pre1 = __ldcg(reinterpret_cast<const uint4*>(yp) + 1);
+                        }
+                    }
+                }
+            }
+            // ---- shrink over this block's eighth of the inputs: warp q takes the 16-wide steps q, q + 8, ...
+            if (klen > 0) {
+                if (warp == 0) {
+                    if (lane == 0) mbar_expect_tx(&bars[1], (uint32_t)cn * kbytes);
+                    __syncwarp();
+                    if (lane < cn) bulk_g2s(Xs + (size_t)lane * sh.kb_pad, X + (size_t)tok[lane] * ldx + k0, kbytes, &bars[1]);
+                }
+                if (alive) alive = mbar_wait(&bars[0], ph_ax, status) && mbar_wait(&bars[1], ph_ax, status);
+                ph_ax ^= 1;
+            }
+            if (!triggered && release_at == 4) {
+                pdl_trigger();
+                triggered = true;
+            }
+            // rows of A in groups of 64 (8 tiles of 8): 32 accumulators per lane
+            for (int j0 = 0; j0 < R; j0 += 64) {
+                float acc[8][4];
+    #pragma unroll
+                for (int i = 0; i < 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+                const int pairs = min(4, (R - j0) >> 4);  // 16-row pairs of tiles in this group
+                const uint32_t grp = (uint32_t)(j0 >> 6) * (uint32_t)sh.g_stride;
+                if (alive && klen > 0) {
+                    const uint32_t xs_w = xs_lane + (uint32_t)warp * 32u, as_w = as_lane + grp + (uint32_t)warp * 32u;
+                    const int n = (nks - warp + SITE_WARPS - 1) / SITE_WARPS;  // this warp's steps
+                    if (pairs == 1) shrink_steps<1>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
+                    else if (pairs == 2) shrink_steps<2>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
+                    else if (pairs == 3) shrink_steps<3>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
+                    else shrink_steps<4>(acc, xs_w, as_w, (uint32_t)sh.kb_pad, n);
+                }
+                __syncthreads();  // every warp is through with this group's rows of A: their place takes the partials
+                float* wp = reinterpret_cast<float*>(As + grp) + (size_t)warp * PLORA_WORK_TOKENS * sh.g_rows + t2;
+    #pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    if (i < 2 * pairs) {
+                        if (g < cn) *reinterpret_cast<float2*>(wp + g * sh.g_rows + i * 8) = make_float2(acc[i][0], acc[i][1]);
+                    }
+                }
+            }
+            __syncthreads();
+            // the eight warps' partials, added in warp order: warp q takes the token rows q, q + 8
+            for (int t = warp; t < cn; t += SITE_WARPS) {
+                for (int j = lane; j < R; j += 32) {
+                    const float* p = reinterpret_cast<const float*>(As + (size_t)(j >> 6) * sh.g_stride) + t * sh.g_rows + (j & 63);
+                    float acc = p[0];
+    #pragma unroll
+                    for (int q = 1; q < SITE_WARPS; q++) acc += p[(size_t)q * PLORA_WORK_TOKENS * sh.g_rows];
+                    Sp[t * sh.rmax + j] = acc;
+                }
+            }
+            if (!triggered && release_at == 1) {
+                pdl_trigger();
+                triggered = true;
+            }
+            // ---- the eight partials meet: every block tells every block that its Sp is written, then reads all
+            // eight and adds them in block order
+            __syncthreads();
+            if (!met) {
+                cluster_wait();  // everybody's barriers exist
+                met = true;
+            }
+            if (tid < SITE_CLUSTER) mbar_arrive_peer(&bars[3], (uint32_t)tid);
+            if (alive) alive = mbar_wait_cluster(&bars[3], ph_s, status);
+            ph_s ^= 1;
+            for (int t = warp; t < cn; t += SITE_WARPS) {
+                for (int j = lane; j < R; j += 32) {
+                    const float* p = Sp + t * sh.rmax + j;
+                    float v[SITE_CLUSTER];
+    #pragma unroll
+                    for (int q = 0; q < SITE_CLUSTER; q++) v[q] = ld_peer_f32(p, q);
+                    float acc = v[0];
+    #pragma unroll
+                    for (int q = 1; q < SITE_CLUSTER; q++) acc += v[q];
+                    // three bf16 terms whose sum is the f32 value
+                    const bf16 hi = __float2bfloat16_rn(acc);
+                    const float r1 = acc - __bfloat162float(hi);
+                    const bf16 mid = __float2bfloat16_rn(r1);
+                    const bf16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+                    unsigned char* s3 = S3 + (size_t)t * sh.sp_pad + (size_t)j * 2;
+                    *reinterpret_cast<bf16*>(s3) = hi;
+                    *reinterpret_cast<bf16*>(s3 + plane_bytes) = mid;
+                    *reinterpret_cast<bf16*>(s3 + 2 * plane_bytes) = lo;
+                }
+            }
+            cluster_arrive_relaxed();  // my reads of the others' partials are done
+            if (!triggered) {
+                pdl_trigger();
+                triggered = true;
+            }
+            if (!waited) {             // early_x: everything so far ran ahead of the kernel before; y must not
+                pdl_wait();
+                waited = true;
+            }
+            __syncthreads();
+            // ---- expand over this block's share of the output columns
+            bool okb = true;
+            {
+                int total = 0;
+    #pragma unroll
+                for (int p = 0; p < PLORA_MAX_PARTS; p++) total += sshare.hi[p] - sshare.lo[p];
+                if (total > 0 && t0 == 0) {  // (a later pass finds the rows of B in place)
+                    if (alive) okb = mbar_wait(&bars[2], ph_b, status);
+                    ph_b ^= 1;
+                }
+            }
+            if (!okb) alive = false;
+            if (alive) {
+                const int tok0 = g < cn ? tok[g] : -1, tok1 = g + 8 < cn ? tok[g + 8] : -1;
+    #pragma unroll 1
+                for (int p = 0; p < PLORA_MAX_PARTS; p++) {
+                    const int r = srec.r[p];
+                    const int lo = sshare.lo[p], hi = sshare.hi[p];
+                    if (r == 0 || hi <= lo) continue;
+                    const uint32_t s3_part = s3_lane + (uint32_t)srec.r_off[p] * 2u;
+                    const uint32_t bs_lane = smem_u32(Bs) + (uint32_t)sshare.boff[p] + (uint32_t)b_row * (uint32_t)r * 2u + (uint32_t)b_piece * 16u;
+                    const size_t ybase = (size_t)srec.off[p] + lo;
+                    // fast form: at most 8 tokens, and y rows that move in 16-byte pieces
+                    const bool fast = cn <= 8 && ((hi - lo) & 7) == 0 && ((reinterpret_cast<uintptr_t>(Y) | ((size_t)ldy * esize) | (ybase * esize)) & 15) == 0;
+                    if (fast) {
+                        const int tk = g < cn ? tok[g] : -1;
+                        const uint32_t s3p = smem_u32(S3) + (uint32_t)srec.r_off[p] * 2u, bsp = smem_u32(Bs) + (uint32_t)sshare.boff[p];
+                        const bool pre = p == pre_part;
+                        if (r == 16) expand_fast<1, F32>(s3p, (uint32_t)sh.sp_pad, plane_bytes, bsp, r, hi - lo, Y, ldy, ybase, tk, warp, lane, pre, pre0, pre1);
+                        else if (r == 32) expand_fast<2, F32>(s3p, (uint32_t)sh.sp_pad, plane_bytes, bsp, r, hi - lo, Y, ldy, ybase, tk, warp, lane, pre, pre0, pre1);
+                        else expand_fast<0, F32>(s3p, (uint32_t)sh.sp_pad, plane_bytes, bsp, r, hi - lo, Y, ldy, ybase, tk, warp, lane, pre, pre0, pre1);
+                    } else if (r == 16) expand_part<1, F32>(s3_part, plane_bytes, bs_lane, r, hi - lo, Y, ldy, ybase, tok0, tok1, warp, t2);
+                    else expand_part<0, F32>(s3_part, plane_bytes, bs_lane, r, hi - lo, Y, ldy, ybase, tok0, tok1, warp, t2);
+                }
+            }
+            cluster_wait();   // nobody reads my partials any more: they may be overwritten (or the block may leave)
+            __syncthreads();  // shared memory is reused by the next pass or work item
         }
-        cluster_wait();   // nobody reads my partials any more: they may be overwritten (or the block may leave)
-        __syncthreads();  // shared memory is reused by the next work item
     }
     if (!met) cluster_wait();  // a block must not leave while a peer may still be arriving at the start-up barrier
     // A grid completes only after the grids before it. Blocks with work have waited; of the blocks that found none,
@@ -482,7 +489,7 @@ Plan plan_for(int K, int parts, int max_rank, int total_rows, int nsub) {
     const size_t a = (size_t)s.g_rows * s.kb_pad, wsum = (size_t)SITE_WARPS * PLORA_WORK_TOKENS * s.g_rows * 4;
     s.g_stride = (int)(((a > wsum ? a : wsum) + 127) & ~(size_t)127);
     s.aw_bytes = s.g_stride * ((s.rmax + 63) / 64);
-    s.x_bytes = (int)(((size_t)PLORA_WORK_TOKENS * s.kb_pad + 127) & ~(size_t)127);
+    s.x_bytes = (int)(((size_t)SITE_TOK * s.kb_pad + 127) & ~(size_t)127);
     const int share = ((total_rows + nsub * SITE_CLUSTER - 1) / (nsub * SITE_CLUSTER) + 1) & ~1;
     // the tile loads of the last columns of a part may run up to 31 rows past the share
     s.b_bytes = (int)((((size_t)share + 32 * parts) * max_rank * 2 + 127) & ~(size_t)127);
