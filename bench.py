@@ -286,11 +286,13 @@ def run_ours(args, rank, world, local_rank):
     # device metadata build + grouping, the block, D2H of y
     # Two steps are in flight at a time (two streams, two result buffers; consecutive steps use different copies),
     # so the copy of one step's inputs overlaps the other's kernels and result copy; the host waits for step i - 1
-    # after issuing step i.
-    e2e_sets = sets if copies >= 2 else sets + [make_set()]  # two steps in flight need two sets of buffers
+    # after issuing step i. (--e2e-depth: one step in flight runs at 312 us per step, two at 181, three at 188.)
+    e2e_sets = list(sets)
+    while len(e2e_sets) < max(2, args.e2e_depth):  # steps in flight need their own sets of buffers
+        e2e_sets.append(make_set())
     torch.cuda.synchronize()
-    depth = 2
-    lanes = [main, torch.cuda.Stream(device=dev)]
+    depth = max(1, min(3, args.e2e_depth))
+    lanes = [main] + [torch.cuda.Stream(device=dev) for _ in range(depth - 1)]
     y_out = [torch.empty(sets[0]["yreg"].numel(), dtype=torch.int16).pin_memory() for _ in range(depth)]
     h2d = in_host.numel() * 2 + meta_host.numel() * 4
     d2h = y_out[0].numel() * 2
@@ -332,10 +334,10 @@ def run_ours(args, rank, world, local_rank):
                     e2e_graphs[(k, lane)].replay()
             else:
                 e2e_issue(e2e_sets[k], lane)
-            if depth == 2 and i >= 1:
-                lanes[(first + i - 1) % depth].synchronize()
-            elif depth == 1:
+            if depth == 1:
                 lanes[0].synchronize()
+            elif i >= depth - 1:  # the host runs depth - 1 steps ahead of the device
+                lanes[(first + i - (depth - 1)) % depth].synchronize()
         for s in lanes:
             s.synchronize()
 
@@ -1058,6 +1060,7 @@ def main():
     ap.add_argument("--inner-repeats", type=int, default=50,
                     help="decode workload: passes of the block per timed step (the result is reported per pass)")
     ap.add_argument("--two-part", action="store_true", help="fp8 workload: the engine's two-part gate + up layer (4096 -> 24576)")
+    ap.add_argument("--e2e-depth", type=int, default=2, help="steps in flight in the end-to-end measurement (1 to 3)")
     ap.add_argument("--no-e2e-graph", action="store_true", help="end-to-end steps as individual calls instead of one CUDA graph per copy")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel layer set that the default run appends")
     ap.add_argument("--streams", type=int, default=1, choices=[1, 2],
