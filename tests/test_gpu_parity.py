@@ -148,6 +148,8 @@ RAGGED = [
     ("one-slot", [40], [1], [24], 512, [("a", 96), ("b", 32), ("c", 32), ("d", 64)]),
     ("odd-k", [5, 1, 1], [2, 1, 2], [8, 40], 1096, [("a", 130)]),
     ("one-token", [1], [1], [1], 64, [("a", 2)]),
+    # 9 to 12 tokens of a slot: the cluster kernel takes a work item's tokens 8 at a time (second passes of 1 to 4)
+    ("second-passes", [9, 10, 12, 8], [1, 2, 3, 2], [16, 32, 16], 512, [("a", 256), ("b", 64)]),
 ]
 
 
