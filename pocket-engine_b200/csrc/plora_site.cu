@@ -1,5 +1,5 @@
 // One kernel per layer for the few-token work items: a thread-block cluster of 8 blocks takes one work item (up
-// to 16 tokens of one slot) and one group of its output columns. Block q of the cluster shrinks over the q-th
+// to 16 tokens of one slot, 8 at a time) and one group of its output columns. Block q of the cluster shrinks over the q-th
 // eighth of the input features; the partial sums meet through distributed shared memory (no trip through global
 // memory, no second launch); every block then expands its eighth of the cluster's columns. Replaces the
 // lora_shrink + lora_expand pair of src/kernels/lora.cuh:23-126 when x and y are both ready at the call (after
@@ -18,8 +18,9 @@
 // measured: released at kernel start, the next layer's blocks take the places that this layer's own late clusters
 // need (a B200 holds about 33 clusters of this kernel, two neighbouring layers can need 48) and sit in their wait.
 //
-// Arithmetic: 16-token tiles on the warp-level tensor-core instruction (m16n8k16, bf16 in, f32 accumulate), the
-// shape the engine's own kernels use for their 16-token tiles. On the CUDA cores the step is bound by
+// Arithmetic: tiles of the warp-level tensor-core instruction (m16n8k16, bf16 in, f32 accumulate), the shape the
+// engine's own kernels use for their 16-token tiles; here a tile carries 8 tokens, and in the expand its other 8
+// rows carry a second term of S (plora_tiles.cuh). On the CUDA cores the step is bound by
 // instruction issue (one conversion per bf16 element plus one multiply-add per token), not by memory; a 128-row
 // tcgen05 tile would spend 1/8 or less of its rows on a work item. The f32 intermediate enters the expand as
 // three bf16 terms (high, middle, low part), whose products with bf16 B are exact in f32, so no precision is
