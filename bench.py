@@ -326,6 +326,9 @@ def run_ours(args, rank, world, local_rank):
                 e2e_graphs[(k, lane)] = g
         torch.cuda.synchronize()
 
+    ahead = max(1, args.e2e_ahead)
+    done = [torch.cuda.Event() for _ in range(ahead + 1)]
+
     def e2e_run(first, count):
         for i in range(count):
             k, lane = (first + i) % len(e2e_sets), (first + i) % depth
@@ -334,10 +337,15 @@ def run_ours(args, rank, world, local_rank):
                     e2e_graphs[(k, lane)].replay()
             else:
                 e2e_issue(e2e_sets[k], lane)
+            # The host waits for the step issued `ahead` steps ago before it issues the next one. Stream order alone
+            # keeps the buffers safe (a copy and a result buffer always meet the same lane); the wait only bounds how
+            # far the host runs ahead of the device, and at one step ahead its wake-up and launch time (some 40 us)
+            # showed up in every step.
+            done[i % len(done)].record(lanes[lane])
             if depth == 1:
                 lanes[0].synchronize()
-            elif i >= depth - 1:  # the host runs depth - 1 steps ahead of the device
-                lanes[(first + i - (depth - 1)) % depth].synchronize()
+            elif i >= ahead:
+                done[(i - ahead) % len(done)].synchronize()
         for s in lanes:
             s.synchronize()
 
@@ -427,7 +435,7 @@ def run_ours(args, rank, world, local_rank):
                 "early_x": bool(args.early_x), "inner_repeats": inner,
                 "timed_region": f"{args.steps} steps x {inner} passes of the block; value and ms_per_step are per pass"},
         "e2e": {"value": world * wl.tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps, "steps_in_flight": depth,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps, "steps_in_flight": depth, "host_runs_ahead": ahead,
                 "launch": "one CUDA graph per copy and lane (copies, metadata kernels, layers)" if e2e_graphs else "individual calls"},
         "gpu_launches": ((4 if args.path == "apply" else 8) if decode else 16) * args.steps * inner,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
@@ -1060,6 +1068,7 @@ def main():
     ap.add_argument("--inner-repeats", type=int, default=50,
                     help="decode workload: passes of the block per timed step (the result is reported per pass)")
     ap.add_argument("--two-part", action="store_true", help="fp8 workload: the engine's two-part gate + up layer (4096 -> 24576)")
+    ap.add_argument("--e2e-ahead", type=int, default=4, help="steps the host may run ahead of the device in the end-to-end measurement")
     ap.add_argument("--e2e-depth", type=int, default=2, help="steps in flight in the end-to-end measurement (1 to 3)")
     ap.add_argument("--no-e2e-graph", action="store_true", help="end-to-end steps as individual calls instead of one CUDA graph per copy")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel layer set that the default run appends")
